@@ -1,0 +1,443 @@
+#!/usr/bin/env python3
+"""Benchmark of the FP8-KV decode-attention step (64 layers) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+
+A "step" is one decode step of the attention path for all 64 layers: quantize-and-append of the
+new token's K/V plus split-K GQA attention over the FP8 cache, replayed as one CUDA graph.
+Headline workload (cfg2): depth 8192, capacity 8192, bs=1, H_q=40, H_kv=8, D=128; the cache is
+full, so every step re-quantises the newest token into the last slot and attends 8192 tokens.
+Other depths of the metric (512, 32768) are measured in the same run and reported under
+"per_depth".  With N > 1 ranks the KV heads are sharded (tensor parallel, strong scaling) and
+every step ends with an all-gather of the per-head outputs over NVLink.
+
+Synthetic data: seeded N(0,1) bf16 K/V quantised to e4m3 with per-(layer, kv head) absmax/448
+scales by the library's own calibration + bulk-append kernels (the reference's fixed-depth
+prompts are token ids for a checkpoint that is not available).
+
+`--impl reference` times the CPU restatement of the reference's padded torch attention
+(oracle/ref_attention.py) on the host cores instead; it is the baseline arm, not the product.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_LAYERS, H_Q, H_KV, D = 64, 40, 8, 128
+METRIC = "decode-attn us/step (64 layers)"
+WORKLOADS = {
+    # name: (depth, capacity, advance)
+    "cfg1": (512, 1024, True),
+    "cfg2": (8192, 8192, False),
+    "cfg3": (32768, 32768 + 256, True),
+}
+PEAK_FALLBACK_GBS = 6650.0
+REF_SAMPLE_LAYERS = 4
+
+
+def kv_bytes_per_step(depth: int, h_kv: int = H_KV) -> int:
+    """Algorithmic bytes of one step: K and V e4m3 bytes of every attended token, all layers."""
+    return N_LAYERS * h_kv * depth * D * 2
+
+
+def load_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return PEAK_FALLBACK_GBS, "fallback"
+
+
+def load_traffic(workload: str):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
+    p = ROOT / "profiles" / "dram_traffic.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()).get(workload)
+        except Exception:  # noqa: BLE001
+            return None
+    return None
+
+
+class ClockSampler:
+    """SM clock and throttle reasons read through NVML (read-only) every few ms by a thread
+    while the timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, torch, index: int, period_s: float = 0.004):
+        self.samples, self.bits, self.max_mhz, self.period = [], 0, None, period_s
+        self.stop_flag = threading.Event()
+        self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode() if not uuid.startswith("GPU-") else uuid.encode())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001 - NVML missing: clocks are reported as unknown
+            self.handle = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop_flag.set()
+        if self.handle is not None:
+            self.thread.join(timeout=1)
+
+    def summary(self) -> dict:
+        reasons = sorted(name for bit, name in self.REASONS.items() if self.bits & bit)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the oracle port on the host cores
+# ------------------------------------------------------------------------------------------
+def run_reference(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import torch
+    from oracle import ref_attention as oracle
+    depth, cap, _ = WORKLOADS[args.workload]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    q, k, v = oracle.make_inputs(0, H_Q, H_KV, D, depth)
+    sk, sv = oracle.head_scales(k), oracle.head_scales(v)
+    kb, vb = oracle.quantize_per_head(k, sk), oracle.quantize_per_head(v, sv)
+    cap = max(cap, depth)
+
+    def sample_step():
+        for _ in range(REF_SAMPLE_LAYERS):
+            oracle.padded_fp8_reference(q, kb, vb, sk, sv, cap)
+
+    for _ in range(args.warmup):
+        sample_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        sample_step()
+    dt = (time.perf_counter() - t0) / args.steps
+    us_per_step = dt * 1e6 * (N_LAYERS / REF_SAMPLE_LAYERS)
+    sample = (f"each timed step = {REF_SAMPLE_LAYERS} of {N_LAYERS} layers of dequant+pad+padded torch attention "
+              f"at depth {depth}, scaled x{N_LAYERS // REF_SAMPLE_LAYERS}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": us_per_step, "unit": "us/step", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": us_per_step / 1e3, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (torch CPU, fp32 softmax)", "data": "synthetic",
+        "config": {"workload": workload_name(args.workload, depth, cap), "timing": "host wall clock"},
+        "cpu_baseline": {"value": us_per_step, "unit": "us/step", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": us_per_step, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_name(key: str, depth: int, cap: int) -> str:
+    return (f"{key}: {N_LAYERS}-layer bs=1 decode attention, depth {depth}, capacity {cap}, H_q={H_Q} H_kv={H_KV} "
+            f"D={D}, FP8-e4m3 KV with per-(layer,kv-head) scales, append+attend per step")
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+class StepRunner:
+    """One workload resident on one GPU: cache, static step buffers, captured graph."""
+
+    def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1):
+        self.pkg, self.torch, self.device, self.depth, self.advance = pkg, torch, device, depth, advance
+        self.h_q, self.h_kv, self.dist, self.world = h_q, h_kv, dist, world
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.cache = pkg.FP8StaticCache(N_LAYERS, 1, h_q, h_kv, D, cap, device=device)
+        prefix = depth if advance else depth - 1      # cfg2: slot depth-1 is rewritten by every step
+        chunk = 8192
+        scales_done = False
+        for t0 in range(0, prefix, chunk):
+            n = min(chunk, prefix - t0)
+            k = torch.randn(N_LAYERS, 1, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
+            v = torch.randn(N_LAYERS, 1, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
+            self.cache.prefill(k, v, calibrate=not scales_done)
+            scales_done = True
+        self.start_pos = prefix
+        self.q = torch.randn(N_LAYERS, 1, h_q, D, generator=g, device=device, dtype=torch.bfloat16)
+        self.k_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
+        self.v_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
+        self.out = torch.empty_like(self.q)
+        self.full_out = torch.empty(world, N_LAYERS, 1, h_q, D, device=device, dtype=torch.bfloat16) if world > 1 else None
+        self.graph = None
+
+    def launch_step(self):
+        c = self.cache
+        self.pkg.append_decode(self.q, self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
+                               workspace=c.workspace, advance=self.advance, out=self.out)
+
+    def gather(self):
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.full_out, self.out)
+
+    def capture(self):
+        torch = self.torch
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self.launch_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.reset_pos()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.launch_step()
+        torch.cuda.synchronize()
+
+    def reset_pos(self):
+        self.cache.seq_pos.fill_(self.start_pos)
+
+    def step(self):
+        self.graph.replay()
+        self.gather()
+
+    def kernels_per_step(self) -> int:
+        return 3 if self.advance else 2      # append, attention(+fused combine), position bump
+
+
+def barrier(dist, world):
+    if world > 1:
+        dist.barrier()
+
+
+def timed_steps(torch, dist, world, runner, steps, warmup, sampler=None) -> float:
+    """Seconds per step on the device: W warm-up steps, then K steps between CUDA events,
+    barrier + synchronize on both sides, max over ranks."""
+    runner.reset_pos()
+    for _ in range(warmup):
+        runner.step()
+    torch.cuda.synchronize()
+    barrier(dist, world)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        runner.step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier(dist, world)
+    sec = e0.elapsed_time(e1) / 1e3 / steps
+    if world > 1:
+        t = torch.tensor([sec], device=runner.device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    return sec
+
+
+def timed_kernel(torch, runner, steps, warmup) -> float:
+    """Average duration of the attention kernel alone (back-to-back launches on the current
+    stream, CUDA events on that stream)."""
+    c = runner.cache
+    off = 0 if runner.advance else 1
+
+    def launch():
+        runner.pkg.decode_attention(runner.q, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
+                                    workspace=c.workspace, seq_len_offset=off, out=runner.out)
+    runner.reset_pos()
+    if runner.advance:
+        c.seq_pos.fill_(runner.depth)
+    for _ in range(warmup):
+        launch()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    runner.reset_pos()
+    return e0.elapsed_time(e1) / 1e3 / steps
+
+
+def timed_e2e(torch, dist, world, runner, steps, warmup) -> tuple[float, int, int]:
+    """Through the public API with HOST buffers: per step, pinned-host q/k/v -> device, the
+    captured step, device -> pinned-host output, and a synchronize (the caller needs the result)."""
+    hq = [runner.q.cpu().pin_memory() for _ in range(2)]
+    hk = [runner.k_new.cpu().pin_memory() for _ in range(2)]
+    hv = [runner.v_new.cpu().pin_memory() for _ in range(2)]
+    src = runner.full_out if world > 1 else runner.out
+    hout = torch.empty(src.shape, dtype=src.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in (hq[0], hk[0], hv[0]))
+    d2h = hout.numel() * hout.element_size()
+
+    def one(i):
+        runner.q.copy_(hq[i & 1], non_blocking=True)
+        runner.k_new.copy_(hk[i & 1], non_blocking=True)
+        runner.v_new.copy_(hv[i & 1], non_blocking=True)
+        runner.step()
+        hout.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+
+    runner.reset_pos()
+    for i in range(warmup):
+        one(i)
+    barrier(dist, world)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / steps
+    barrier(dist, world)
+    sec = max(e0.elapsed_time(e1) / 1e3 / steps, wall)
+    if world > 1:
+        t = torch.tensor([sec], device=runner.device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    return sec, h2d, d2h
+
+
+def cpu_baseline(depth: int, cap: int) -> dict:
+    from oracle import ref_attention as oracle
+    threads = os.cpu_count() or 1
+    layers, repeats = 4, 2
+    r = oracle.cpu_attention_seconds(H_Q, H_KV, D, depth, max(cap, depth), layers, repeats, threads)
+    return {"value": r["full_s_per_layer"] * N_LAYERS * 1e6, "unit": "us/step", "cores": threads, "kind": "port",
+            "attn_only_us_per_step": r["attn_s_per_layer"] * N_LAYERS * 1e6,
+            "sample": f"median of {r['samples']} single-layer runs (dequant + pad + padded torch attention) at depth "
+                      f"{depth}, capacity {max(cap, depth)}, scaled x{N_LAYERS} layers"}
+
+
+def run_ours(args) -> int:
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks")
+    dist = None
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    pkg = importlib.import_module("qwen38-5080_b200")
+    if H_KV % world:
+        raise SystemExit("KV-head sharding needs a GPU count that divides 8")
+    h_kv, h_q = H_KV // world, H_Q // world
+
+    per_depth, runners = {}, {}
+    order = [args.workload] + [w for w in WORKLOADS if w != args.workload and not args.only]
+    headline = None
+    for key in order:
+        depth, cap, advance = WORKLOADS[key]
+        room = cap - depth - args.warmup - 4 if advance else 1 << 30   # the cache must not overflow
+        steps = max(1, min(args.steps, room))
+        runner = StepRunner(pkg, torch, device, depth, cap, advance, h_q, h_kv, seed=rank, dist=dist, world=world)
+        runner.capture()
+        if world > 1:   # communicator warm-up outside the timed region
+            runner.gather()
+            torch.cuda.synchronize()
+        with ClockSampler(torch, local) as sampler:
+            sec = timed_steps(torch, dist, world, runner, steps, args.warmup)
+            ksec = timed_kernel(torch, runner, steps, args.warmup)
+        status = runner.cache.workspace.read_status()
+        if status:
+            raise SystemExit(f"device status {status} after {key}")
+        total_bytes = kv_bytes_per_step(depth)                 # whole job (all ranks)
+        entry = {"us_per_step": sec * 1e6, "us_per_layer": sec * 1e6 / N_LAYERS,
+                 "hbm_gbs_whole_job": total_bytes / sec / 1e9, "hbm_gbs_per_gpu": total_bytes / world / sec / 1e9,
+                 "frac_of_8TBs_per_gpu": total_bytes / world / sec / 8e12,
+                 "attn_kernel_us": ksec * 1e6, "attn_kernel_gbs_per_gpu": total_bytes / world / ksec / 1e9,
+                 "steps": steps}
+        per_depth[str(depth)] = entry
+        if key == args.workload:
+            headline = (key, runner, sec, ksec, sampler.summary(), steps)
+            e2e_sec, h2d, d2h = timed_e2e(torch, dist, world, runner, steps, args.warmup)
+        else:
+            del runner
+            torch.cuda.empty_cache()
+
+    key, runner, sec, ksec, clocks, steps = headline
+    depth, cap, advance = WORKLOADS[key]
+    peak, peak_kind = load_peak()
+    bytes_per_launch = kv_bytes_per_step(depth, h_kv)           # one GPU's launch
+    achieved = bytes_per_launch / ksec / 1e9
+    line = {
+        "metric": METRIC, "value": sec * 1e6, "unit": "us/step", "n_gpus": world, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8-e4m3 KV, f16 tensor-core products, fp32 accumulate/softmax, bf16 in/out",
+        "data": "synthetic",
+        "config": {"workload": workload_name(key, depth, cap), "sharding": f"kv-head tensor parallel x{world}",
+                   "l2": f"inputs larger than L2 ({kv_bytes_per_step(depth, h_kv) / 1e6:.0f} MB KV per GPU per step)"
+                         if bytes_per_launch > 200e6 else "KV working set smaller than L2: L2-warm figure",
+                   "execution": "CUDA graph replay of append + attention (+ NCCL all-gather when sharded)"},
+        "hbm_gbs": kv_bytes_per_step(depth) / sec / 1e9,
+        "frac_of_8TBs": kv_bytes_per_step(depth) / world / sec / 8e12,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": load_traffic(key), "kernel": "attn_streamk_mma_kernel<128>", "peak_kind": peak_kind,
+                     "algorithmic_bytes_per_launch": bytes_per_launch, "launch_us": ksec * 1e6},
+        "e2e": {"value": e2e_sec * 1e6, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": runner.kernels_per_step() * steps,
+        "clocks": clocks,
+        "per_depth": per_depth,
+    }
+    if world == 1 and rank == 0 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(depth, cap)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
+    ap.add_argument("--only", action="store_true", help="measure only the headline workload")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,215 @@
+/*
+ * b200attn — C-ABI of the B200 (sm_100a) decode-attention library.
+ *
+ * One hot path of xzzqqq/qwen38-5080 is replaced: bs=1 / batched decode attention over an
+ * FP8-e4m3 static KV cache — (A) quantize-and-append of the step's K/V, (B) split-K GQA
+ * attention partials, (C) log-sum-exp combine.  Every entry point takes plain pointers and
+ * sizes; device pointers belong to the caller (torch tensors on the Python side), `stream`
+ * is a cudaStream_t passed as void*, and every call is asynchronous on that stream: no host
+ * synchronisation, no host read of device state, no allocation.  That makes a call sequence
+ * CUDA-graph capturable as the reference's graph runner requires
+ * (runner/model/graph_runner.py:127-198: fixed addresses, device-side position).
+ *
+ * Return value: 0 = launched; <0 = host-side argument error, nothing launched (the
+ * counterpart of the reference's "reject before submitting kernels" capacity guard,
+ * runner/model/decode_runner.py:323-332).  Soft errors seen on the device (position at
+ * capacity, sequence length beyond capacity, a bounded wait that ran out) are OR-ed into
+ * the caller's `status` word as B200ATTN_STATUS_* bits; the kernel then skips the
+ * offending access and returns normally.
+ */
+#ifndef B200ATTN_H
+#define B200ATTN_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200ATTN_VERSION 100
+
+/* host-side error codes */
+#define B200ATTN_OK                 0
+#define B200ATTN_ERR_NULL          -1   /* a required pointer is NULL */
+#define B200ATTN_ERR_SHAPE         -2   /* unsupported head shape / group size / head_dim */
+#define B200ATTN_ERR_ALIGN         -3   /* pointer or stride not 16-byte aligned */
+#define B200ATTN_ERR_WORKSPACE     -4   /* workspace too small for the requested split count */
+#define B200ATTN_ERR_SPLITS        -5   /* split count out of range */
+#define B200ATTN_ERR_CUDA          -6   /* a CUDA runtime / driver call failed (see b200attn_last_cuda_error) */
+#define B200ATTN_ERR_CAPACITY      -7   /* host-known length exceeds capacity */
+#define B200ATTN_ERR_VARIANT       -8   /* unknown kernel variant */
+#define B200ATTN_ERR_TOO_LARGE     -9   /* size beyond a fixed limit of the entry point */
+
+/* device status bits (OR-ed into *status) */
+#define B200ATTN_STATUS_POS_AT_CAPACITY  1  /* append skipped: seq_pos[b] >= capacity */
+#define B200ATTN_STATUS_LEN_OVER_CAP     2  /* seq_len[b] > capacity: clamped to capacity */
+#define B200ATTN_STATUS_WAIT_TIMEOUT     4  /* a bounded wait on a copy barrier ran out */
+#define B200ATTN_STATUS_LEN_NEGATIVE     8  /* seq_len[b] < 0: treated as 0 */
+
+/* kernel variants for b200attn_decode */
+#define B200ATTN_VARIANT_AUTO     0   /* the library's default (the fastest validated variant) */
+#define B200ATTN_VARIANT_SIMT     1   /* CUDA-core split-K partial kernel + separate combine kernel */
+#define B200ATTN_VARIANT_MMA      2   /* TMA/mbarrier staged, tensor-core (mma.sync f16) stream-K kernel with fused combine */
+
+/* scale granularity of the FP8 cache */
+#define B200ATTN_SCALE_PER_HEAD   0   /* fp32 scale per (layer, kv_head): [n_layers][h_kv] */
+#define B200ATTN_SCALE_PER_TOKEN  1   /* fp32 scale per (layer, seq, token, kv_head): [n_layers][batch][capacity][h_kv]
+                                         — the layout the reference froze,
+                                         docs/journal/2026-10-23-phase2-r3-coordinator.md:46-48 */
+
+/*
+ * Geometry of one call.  The cache is the FP8 counterpart of the reference's static cache
+ * (runner/model/static_cache.py:135-158: keys/values [B, H_kv, capacity, D], fixed address,
+ * zero-initialised), stacked over layers:
+ *     k_cache / v_cache : u8 [n_layers][batch][h_kv][capacity][head_dim]   (e4m3fn bytes)
+ * `k_layer_stride` / `v_layer_stride` are the byte distances between consecutive layers
+ * (0 means dense = batch*h_kv*capacity*head_dim), so that per-layer tensors allocated
+ * separately can be driven with n_layers = 1 and offset base pointers.
+ * Tensor-parallel sharding by KV head is expressed by passing the local h_kv / h_q.
+ */
+typedef struct B200AttnShape {
+  int n_layers;      /* 64 (BASELINE), 16 (reference model), or 1 for the per-layer drop-in */
+  int batch;         /* sequences, >= 1 */
+  int h_q;           /* query heads (40 | 24); must be a multiple of h_kv, group size <= 8 */
+  int h_kv;          /* KV heads (8 | 4) */
+  int head_dim;      /* 128 or 256 */
+  int capacity;      /* token slots per sequence */
+  int scale_mode;    /* B200ATTN_SCALE_* */
+  int reserved;      /* must be 0 */
+  long long k_layer_stride;
+  long long v_layer_stride;
+} B200AttnShape;
+
+/* Library version (B200ATTN_VERSION of the build). */
+int b200attn_version(void);
+
+/* Text for a host-side error code. */
+const char* b200attn_error_string(int code);
+
+/* Last CUDA error code seen by a failing call on this thread (0 if none). */
+int b200attn_last_cuda_error(void);
+
+/*
+ * Split count for the SIMT variant / CTA count for the stream-K variant at a given maximum
+ * sequence length, chosen to fill `num_sms` SMs (148 on B200).  Pure host function.
+ * Replaces the split heuristic of the reference's fused kernel ("one program = (kv_head,
+ * split)", docs/journal/2026-10-23-phase2-r3-coordinator.md:140-141).
+ */
+int b200attn_pick_splits(const B200AttnShape* shape, int max_seq_len, int num_sms, int variant);
+
+/*
+ * Bytes of workspace b200attn_decode needs for `num_splits` (as returned by
+ * b200attn_pick_splits, or larger).  The workspace holds split-K partials
+ * (m, l, acc[G][D] in fp32) and the arrival tickets of the fused combine.
+ */
+int b200attn_workspace_bytes(const B200AttnShape* shape, int num_splits, int variant, size_t* bytes);
+
+/*
+ * Zero the workspace (tickets must start at zero; the kernels leave them at zero again).
+ * Call once after allocation and after any call that reported a status error.
+ */
+int b200attn_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * A. Quantize-and-append one token per sequence for n_layers layers at once.
+ * Replaces StaticCapFullAttentionLayer.update -> StaticLayer.update -> index_copy_
+ * (runner/model/static_cache.py:69-77) with the FP8 format frozen in
+ * docs/journal/2026-10-23-phase2-r3-coordinator.md:43-49:
+ *     byte = e4m3fn_rne( clamp( float(x) / s, -448, 448 ) )
+ * written at token slot seq_pos[b].  In B200ATTN_SCALE_PER_HEAD mode `k_scale`/`v_scale`
+ * are inputs; in B200ATTN_SCALE_PER_TOKEN mode they are outputs (s = amax|x|/448 over the
+ * head's head_dim values, written at [layer][b][seq_pos[b]][head]).
+ *   k_new, v_new : bf16 [n_layers][batch][h_kv][head_dim]
+ *   seq_pos      : int32 [batch], tokens already cached (device memory)
+ *   advance_pos  : 1 -> seq_pos[b] += 1 after all layers were written (the reference's
+ *                  cumulative_length.add_, static_cache.py:14-15)
+ */
+int b200attn_kv_quant_append(const B200AttnShape* shape,
+                             const void* k_new_bf16, const void* v_new_bf16,
+                             void* k_cache_u8, void* v_cache_u8,
+                             float* k_scale, float* v_scale,
+                             int* seq_pos, int advance_pos,
+                             int* status, void* stream);
+
+/*
+ * Prefill-side bulk quantize-append: `n_tokens` consecutive tokens per sequence, written at
+ * slots [seq_pos[b], seq_pos[b]+n_tokens).  Counterpart of the reference's q_len>1 update
+ * (runner/model/static_cache.py:76-77; prefill chunk 128, runner/model/decode_runner.py:229-235).
+ *   k_new, v_new : bf16 [n_layers][batch][h_kv][n_tokens][head_dim]
+ */
+int b200attn_kv_quant_append_bulk(const B200AttnShape* shape, int n_tokens,
+                                  const void* k_new_bf16, const void* v_new_bf16,
+                                  void* k_cache_u8, void* v_cache_u8,
+                                  float* k_scale, float* v_scale,
+                                  int* seq_pos, int advance_pos,
+                                  int* status, void* stream);
+
+/*
+ * B+C. Decode attention for one query token per sequence: attends token slots
+ * [0, seq_len[b] + seq_len_offset) of sequence b.  Replaces repeat_kv + eager attention
+ * (bench/micro/attn_length_effect.py:41-66, the reference's replica of transformers'
+ * eager_attention_forward) together with the capacity-length mask of
+ * StaticCapFullAttentionLayer.get_mask_sizes (runner/model/static_cache.py:79-82): slots
+ * at or beyond the valid length never influence the result, whatever bytes they hold.
+ *   q            : bf16 [n_layers][batch][h_q][head_dim]
+ *   k_scale,v_scale : fp32, layout by shape->scale_mode
+ *   seq_len      : int32 [batch] on the device
+ *   seq_len_offset : added to every seq_len[b] (pass seq_pos with offset 1 to attend the
+ *                  token appended in the same step without bumping seq_pos first)
+ *   softmax_scale: head_dim^-0.5
+ *   num_splits   : from b200attn_pick_splits (0 = pick for capacity and 148 SMs)
+ *   out          : bf16 [n_layers][batch][h_q][head_dim]  (the reference's
+ *                  out.transpose(1,2).contiguous() layout, attn_length_effect.py:66)
+ */
+int b200attn_decode(const B200AttnShape* shape,
+                    const void* q_bf16,
+                    const void* k_cache_u8, const void* v_cache_u8,
+                    const float* k_scale, const float* v_scale,
+                    const int* seq_len, int seq_len_offset,
+                    float softmax_scale,
+                    int variant, int num_splits,
+                    void* workspace, size_t workspace_bytes,
+                    void* out_bf16,
+                    int* status, void* stream);
+
+/*
+ * Fused convenience for one decode step: A (append at seq_pos) then B+C attending
+ * seq_pos[b]+1 tokens, then seq_pos[b] += 1 if advance_pos.  Same stream, no host sync.
+ */
+int b200attn_append_decode(const B200AttnShape* shape,
+                           const void* q_bf16,
+                           const void* k_new_bf16, const void* v_new_bf16,
+                           void* k_cache_u8, void* v_cache_u8,
+                           float* k_scale, float* v_scale,
+                           int* seq_pos, int advance_pos,
+                           float softmax_scale,
+                           int variant, int num_splits,
+                           void* workspace, size_t workspace_bytes,
+                           void* out_bf16,
+                           int* status, void* stream);
+
+/*
+ * On-demand dequantised view of a cache prefix for reference / prefill use
+ * (the reference keeps dequant_kv for exactly these, never on the decode path:
+ * docs/journal/2026-10-23-phase2-r3-coordinator.md:162-163):
+ *     out_bf16[l][b][h][t][:] = bf16( float(byte) * s )   for t < n_tokens
+ *   out : bf16 [n_layers][batch][h_kv][n_tokens][head_dim]
+ */
+int b200attn_dequant_prefix(const B200AttnShape* shape, int n_tokens,
+                            const void* cache_u8, long long layer_stride,
+                            const float* scale,
+                            void* out_bf16, void* stream);
+
+/*
+ * Per-(layer, kv_head) scale calibration over a bf16 prefix on the device:
+ *     scale[l][h] = max_{b,t<n_tokens,d} |x| / 448
+ *   x : bf16 [n_layers][batch][h_kv][n_tokens][head_dim]
+ * (BASELINE config: "quantised to FP8-e4m3 with a per-(layer, kv-head) fp32 absmax/448 scale").
+ */
+int b200attn_calibrate_scales(const B200AttnShape* shape, int n_tokens,
+                              const void* x_bf16, float* scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H */

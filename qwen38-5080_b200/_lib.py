@@ -1,0 +1,92 @@
+"""ctypes binding of libb200attn.so (the C-ABI declared in include/b200attn.h).
+
+The library is the product: there is no Python or CPU fallback.  If the shared object is
+missing and cannot be built, importing the ops fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "libb200attn.so"
+
+c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_longlong
+
+# host-side error codes / status bits / variants (include/b200attn.h)
+OK = 0
+ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_SPLITS, ERR_CUDA, ERR_CAPACITY, ERR_VARIANT, ERR_TOO_LARGE = range(-1, -10, -1)
+STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEGATIVE = 1, 2, 4, 8
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA = 0, 1, 2
+VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA}
+SCALE_PER_HEAD, SCALE_PER_TOKEN = 0, 1
+
+
+class B200AttnShape(ctypes.Structure):
+    _fields_ = [
+        ("n_layers", c_int), ("batch", c_int), ("h_q", c_int), ("h_kv", c_int), ("head_dim", c_int),
+        ("capacity", c_int), ("scale_mode", c_int), ("reserved", c_int),
+        ("k_layer_stride", c_ll), ("v_layer_stride", c_ll),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/b200attn.h declares
+PROTOTYPES = {
+    "b200attn_version": (c_int, []),
+    "b200attn_error_string": (ctypes.c_char_p, [c_int]),
+    "b200attn_last_cuda_error": (c_int, []),
+    "b200attn_pick_splits": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_int, c_int]),
+    "b200attn_workspace_bytes": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_int, ctypes.POINTER(c_size_t)]),
+    "b200attn_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "b200attn_kv_quant_append": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "b200attn_kv_quant_append_bulk": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "b200attn_decode": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p,
+                                c_void_p]),
+    "b200attn_append_decode": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
+                                       c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
+    "b200attn_dequant_prefix": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_void_p, c_ll, c_void_p, c_void_p,
+                                        c_void_p]),
+    "b200attn_calibrate_scales": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_void_p, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+class B200AttnError(ValueError):
+    """A host-side argument error reported by the library (nothing was launched)."""
+
+    def __init__(self, code: int, where: str):
+        self.code = code
+        msg = lib().b200attn_error_string(code).decode()
+        if code == ERR_CUDA:
+            msg += f" (cudaError {lib().b200attn_last_cuda_error()})"
+        super().__init__(f"{where}: {msg} [{code}]")
+
+
+def lib() -> ctypes.CDLL:
+    """Load (building first if the shared object is absent and nvcc exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists() or os.environ.get("B200ATTN_REBUILD") == "1":
+        from . import build as _build  # raises if nvcc is missing: no fallback
+        _build.build()
+    if not LIB_PATH.exists():
+        raise RuntimeError(f"{LIB_PATH} is missing: build it with `python {PKG_DIR / 'build.py'}`")
+    handle = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(handle, name)  # AttributeError if the build lost a symbol
+        fn.restype, fn.argtypes = res, args
+    _lib = handle
+    return _lib
+
+
+def check(code: int, where: str) -> int:
+    if code < 0:
+        raise B200AttnError(code, where)
+    return code

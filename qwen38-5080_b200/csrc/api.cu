@@ -1,0 +1,210 @@
+// C-ABI layer of libb200attn: argument validation on the host, then kernel launches on the
+// caller's stream.  Nothing here allocates, synchronises or reads device memory.
+#include "common.cuh"
+
+using namespace b200attn;
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return B200ATTN_ERR_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Validate the shape and resolve strides.  Returns 0 or a B200ATTN_ERR_* code.
+int resolve(const B200AttnShape* s, Geometry* g) {
+  if (!s) return B200ATTN_ERR_NULL;
+  if (s->n_layers < 1 || s->batch < 1 || s->h_q < 1 || s->h_kv < 1 || s->capacity < 1) return B200ATTN_ERR_SHAPE;
+  if (s->head_dim != 128 && s->head_dim != 256) return B200ATTN_ERR_SHAPE;
+  if (s->h_q % s->h_kv) return B200ATTN_ERR_SHAPE;
+  const int group = s->h_q / s->h_kv;
+  if (group < 1 || group > kMaxGroup) return B200ATTN_ERR_SHAPE;
+  if (s->scale_mode != B200ATTN_SCALE_PER_HEAD && s->scale_mode != B200ATTN_SCALE_PER_TOKEN) return B200ATTN_ERR_SHAPE;
+  if (s->reserved != 0) return B200ATTN_ERR_SHAPE;
+  if ((long long)s->n_layers * s->batch > 65535) return B200ATTN_ERR_SHAPE;
+  const long long dense = (long long)s->batch * s->h_kv * s->capacity * s->head_dim;
+  g->n_layers = s->n_layers; g->batch = s->batch; g->h_q = s->h_q; g->h_kv = s->h_kv;
+  g->head_dim = s->head_dim; g->capacity = s->capacity; g->scale_mode = s->scale_mode; g->group = group;
+  g->k_layer_stride = s->k_layer_stride ? s->k_layer_stride : dense;
+  g->v_layer_stride = s->v_layer_stride ? s->v_layer_stride : dense;
+  if (s->n_layers > 1 && (g->k_layer_stride < dense || g->v_layer_stride < dense)) return B200ATTN_ERR_SHAPE;
+  if ((g->k_layer_stride & 15) || (g->v_layer_stride & 15)) return B200ATTN_ERR_ALIGN;
+  return B200ATTN_OK;
+}
+
+// AUTO = the tensor-core stream-K kernel wherever it applies (per-head scales); the per-token
+// scale layout is served by the SIMT kernel.  An explicit request that cannot be met is an error.
+int resolve_variant(int variant, const Geometry& g) {
+  const bool mma_ok = g.scale_mode == B200ATTN_SCALE_PER_HEAD && g.batch <= 2048;
+  if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
+  if (variant == B200ATTN_VARIANT_SIMT) return variant;
+  if (variant == B200ATTN_VARIANT_MMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
+  return B200ATTN_ERR_VARIANT;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200attn_version(void) { return B200ATTN_VERSION; }
+
+const char* b200attn_error_string(int code) {
+  switch (code) {
+    case B200ATTN_OK: return "ok";
+    case B200ATTN_ERR_NULL: return "a required pointer is NULL";
+    case B200ATTN_ERR_SHAPE: return "unsupported shape (head_dim 128|256, h_q multiple of h_kv, group <= 8, sizes >= 1)";
+    case B200ATTN_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
+    case B200ATTN_ERR_WORKSPACE: return "workspace too small";
+    case B200ATTN_ERR_SPLITS: return "split count out of range";
+    case B200ATTN_ERR_CUDA: return "CUDA call failed";
+    case B200ATTN_ERR_CAPACITY: return "length exceeds capacity";
+    case B200ATTN_ERR_VARIANT: return "unknown kernel variant";
+    case B200ATTN_ERR_TOO_LARGE: return "size beyond the fixed limit of this entry point";
+  }
+  return "unknown error code";
+}
+
+int b200attn_last_cuda_error(void) { return g_last_cuda_error; }
+
+int b200attn_pick_splits(const B200AttnShape* shape, int max_seq_len, int num_sms, int variant) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (max_seq_len < 0) return B200ATTN_ERR_CAPACITY;
+  if (num_sms < 1) num_sms = 148;
+  const int v = resolve_variant(variant, g);
+  if (v < 0) return v;
+  return v == B200ATTN_VARIANT_SIMT ? simt_pick_splits(g, max_seq_len, num_sms)
+                                    : mma_pick_ctas(g, max_seq_len, num_sms);
+}
+
+int b200attn_workspace_bytes(const B200AttnShape* shape, int num_splits, int variant, size_t* bytes) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (!bytes) return B200ATTN_ERR_NULL;
+  if (num_splits < 1 || num_splits > 65535) return B200ATTN_ERR_SPLITS;
+  const int v = resolve_variant(variant, g);
+  if (v < 0) return v;
+  *bytes = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(g, num_splits) : mma_workspace_bytes(g, num_splits);
+  return B200ATTN_OK;
+}
+
+int b200attn_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace) return B200ATTN_ERR_NULL;
+  cudaError_t e = cudaMemsetAsync(workspace, 0, workspace_bytes, (cudaStream_t)stream);
+  return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
+}
+
+int b200attn_kv_quant_append_bulk(const B200AttnShape* shape, int n_tokens,
+                                  const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                                  float* k_scale, float* v_scale, int* seq_pos, int advance_pos,
+                                  int* status, void* stream) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale || !seq_pos || !status) return B200ATTN_ERR_NULL;
+  if (n_tokens < 1 || n_tokens > g.capacity) return B200ATTN_ERR_CAPACITY;
+  if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return B200ATTN_ERR_ALIGN;
+  cudaError_t e = launch_append(g, n_tokens, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos,
+                                advance_pos, status, (cudaStream_t)stream);
+  return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
+}
+
+int b200attn_kv_quant_append(const B200AttnShape* shape, const void* k_new, const void* v_new,
+                             void* k_cache, void* v_cache, float* k_scale, float* v_scale,
+                             int* seq_pos, int advance_pos, int* status, void* stream) {
+  return b200attn_kv_quant_append_bulk(shape, 1, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos,
+                                       advance_pos, status, stream);
+}
+
+int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cache, const void* v_cache,
+                    const float* k_scale, const float* v_scale, const int* seq_len, int seq_len_offset,
+                    float softmax_scale, int variant, int num_splits, void* workspace,
+                    size_t workspace_bytes, void* out, int* status, void* stream) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !seq_len || !out || !status) return B200ATTN_ERR_NULL;
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out)) return B200ATTN_ERR_ALIGN;
+  const int v = resolve_variant(variant, g);
+  if (v < 0) return v;
+  if (num_splits == 0)
+    num_splits = v == B200ATTN_VARIANT_SIMT ? simt_pick_splits(g, g.capacity, 148) : mma_pick_ctas(g, g.capacity, 148);
+  if (num_splits < 1 || num_splits > 65535) return B200ATTN_ERR_SPLITS;
+  const size_t need = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(g, num_splits) : mma_workspace_bytes(g, num_splits);
+  const bool needs_ws = !(v == B200ATTN_VARIANT_SIMT && num_splits == 1);
+  if (needs_ws) {
+    if (!workspace) return B200ATTN_ERR_NULL;
+    if (!aligned16(workspace)) return B200ATTN_ERR_ALIGN;
+    if (workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
+  }
+  DecodeArgs a{q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
+               num_splits, workspace, workspace_bytes, out, status};
+  cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
+                                             : launch_decode_mma(g, a, (cudaStream_t)stream);
+  return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
+}
+
+int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void* k_new, const void* v_new,
+                           void* k_cache, void* v_cache, float* k_scale, float* v_scale, int* seq_pos,
+                           int advance_pos, float softmax_scale, int variant, int num_splits,
+                           void* workspace, size_t workspace_bytes, void* out, int* status, void* stream) {
+  // Validate everything before the first launch so that an argument error launches nothing.
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (!q || !out || !seq_pos || !status) return B200ATTN_ERR_NULL;
+  const int v = resolve_variant(variant, g);
+  if (v < 0) return v;
+  if (num_splits == 0)
+    num_splits = v == B200ATTN_VARIANT_SIMT ? simt_pick_splits(g, g.capacity, 148) : mma_pick_ctas(g, g.capacity, 148);
+  if (num_splits < 1 || num_splits > 65535) return B200ATTN_ERR_SPLITS;
+  const size_t need = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(g, num_splits) : mma_workspace_bytes(g, num_splits);
+  if (!(v == B200ATTN_VARIANT_SIMT && num_splits == 1)) {
+    if (!workspace) return B200ATTN_ERR_NULL;
+    if (workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
+  }
+  if (!aligned16(q) || !aligned16(out) || !aligned16(workspace)) return B200ATTN_ERR_ALIGN;
+  rc = b200attn_kv_quant_append_bulk(shape, 1, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 0,
+                                     status, stream);
+  if (rc) return rc;
+  rc = b200attn_decode(shape, q, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
+                       workspace, workspace_bytes, out, status, stream);
+  if (rc) return rc;
+  if (advance_pos) {
+    cudaError_t e = launch_advance_pos(g, 1, seq_pos, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  return B200ATTN_OK;
+}
+
+int b200attn_dequant_prefix(const B200AttnShape* shape, int n_tokens, const void* cache, long long layer_stride,
+                            const float* scale, void* out, void* stream) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (!cache || !scale || !out) return B200ATTN_ERR_NULL;
+  if (n_tokens < 0 || n_tokens > g.capacity) return B200ATTN_ERR_CAPACITY;
+  if (!aligned16(cache) || !aligned16(out) || (layer_stride & 15)) return B200ATTN_ERR_ALIGN;
+  if (layer_stride == 0) layer_stride = (long long)g.batch * g.h_kv * g.capacity * g.head_dim;
+  cudaError_t e = launch_dequant_prefix(g, n_tokens, cache, layer_stride, scale, out, (cudaStream_t)stream);
+  return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
+}
+
+int b200attn_calibrate_scales(const B200AttnShape* shape, int n_tokens, const void* x, float* scale, void* stream) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (!x || !scale) return B200ATTN_ERR_NULL;
+  if (n_tokens < 1) return B200ATTN_ERR_CAPACITY;
+  if (!aligned16(x)) return B200ATTN_ERR_ALIGN;
+  cudaError_t e = launch_calibrate(g, n_tokens, x, scale, (cudaStream_t)stream);
+  return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
+}
+
+}  // extern "C"

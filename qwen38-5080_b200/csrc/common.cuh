@@ -1,0 +1,108 @@
+// Shared device helpers and the internal launcher interface of libb200attn.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200attn.h"
+
+namespace b200attn {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kE4m3Max = 448.0f;
+constexpr int kMaxGroup = 8;  // query heads per KV head the kernels support (BASELINE 5, reference 6)
+
+// Resolved geometry handed to the launchers (strides in bytes, always filled in).
+struct Geometry {
+  int n_layers, batch, h_q, h_kv, head_dim, capacity, scale_mode, group;
+  long long k_layer_stride, v_layer_stride;
+};
+
+// ---- fp8 / bf16 conversion ---------------------------------------------------------------
+
+// Two e4m3 bytes (low 16 bits of `pair`) -> two floats, exact.
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t pair) {
+  uint32_t h2;
+  asm("{ .reg .b16 lo; cvt.u16.u32 lo, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(h2) : "r"(pair));
+  return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+
+// Two e4m3 bytes held in a 16-bit register -> packed f16x2 (exact).
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t pair) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(pair));
+  return h2;
+}
+
+// 16 e4m3 bytes -> 16 floats.
+__device__ __forceinline__ void e4m3x16_to_float(const uint4& raw, float* out) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 a = e4m3x2_to_float2(w[i] & 0xFFFFu);
+    float2 b = e4m3x2_to_float2(w[i] >> 16);
+    out[4 * i + 0] = a.x; out[4 * i + 1] = a.y; out[4 * i + 2] = b.x; out[4 * i + 3] = b.y;
+  }
+}
+
+// clamp(x / s, -448, 448) -> e4m3fn byte, round to nearest even.  IEEE division.  A NaN input
+// keeps its sign and becomes 0x7F / 0xFF, as a float32 -> float8_e4m3fn cast of a clamped NaN
+// does on the host (GPU arithmetic would canonicalise the sign away, so it is taken from x);
+// a NaN produced by the division itself (0/0, inf/inf) becomes 0x7F.
+__device__ __forceinline__ uint8_t quantize_e4m3(float x, float s) {
+  if (x != x) return (uint8_t)(0x7F | ((__float_as_uint(x) >> 31) << 7));
+  float y = __fdiv_rn(x, s);
+  if (y != y) return (uint8_t)0x7F;
+  y = fminf(fmaxf(y, -kE4m3Max), kE4m3Max);
+  return (uint8_t)__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+
+// ---- launchers (defined in the .cu files; called by the C-ABI layer in api.cu) ------------
+
+cudaError_t launch_append(const Geometry& g, int n_tokens, const void* k_new, const void* v_new,
+                          void* k_cache, void* v_cache, float* k_scale, float* v_scale,
+                          int* seq_pos, int advance_pos, int* status, cudaStream_t stream);
+
+cudaError_t launch_advance_pos(const Geometry& g, int n_tokens, int* seq_pos, cudaStream_t stream);
+
+cudaError_t launch_dequant_prefix(const Geometry& g, int n_tokens, const void* cache,
+                                  long long layer_stride, const float* scale, void* out,
+                                  cudaStream_t stream);
+
+cudaError_t launch_calibrate(const Geometry& g, int n_tokens, const void* x, float* scale,
+                             cudaStream_t stream);
+
+struct DecodeArgs {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const float* k_scale;
+  const float* v_scale;
+  const int* seq_len;
+  int seq_len_offset;
+  float softmax_scale;
+  int num_splits;
+  void* workspace;
+  size_t workspace_bytes;
+  void* out;
+  int* status;
+};
+
+// SIMT variant: split-K partial kernel + combine kernel.
+size_t simt_workspace_bytes(const Geometry& g, int num_splits);
+int simt_pick_splits(const Geometry& g, int max_seq_len, int num_sms);
+cudaError_t launch_decode_simt(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
+
+// MMA variant: TMA-staged, tensor-core stream-K kernel with fused combine.
+size_t mma_workspace_bytes(const Geometry& g, int num_ctas);
+int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
+cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
+
+}  // namespace b200attn

@@ -1,0 +1,664 @@
+// Tensor-core stream-K variant of the FP8-KV decode attention (the default path).
+//
+// One persistent launch covers every (layer, sequence, kv head) of a decode step:
+//   * the KV cache is cut into tiles of TILE_T tokens; all tiles of the step form one linear
+//     sequence which is divided evenly over the resident CTAs (stream-K), so ragged batches and
+//     any depth fill all 148 SMs and each CTA touches at most two partially owned
+//     (layer, sequence, kv head) "pairs";
+//   * a producer warp streams K and V tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle)
+//     into a ring of shared-memory stages guarded by full/empty mbarriers; every KV byte is read
+//     from HBM exactly once and serves all G query heads of the group;
+//   * four consumer warps each own 16 tokens of a tile.  FP8 bytes go from shared memory to
+//     registers, are widened to f16 in registers (cvt.rn.f16x2.e4m3x2, exact) and feed
+//     mma.sync.m16n8k16 with the query heads on the N side (G <= 8): S^T = K q^T, then
+//     O^T += V^T P^T after a warp-level movmatrix transpose of the probabilities.  Accumulation
+//     and the log2-domain online softmax are fp32.  The per-head scales never enter the loop:
+//     k_scale*softmax_scale*log2e multiplies the scores, v_scale the final normalisation;
+//   * a pair owned by one CTA is normalised and written directly; otherwise each owner writes an
+//     (m, l, acc) partial and takes an arrival ticket; the last arriver merges the partials in
+//     CTA order (deterministic, so replays are bitwise identical) and resets the ticket.  Nothing
+//     ever spins on another CTA.  The only waits are on the CTA's own copy barriers, and those
+//     are bounded: on expiry the CTA flags B200ATTN_STATUS_WAIT_TIMEOUT, stops waiting, drains
+//     its copies and returns.
+//
+// It replaces repeat_kv + eager attention + the capacity mask of the reference
+// (bench/micro/attn_length_effect.py:41-66, runner/model/static_cache.py:79-82) and follows the
+// split/combine structure of its fused kernel
+// (docs/journal/2026-10-23-phase2-r3-coordinator.md:137-141).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace b200attn {
+
+namespace {
+
+constexpr int kTileT = 64;                 // tokens per tile
+constexpr int kConsumerWarps = 4;          // 16 tokens each
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;  // + producer warp
+constexpr int kMaxBatchMma = 2048;
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait
+
+struct MmaParams {
+  Geometry g;
+  const uint16_t* q;
+  const float* k_scale;
+  const float* v_scale;
+  const int* seq_len;
+  int seq_len_offset;
+  float score_scale;     // softmax_scale * log2(e)
+  float* ws_acc;         // [num_ctas][2][G][D]
+  float* ws_ml;          // [num_ctas][2][2][8]
+  int* tickets;          // [pairs]
+  uint16_t* out;
+  int* status;
+  int stages;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (and raises the CTA's timeout flag) when the budget runs out or
+// when another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* timed_out, int* status) {
+  if (*timed_out) return false;
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*timed_out) return false;
+    if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      *timed_out = 1;
+      atomicOr(status, B200ATTN_STATUS_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t cvt_lo(uint32_t w) { return e4m3x2_to_f16x2((uint16_t)(w & 0xFFFFu)); }
+__device__ __forceinline__ uint32_t cvt_hi(uint32_t w) { return e4m3x2_to_f16x2((uint16_t)(w >> 16)); }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------------------------
+// the stream-K walk: linear tile index -> (layer, sequence, kv head, tile)
+// ---------------------------------------------------------------------------------------------
+struct Cursor {
+  int layer, b, h, tile;   // position of the current tile
+  int tiles_b;             // tiles of sequence b
+  int len_b;               // valid tokens of sequence b
+};
+
+// cum[b] = tiles of sequences < b; len[] clamped lengths.  Both in shared memory.
+__device__ __forceinline__ Cursor locate(long long idx, const int* cum, const int* len, int batch, int h_kv) {
+  const long long per_layer = (long long)cum[batch] * h_kv;
+  Cursor c;
+  c.layer = (int)(idx / per_layer);
+  const long long r = idx - (long long)c.layer * per_layer;
+  int lo = 0, hi = batch - 1;   // largest b with cum[b]*h_kv <= r (and tiles_b > 0 follows from r < cum[b+1]*h_kv)
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if ((long long)cum[mid] * h_kv <= r) lo = mid; else hi = mid - 1;
+  }
+  // sequences with zero tiles share cum[] with their successor: step forward to the one that owns r
+  while (cum[lo + 1] == cum[lo]) ++lo;
+  c.b = lo;
+  c.tiles_b = cum[lo + 1] - cum[lo];
+  c.len_b = len[lo];
+  const long long rr = r - (long long)cum[lo] * h_kv;
+  c.h = (int)(rr / c.tiles_b);
+  c.tile = (int)(rr - (long long)c.h * c.tiles_b);
+  return c;
+}
+
+// Move to the first tile of the next pair.
+__device__ __forceinline__ void next_pair(Cursor& c, const int* cum, const int* len, int batch, int h_kv) {
+  c.tile = 0;
+  if (++c.h < h_kv) return;
+  c.h = 0;
+  for (;;) {
+    if (++c.b == batch) { c.b = 0; ++c.layer; }
+    if (cum[c.b + 1] != cum[c.b]) break;   // at least one sequence is non-empty when total > 0
+  }
+  c.tiles_b = cum[c.b + 1] - cum[c.b];
+  c.len_b = len[c.b];
+}
+
+// CTA that owns linear tile x when `total` tiles are divided over n CTAs as [c*total/n, (c+1)*total/n).
+__device__ __forceinline__ int owner_of(long long x, long long total, int n) {
+  return (int)(((x + 1) * n - 1) / total);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                        const MmaParams p) {
+  constexpr int DH = D / 128;              // 128-byte column blocks per row
+  constexpr int KSTEPS = D / 16;           // mma k-steps for QK^T == mma tiles for PV
+  constexpr int TILE_BYTES = kTileT * D;   // one K (or V) tile
+  const Geometry& g = p.g;
+  const int G = g.group;
+  const int stages = p.stages;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates ("groupID", "threadID_in_group")
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + (size_t)stages * TILE_BYTES;
+  float* sO = reinterpret_cast<float*>(sV + (size_t)stages * TILE_BYTES);   // [4][G][D]
+  float* sM = sO + kConsumerWarps * G * D;                                   // [4][8]
+  float* sL = sM + kConsumerWarps * 8;                                       // [4][8]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sL + kConsumerWarps * 8);     // full[stages], empty[stages]
+  int* sFlags = reinterpret_cast<int*>(bars + 2 * stages);                   // [0] timed_out [1] is_last [2] any_empty
+  int* sLen = sFlags + 4;                                                    // [batch]
+  int* sCum = sLen + g.batch;                                                // [batch+1]
+  volatile int* timed_out = sFlags;
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * stages;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full0 + 8u * s, 1);
+      mbar_init(empty0 + 8u * s, kConsumerWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    sFlags[0] = 0; sFlags[1] = 0; sFlags[3] = 0;
+    int acc = 0, any_empty = 0, st = 0;
+    for (int b = 0; b < g.batch; ++b) {
+      int len = p.seq_len[b] + p.seq_len_offset;
+      if (len < 0) { len = 0; st |= B200ATTN_STATUS_LEN_NEGATIVE; }
+      if (len > g.capacity) { len = g.capacity; st |= B200ATTN_STATUS_LEN_OVER_CAP; }
+      sLen[b] = len;
+      sCum[b] = acc;
+      acc += (len + kTileT - 1) / kTileT;
+      any_empty |= len == 0;
+    }
+    sCum[g.batch] = acc;
+    sFlags[2] = any_empty;
+    if (st && blockIdx.x == 0) atomicOr(p.status, st);
+  }
+  if (warp == kConsumerWarps && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
+  }
+  __syncthreads();
+
+  // sequences of length 0 have no tiles: their outputs are zero, written by whoever gets there
+  if (sFlags[2]) {
+    const long long rows = (long long)g.n_layers * g.batch;
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+      if (sLen[r % g.batch] == 0)
+        for (int i = tid; i < g.h_q * D; i += kThreads) p.out[r * g.h_q * D + i] = 0;
+    }
+  }
+
+  const long long per_layer = (long long)sCum[g.batch] * g.h_kv;
+  const long long total = per_layer * g.n_layers;
+  const int n_eff = (int)(total < (long long)gridDim.x ? total : (long long)gridDim.x);
+  const bool has_work = (long long)blockIdx.x < (long long)n_eff;
+  long long r0 = 0, r1 = 0;
+  if (has_work) {
+    r0 = (long long)blockIdx.x * total / n_eff;
+    r1 = ((long long)blockIdx.x + 1) * total / n_eff;
+  }
+
+  if (warp == kConsumerWarps) {
+    // ===================== producer warp: one elected lane issues the copies =====================
+    if (lane == 0 && has_work) {
+      Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+      int it = 0;
+      for (long long idx = r0; idx < r1; ++idx, ++it) {
+        const int s = it % stages;
+        if (it >= stages && !mbar_wait(empty0 + 8u * s, ((it / stages) - 1) & 1, timed_out, p.status)) break;
+        const uint32_t fb = full0 + 8u * s;
+        mbar_arrive_expect_tx(fb, 2u * TILE_BYTES);
+        const int row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTileT;
+#pragma unroll
+        for (int hf = 0; hf < DH; ++hf) {
+          tma_load_3d(smem_u32(sK + (size_t)s * TILE_BYTES + hf * kTileT * 128), &kmap, hf * 128, row, c.layer, fb);
+          tma_load_3d(smem_u32(sV + (size_t)s * TILE_BYTES + hf * kTileT * 128), &vmap, hf * 128, row, c.layer, fb);
+        }
+        if (++c.tile == c.tiles_b && idx + 1 < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+      }
+      sFlags[3] = it;   // copies issued, for the drain below
+    }
+  } else if (has_work) {
+    // ================================ consumer warps ================================
+    Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+    long long cur = r0;
+    int it = 0;
+    const uint32_t sK_addr = smem_u32(sK), sV_addr = smem_u32(sV);
+    const int row_lo = warp * 16 + gq;   // K row of this thread inside a tile (and row_lo + 8)
+
+    while (cur < r1) {
+      const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
+      const long long seg_end = pair_end < r1 ? pair_end : r1;
+      const int ntiles = (int)(seg_end - cur);
+      const long long lb = (long long)c.layer * g.batch + c.b;
+      const long long pair = lb * g.h_kv + c.h;
+
+      // ---- query fragments (B operand of S^T = K q^T): head gq, dims hf*128 + 32*tq + 4*ks' ----
+      // Each head is rescaled by a power of two so that its largest |q| lies in [1, 2): exact,
+      // keeps every product inside f16 range whatever the magnitude of q.
+      uint32_t qf[KSTEPS][2];
+      float sc0, sc1;   // score multipliers of heads 2*tq and 2*tq+1 (this thread's S columns)
+      {
+        float qv[DH][32];
+        float amax = 0.f;
+        if (gq < G) {
+          const uint16_t* qp = p.q + (lb * g.h_q + c.h * G + gq) * D + 32 * tq;
+#pragma unroll
+          for (int hf = 0; hf < DH; ++hf) {
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(qp + hf * 128 + v4 * 8);
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                qv[hf][v4 * 8 + 2 * i] = bf16_bits_to_float(w[i] & 0xFFFFu);
+                qv[hf][v4 * 8 + 2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
+              }
+            }
+          }
+#pragma unroll
+          for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(qv[hf][i]));
+        } else {
+#pragma unroll
+          for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) qv[hf][i] = 0.f;
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF);
+        ex = ex < 1 ? 127 : (ex > 253 ? 253 : ex);   // zero / denormal / inf / NaN heads: no rescale worth doing
+        const float down = __uint_as_float((uint32_t)(254 - ex) << 23);   // 2^(127-ex)
+        const float up = __uint_as_float((uint32_t)ex << 23);             // 2^(ex-127)
+#pragma unroll
+        for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            __half2 b0 = __floats2half2_rn(qv[hf][4 * w] * down, qv[hf][4 * w + 1] * down);
+            __half2 b1 = __floats2half2_rn(qv[hf][4 * w + 2] * down, qv[hf][4 * w + 3] * down);
+            qf[hf * 8 + w][0] = *reinterpret_cast<uint32_t*>(&b0);
+            qf[hf * 8 + w][1] = *reinterpret_cast<uint32_t*>(&b1);
+          }
+        const float ks = p.k_scale[c.layer * g.h_kv + c.h] * p.score_scale;
+        const float mult = up * ks;                       // held by the lanes of head gq
+        sc0 = __shfl_sync(0xffffffffu, mult, 8 * tq);     // head 2*tq   lives in lanes 8*tq .. 8*tq+3
+        sc1 = __shfl_sync(0xffffffffu, mult, 8 * tq + 4); // head 2*tq+1 lives in lanes 8*tq+4 ..
+      }
+
+      float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+      float o[KSTEPS][4];
+#pragma unroll
+      for (int j = 0; j < KSTEPS; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+
+      for (int ti = 0; ti < ntiles; ++ti, ++it) {
+        const int s = it % stages;
+        const bool ok = mbar_wait(full0 + 8u * s, (it / stages) & 1, timed_out, p.status);
+        const int tok0 = (c.tile + ti) * kTileT + warp * 16;   // first token of this warp's 16
+        if (ok && tok0 < c.len_b) {
+          // ---------------- S^T[16 tokens x 8 heads] = K q^T ----------------
+          float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint32_t kt = sK_addr + s * TILE_BYTES;
+#pragma unroll
+          for (int hf = 0; hf < DH; ++hf) {
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+              const uint32_t off = hf * kTileT * 128 + (((2 * tq + ch) ^ gq) << 4);
+              const uint4 klo = lds128(kt + off + row_lo * 128);
+              const uint4 khi = lds128(kt + off + (row_lo + 8) * 128);
+              const uint32_t wl[4] = {klo.x, klo.y, klo.z, klo.w};
+              const uint32_t wh[4] = {khi.x, khi.y, khi.z, khi.w};
+#pragma unroll
+              for (int wi = 0; wi < 4; ++wi) {
+                const int ks = hf * 8 + ch * 4 + wi;
+                mma_f16(sacc, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
+              }
+            }
+          }
+          // ---------------- online softmax (log2 domain) ----------------
+          float s0 = sacc[0] * sc0, s1 = sacc[1] * sc1, s2 = sacc[2] * sc0, s3 = sacc[3] * sc1;
+          if (tok0 + gq >= c.len_b) { s0 = -INFINITY; s1 = -INFINITY; }
+          if (tok0 + gq + 8 >= c.len_b) { s2 = -INFINITY; s3 = -INFINITY; }
+          float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+          for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+          }
+          const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+          const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+          const float al0 = ex2(m0 - ms0), al1 = ex2(m1 - ms1);
+          const float p0 = ex2(s0 - ms0), p1 = ex2(s1 - ms1), p2 = ex2(s2 - ms0), p3 = ex2(s3 - ms1);
+          m0 = mn0; m1 = mn1;
+          l0 = l0 * al0 + (p0 + p2);
+          l1 = l1 * al1 + (p1 + p3);
+          if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+            for (int j = 0; j < KSTEPS; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
+          }
+          // P^T fragments (B operand of O^T += V^T P^T): transpose [token x head] -> [head x token]
+          __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
+          const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pa));
+          const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pb));
+
+          // ---------------- O^T[D dims x 8 heads] += V^T P^T ----------------
+          const uint32_t vt = sV_addr + s * TILE_BYTES;
+          const int vr = warp * 16 + 2 * tq;   // V rows vr, vr+1, vr+8, vr+9
+          const bool tail = tok0 + 16 > c.len_b;
+#pragma unroll
+          for (int hf = 0; hf < DH; ++hf) {
+            const uint32_t vb = vt + hf * kTileT * 128;
+            uint4 va = lds128(vb + vr * 128 + ((gq ^ (2 * tq)) << 4));
+            uint4 vbb = lds128(vb + (vr + 1) * 128 + ((gq ^ (2 * tq + 1)) << 4));
+            uint4 vc = lds128(vb + (vr + 8) * 128 + ((gq ^ (2 * tq)) << 4));
+            uint4 vd = lds128(vb + (vr + 9) * 128 + ((gq ^ (2 * tq + 1)) << 4));
+            if (tail) {   // slots at or beyond the valid length may hold anything, NaN patterns included
+              const int tv = tok0 + 2 * tq;
+              const uint4 z = make_uint4(0, 0, 0, 0);
+              if (tv >= c.len_b) va = z;
+              if (tv + 1 >= c.len_b) vbb = z;
+              if (tv + 8 >= c.len_b) vc = z;
+              if (tv + 9 >= c.len_b) vd = z;
+            }
+            const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vbb.x, vbb.y, vbb.z, vbb.w};
+            const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+              const uint32_t x01 = prmt(wa[wi], wb[wi], 0x5140), x23 = prmt(wa[wi], wb[wi], 0x7362);
+              const uint32_t y01 = prmt(wc[wi], wd[wi], 0x5140), y23 = prmt(wc[wi], wd[wi], 0x7362);
+              mma_f16(o[hf * 8 + 2 * wi], cvt_lo(x01), cvt_hi(x01), cvt_lo(y01), cvt_hi(y01), pb0, pb1);
+              mma_f16(o[hf * 8 + 2 * wi + 1], cvt_lo(x23), cvt_hi(x23), cvt_lo(y23), cvt_hi(y23), pb0, pb1);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8u * s);
+      }
+
+      // ---------------- end of segment: merge the four warps ----------------
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+      }
+      if (gq == 0) {
+        sM[warp * 8 + 2 * tq] = m0; sM[warp * 8 + 2 * tq + 1] = m1;
+        sL[warp * 8 + 2 * tq] = l0; sL[warp * 8 + 2 * tq + 1] = l1;
+      }
+      bar_consumers();
+      {
+        float M0 = -INFINITY, M1 = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+          M0 = fmaxf(M0, sM[w * 8 + 2 * tq]);
+          M1 = fmaxf(M1, sM[w * 8 + 2 * tq + 1]);
+        }
+        const float f0 = m0 == -INFINITY ? 0.f : ex2(m0 - M0), f1 = m1 == -INFINITY ? 0.f : ex2(m1 - M1);
+        // o[hf*8 + 2*wi + e]: regs 0,1 -> dim hf*128 + 16*gq + 4*wi + 2*e, regs 2,3 -> that dim + 1
+        const int h0 = 2 * tq, h1 = 2 * tq + 1;
+#pragma unroll
+        for (int j = 0; j < KSTEPS; ++j) {
+          const int dim = (j >> 3) * 128 + 16 * gq + 2 * (j & 7);
+          if (h0 < G) {
+            sO[(warp * G + h0) * D + dim] = o[j][0] * f0;
+            sO[(warp * G + h0) * D + dim + 1] = o[j][2] * f0;
+          }
+          if (h1 < G) {
+            sO[(warp * G + h1) * D + dim] = o[j][1] * f1;
+            sO[(warp * G + h1) * D + dim + 1] = o[j][3] * f1;
+          }
+        }
+      }
+      bar_consumers();
+      const bool complete = cur == pair_start && seg_end == pair_end;
+      const float vs = p.v_scale[c.layer * g.h_kv + c.h];
+      const int slot = cur == r0 ? 0 : 1;
+      float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
+      float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
+      for (int idx = tid; idx < G * D; idx += kConsumerThreads) {
+        const int head = idx / D, dim = idx - head * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sM[w * 8 + head]);
+        float a = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+          const float mw = sM[w * 8 + head];
+          ll += sL[w * 8 + head] * (mw == -INFINITY ? 0.f : ex2(mw - M));
+          a += sO[(w * G + head) * D + dim];
+        }
+        if (complete) {
+          const float ov = ll > 0.f ? a * vs / ll : 0.f;
+          __nv_bfloat16 ob = __float2bfloat16_rn(ov);
+          p.out[(lb * g.h_q + c.h * G + head) * D + dim] = *reinterpret_cast<uint16_t*>(&ob);
+        } else {
+          pacc[idx] = a;
+          if (dim == 0) { pml[head] = M; pml[8 + head] = ll; }
+        }
+      }
+      if (!complete) {
+        // ---- fused combine: the last owner of the pair to arrive merges all partials ----
+        const int c_first = owner_of(pair_start, total, n_eff), c_last = owner_of(pair_end - 1, total, n_eff);
+        bar_consumers();
+        if (tid == 0) {
+          __threadfence();
+          const int ticket = atomicAdd(p.tickets + pair, 1);
+          sFlags[1] = ticket == c_last - c_first;
+        }
+        bar_consumers();
+        if (sFlags[1]) {
+          __threadfence();
+          for (int idx = tid; idx < G * D; idx += kConsumerThreads) {
+            const int head = idx / D;
+            float M = -INFINITY;
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const int sl = (cc == c_first && (long long)cc * total / n_eff < pair_start) ? 1 : 0;
+              M = fmaxf(M, __ldcg(p.ws_ml + ((long long)cc * 2 + sl) * 16 + head));
+            }
+            float a = 0.f, ll = 0.f;
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const int sl = (cc == c_first && (long long)cc * total / n_eff < pair_start) ? 1 : 0;
+              const float* ml = p.ws_ml + ((long long)cc * 2 + sl) * 16;
+              const float mc = __ldcg(ml + head);
+              const float f = mc == -INFINITY ? 0.f : ex2(mc - M);
+              ll += __ldcg(ml + 8 + head) * f;
+              a += __ldcg(p.ws_acc + ((long long)cc * 2 + sl) * G * D + idx) * f;
+            }
+            const float ov = ll > 0.f ? a * vs / ll : 0.f;
+            __nv_bfloat16 ob = __float2bfloat16_rn(ov);
+            p.out[(lb * g.h_q + c.h * G + head) * D + (idx - head * D)] = *reinterpret_cast<uint16_t*>(&ob);
+          }
+          if (tid == 0) p.tickets[pair] = 0;   // ready for the next launch
+        }
+      }
+      bar_consumers();   // sM / sL / sO / sFlags[1] are reused by the next segment
+
+      cur = seg_end;
+      if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+    }
+  }
+  __syncthreads();
+  if (sFlags[0] && tid == kConsumerThreads) {
+    // A wait gave up.  Copies already issued still land in this CTA's shared memory: wait for
+    // them (bounded) so the CTA does not retire underneath them.
+    const int it = sFlags[3];
+    for (int s = 0; s < stages && s < it; ++s) {
+      const int last_it = ((it - 1 - s) / stages) * stages + s;   // last iteration that used stage s
+      const uint32_t par = (last_it / stages) & 1;
+      const unsigned long long t0 = global_timer_ns();
+      while (!mbar_try_wait(full0 + 8u * s, par) && global_timer_ns() - t0 < kWaitBudgetNs) {}
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// u8 view [n_layers][rows = batch*h_kv*capacity][D], box = 128 bytes x kTileT rows, 128-byte swizzle.
+bool encode_cache_map(CUtensorMap* map, const void* base, const Geometry& g, long long layer_stride) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)g.head_dim, (cuuint64_t)g.batch * g.h_kv * g.capacity, (cuuint64_t)g.n_layers};
+  const cuuint64_t strides[2] = {(cuuint64_t)g.head_dim, (cuuint64_t)layer_stride};
+  const cuuint32_t box[3] = {128, (cuuint32_t)kTileT, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int stages_for(const Geometry& g) { return g.head_dim == 128 ? 4 : 3; }
+
+size_t smem_bytes_for(const Geometry& g, int stages) {
+  size_t b = 1024;                                            // alignment slack
+  b += (size_t)2 * stages * kTileT * g.head_dim;              // K and V rings
+  b += (size_t)kConsumerWarps * g.group * g.head_dim * 4;     // sO
+  b += (size_t)2 * kConsumerWarps * 8 * 4;                    // sM, sL
+  b += (size_t)2 * stages * 8;                                // barriers
+  b += 16;                                                    // flags
+  b += (size_t)(2 * g.batch + 1) * 4;                         // sLen, sCum
+  return (b + 15) & ~(size_t)15;
+}
+
+}  // namespace
+
+size_t mma_workspace_bytes(const Geometry& g, int num_ctas) {
+  const size_t pairs = (size_t)g.n_layers * g.batch * g.h_kv;
+  size_t b = (size_t)num_ctas * 2 * g.group * g.head_dim * sizeof(float);   // ws_acc
+  b += (size_t)num_ctas * 2 * 16 * sizeof(float);                            // ws_ml
+  b += pairs * sizeof(int);                                                  // tickets
+  return (b + 255) & ~(size_t)255;
+}
+
+int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
+  (void)max_seq_len;
+  const size_t smem = smem_bytes_for(g, stages_for(g));
+  int per_sm = (int)((227 * 1024) / (smem + 1024));   // + per-CTA reservation
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 2) per_sm = 2;
+  return num_sms * per_sm;
+}
+
+cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream) {
+  if (g.scale_mode != B200ATTN_SCALE_PER_HEAD || g.batch > kMaxBatchMma) return cudaErrorNotSupported;
+  CUtensorMap kmap, vmap;
+  if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride) || !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride))
+    return cudaErrorInvalidValue;
+  MmaParams p;
+  p.g = g;
+  p.q = (const uint16_t*)a.q;
+  p.k_scale = a.k_scale;
+  p.v_scale = a.v_scale;
+  p.seq_len = a.seq_len;
+  p.seq_len_offset = a.seq_len_offset;
+  p.score_scale = a.softmax_scale * kLog2e;
+  const int n = a.num_splits;
+  p.ws_acc = (float*)a.workspace;
+  p.ws_ml = p.ws_acc + (size_t)n * 2 * g.group * g.head_dim;
+  p.tickets = (int*)(p.ws_ml + (size_t)n * 2 * 16);
+  p.out = (uint16_t*)a.out;
+  p.status = a.status;
+  p.stages = stages_for(g);
+  const size_t smem = smem_bytes_for(g, p.stages);
+  cudaError_t e;
+  if (g.head_dim == 128) {
+    e = cudaFuncSetAttribute(attn_streamk_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attn_streamk_mma_kernel<128><<<n, kThreads, smem, stream>>>(kmap, vmap, p);
+  } else {
+    e = cudaFuncSetAttribute(attn_streamk_mma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attn_streamk_mma_kernel<256><<<n, kThreads, smem, stream>>>(kmap, vmap, p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace b200attn
