@@ -38,7 +38,6 @@ extern "C" {
 #define B200ATTN_ERR_CUDA          -6   /* a CUDA runtime / driver call failed (see b200attn_last_cuda_error) */
 #define B200ATTN_ERR_CAPACITY      -7   /* host-known length exceeds capacity */
 #define B200ATTN_ERR_VARIANT       -8   /* unknown kernel variant */
-#define B200ATTN_ERR_TOO_LARGE     -9   /* size beyond a fixed limit of the entry point */
 
 /* device status bits (OR-ed into *status) */
 #define B200ATTN_STATUS_POS_AT_CAPACITY  1  /* append skipped: seq_pos[b] >= capacity */

@@ -63,7 +63,6 @@ const char* b200attn_error_string(int code) {
     case B200ATTN_ERR_CUDA: return "CUDA call failed";
     case B200ATTN_ERR_CAPACITY: return "length exceeds capacity";
     case B200ATTN_ERR_VARIANT: return "unknown kernel variant";
-    case B200ATTN_ERR_TOO_LARGE: return "size beyond the fixed limit of this entry point";
   }
   return "unknown error code";
 }
