@@ -173,11 +173,11 @@ def workload_name(key: str, depth: int, cap: int) -> str:
 class StepRunner:
     """One workload resident on one GPU: cache, static step buffers, captured graph."""
 
-    def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1):
+    def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto"):
         self.pkg, self.torch, self.device, self.depth, self.advance = pkg, torch, device, depth, advance
         self.h_q, self.h_kv, self.dist, self.world = h_q, h_kv, dist, world
         g = torch.Generator(device=device).manual_seed(seed)
-        self.cache = pkg.FP8StaticCache(N_LAYERS, 1, h_q, h_kv, D, cap, device=device)
+        self.cache = pkg.FP8StaticCache(N_LAYERS, 1, h_q, h_kv, D, cap, device=device, variant=variant)
         prefix = depth if advance else depth - 1      # cfg2: slot depth-1 is rewritten by every step
         chunk = 8192
         scales_done = False
@@ -227,7 +227,8 @@ class StepRunner:
         self.gather()
 
     def kernels_per_step(self) -> int:
-        return 3 if self.advance else 2      # append, attention(+fused combine), position bump
+        n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump
+        return n + (1 if self.cache.workspace.variant == "simt" and self.cache.workspace.num_splits > 1 else 0)
 
 
 def barrier(dist, world):
@@ -365,7 +366,8 @@ def run_ours(args) -> int:
         depth, cap, advance = WORKLOADS[key]
         room = cap - depth - args.warmup - 4 if advance else 1 << 30   # the cache must not overflow
         steps = max(1, min(args.steps, room))
-        runner = StepRunner(pkg, torch, device, depth, cap, advance, h_q, h_kv, seed=rank, dist=dist, world=world)
+        runner = StepRunner(pkg, torch, device, depth, cap, advance, h_q, h_kv, seed=rank, dist=dist, world=world,
+                            variant=args.variant)
         runner.capture()
         if world > 1:   # communicator warm-up outside the timed region
             runner.gather()
@@ -407,7 +409,7 @@ def run_ours(args) -> int:
         "hbm_gbs": kv_bytes_per_step(depth) / sec / 1e9,
         "frac_of_8TBs": kv_bytes_per_step(depth) / world / sec / 8e12,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": load_traffic(key), "kernel": "attn_streamk_mma_kernel<128>", "peak_kind": peak_kind,
+                     "traffic": load_traffic(key), "kernel": "attn_splitk_simt_kernel<128,5>" if args.variant == "simt" else "attn_streamk_mma_kernel<128>", "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": bytes_per_launch, "launch_us": ksec * 1e6},
         "e2e": {"value": e2e_sec * 1e6, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": runner.kernels_per_step() * steps,
@@ -431,9 +433,13 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
+    ap.add_argument("--variant", choices=["auto", "mma", "simt"], default="auto", help="attention kernel variant")
+    ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global N_LAYERS
+    N_LAYERS = args.layers
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
