@@ -10,7 +10,7 @@ import os
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
-LIB_PATH = PKG_DIR / "libb200attn.so"
+LIB_PATH = Path(os.environ.get("B200ATTN_LIB") or PKG_DIR / "libb200attn.so")   # override: an alternative build
 
 c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_longlong
 

@@ -8,16 +8,19 @@
 //   * a producer warp streams K and V tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle)
 //     into a ring of shared-memory stages guarded by full/empty mbarriers; every KV byte is read
 //     from HBM exactly once and serves all G query heads of the group;
+//   * the producer also stages the G query rows of each pair (one cp.async.bulk per segment);
 //   * four consumer warps each own 16 tokens of a tile.  FP8 bytes go from shared memory to
 //     registers, are widened to f16 in registers (cvt.rn.f16x2.e4m3x2, exact) and feed
 //     mma.sync.m16n8k16 with the query heads on the N side (G <= 8): S^T = K q^T, then
 //     O^T += V^T P^T after a warp-level movmatrix transpose of the probabilities.  Accumulation
 //     and the log2-domain online softmax are fp32.  The per-head scales never enter the loop:
 //     k_scale*softmax_scale*log2e multiplies the scores, v_scale the final normalisation;
-//   * a pair owned by one CTA is normalised and written directly; otherwise each owner writes an
-//     (m, l, acc) partial and takes an arrival ticket; the last arriver merges the partials in
-//     CTA order (deterministic, so replays are bitwise identical) and resets the ticket.  Nothing
-//     ever spins on another CTA.  The only waits are on the CTA's own copy barriers, and those
+//   * at the end of a pair (or of the CTA's range) the consumer warps dump their (m, l, acc)
+//     state into a double-buffered shared-memory area and go straight on to the next pair; an
+//     epilogue warp merges the four states off the critical path.  A pair owned by one CTA is
+//     normalised and written directly; otherwise each owner writes an (m, l, acc) partial and
+//     takes an arrival ticket; the last arriver merges the partials in CTA order (deterministic,
+//     so replays are bitwise identical) and resets the ticket.  Nothing ever spins on another CTA.  The only waits are on the CTA's own copy barriers, and those
 //     are bounded: on expiry the CTA flags B200ATTN_STATUS_WAIT_TIMEOUT, stops waiting, drains
 //     its copies and returns.
 //
@@ -38,7 +41,9 @@ namespace {
 constexpr int kTileT = 64;                 // tokens per tile
 constexpr int kConsumerWarps = 4;          // 16 tokens each
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;  // + producer warp
+constexpr int kProducerWarp = kConsumerWarps;          // warp 4: TMA issue
+constexpr int kEpilogueWarp = kConsumerWarps + 1;      // warp 5: merge, output, fused combine
+constexpr int kThreads = kConsumerThreads + 64;
 constexpr int kMaxBatchMma = 2048;
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait
 
@@ -115,7 +120,13 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void sts64(uint32_t addr, float x, float y) {
+  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(x), "f"(y) : "memory");
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -143,6 +154,18 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+
+#ifdef B200ATTN_TRACE
+// Development-only timeline: per CTA, globaltimer stamps of (0) kernel entry, (1) prologue done,
+// (2) first tile landed, (3) first segment's tiles consumed, (4) first segment's state dumped,
+// (5) last tile consumed, (6) exit, (7) epilogue warp done.
+__device__ unsigned long long g_trace[4096 * 8];
+#define TRACE(slot) do { if (tid == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
+#define TRACE_LANE0(slot) do { if (lane == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#define TRACE_LANE0(slot) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // the stream-K walk: linear tile index -> (layer, sequence, kv head, tile)
@@ -193,6 +216,11 @@ __device__ __forceinline__ int owner_of(long long x, long long total, int n) {
   return (int)(((x + 1) * n - 1) / total);
 }
 
+
+// Position (in float2 units) of dim pair u inside a dumped head row.  The xor spreads the
+// consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
+__device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
+
 template <int D>
 __global__ void __launch_bounds__(kThreads)
 attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -200,31 +228,44 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   constexpr int DH = D / 128;              // 128-byte column blocks per row
   constexpr int KSTEPS = D / 16;           // mma k-steps for QK^T == mma tiles for PV
   constexpr int TILE_BYTES = kTileT * D;   // one K (or V) tile
+  constexpr int DP = D + 4;                // padded head row of a dumped state, in floats
+  constexpr int UR = D / 64;               // dim pairs per epilogue lane
   const Geometry& g = p.g;
   const int G = g.group;
   const int stages = p.stages;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates ("groupID", "threadID_in_group")
+  const uint32_t q_bytes = (uint32_t)G * D * 2;
+  const int dump_warp_floats = G * DP;
 
+  TRACE(0);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
   uint8_t* sK = smem;
   uint8_t* sV = sK + (size_t)stages * TILE_BYTES;
-  float* sO = reinterpret_cast<float*>(sV + (size_t)stages * TILE_BYTES);   // [4][G][D]
-  float* sM = sO + kConsumerWarps * G * D;                                   // [4][8]
-  float* sL = sM + kConsumerWarps * 8;                                       // [4][8]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sL + kConsumerWarps * 8);     // full[stages], empty[stages]
-  int* sFlags = reinterpret_cast<int*>(bars + 2 * stages);                   // [0] timed_out [1] is_last [2] any_empty
-  int* sLen = sFlags + 4;                                                    // [batch]
-  int* sCum = sLen + g.batch;                                                // [batch+1]
+  uint8_t* sQ = sV + (size_t)stages * TILE_BYTES;                                     // [2][G*D] bf16
+  float* sDump = reinterpret_cast<float*>(sQ + 2 * q_bytes);                          // [2][4][G][DP]
+  float* sML = sDump + 2 * kConsumerWarps * dump_warp_floats;                         // [2][4][16]: m[8], l[8]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + 2 * kConsumerWarps * 16);
+  int* sFlags = reinterpret_cast<int*>(bars + 2 * stages + 8);                        // [0] timed_out [2] any_empty [3] copies
+  int* sLen = sFlags + 4;                                                             // [batch]
+  int* sCum = sLen + g.batch;                                                         // [batch+1]
   volatile int* timed_out = sFlags;
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * stages;
+  const uint32_t qfull0 = empty0 + 8u * stages, qempty0 = qfull0 + 16u;
+  const uint32_t dfull0 = qempty0 + 16u, dempty0 = dfull0 + 16u;
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(full0 + 8u * s, 1);
       mbar_init(empty0 + 8u * s, kConsumerWarps);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(qfull0 + 8u * i, 1);
+      mbar_init(qempty0 + 8u * i, kConsumerWarps);
+      mbar_init(dfull0 + 8u * i, kConsumerWarps);
+      mbar_init(dempty0 + 8u * i, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -243,7 +284,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     sFlags[2] = any_empty;
     if (st && blockIdx.x == 0) atomicOr(p.status, st);
   }
-  if (warp == kConsumerWarps && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
   }
@@ -262,18 +303,29 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   const long long total = per_layer * g.n_layers;
   const int n_eff = (int)(total < (long long)gridDim.x ? total : (long long)gridDim.x);
   const bool has_work = (long long)blockIdx.x < (long long)n_eff;
+  TRACE(1);
   long long r0 = 0, r1 = 0;
   if (has_work) {
     r0 = (long long)blockIdx.x * total / n_eff;
     r1 = ((long long)blockIdx.x + 1) * total / n_eff;
   }
 
-  if (warp == kConsumerWarps) {
+  if (warp == kProducerWarp) {
     // ===================== producer warp: one elected lane issues the copies =====================
     if (lane == 0 && has_work) {
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
-      int it = 0;
+      int it = 0, seg = 0;
+      bool seg_start = true;
       for (long long idx = r0; idx < r1; ++idx, ++it) {
+        if (seg_start) {   // the G query rows of this pair, once per segment
+          const int qb = seg & 1;
+          if (seg >= 2 && !mbar_wait(qempty0 + 8u * qb, ((seg >> 1) - 1) & 1, timed_out, p.status)) break;
+          mbar_arrive_expect_tx(qfull0 + 8u * qb, q_bytes);
+          const long long lb = (long long)c.layer * g.batch + c.b;
+          bulk_load(smem_u32(sQ + qb * q_bytes), p.q + (lb * g.h_q + c.h * G) * D, q_bytes, qfull0 + 8u * qb);
+          ++seg;
+          seg_start = false;
+        }
         const int s = it % stages;
         if (it >= stages && !mbar_wait(empty0 + 8u * s, ((it / stages) - 1) & 1, timed_out, p.status)) break;
         const uint32_t fb = full0 + 8u * s;
@@ -284,15 +336,145 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
           tma_load_3d(smem_u32(sK + (size_t)s * TILE_BYTES + hf * kTileT * 128), &kmap, hf * 128, row, c.layer, fb);
           tma_load_3d(smem_u32(sV + (size_t)s * TILE_BYTES + hf * kTileT * 128), &vmap, hf * 128, row, c.layer, fb);
         }
-        if (++c.tile == c.tiles_b && idx + 1 < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+        if (++c.tile == c.tiles_b) {
+          seg_start = true;
+          if (idx + 1 < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+        }
       }
-      sFlags[3] = it;   // copies issued, for the drain below
+      sFlags[3] = it;   // tile copies issued, for the drain at the end
+      sFlags[1] = seg;  // query copies issued
+    }
+  } else if (warp == kEpilogueWarp) {
+    // ===================== epilogue warp: merge dumped states, write, fused combine =====================
+    if (has_work) {
+      Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+      long long cur = r0;
+      int seg = 0;
+      while (cur < r1) {
+        const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
+        const long long seg_end = pair_end < r1 ? pair_end : r1;
+        const long long lb = (long long)c.layer * g.batch + c.b;
+        const long long pair = lb * g.h_kv + c.h;
+        const bool complete = cur == pair_start && seg_end == pair_end;
+        const float vs = p.v_scale[c.layer * g.h_kv + c.h];
+        const int db = seg & 1;
+        const bool ok = mbar_wait(dfull0 + 8u * db, (seg >> 1) & 1, timed_out, p.status);
+        const float* dump = sDump + db * kConsumerWarps * dump_warp_floats;
+        const float* ml = sML + db * kConsumerWarps * 16;
+        const int slot = cur == r0 ? 0 : 1;
+        float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
+        float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
+        uint16_t* orow = p.out + (lb * g.h_q + c.h * G) * D;
+        if (ok) {
+          for (int h = 0; h < G; ++h) {
+            float mw[kConsumerWarps], M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) { mw[w] = ml[w * 16 + h]; M = fmaxf(M, mw[w]); }
+            float ll = 0.f, ax[UR], ay[UR];
+#pragma unroll
+            for (int r = 0; r < UR; ++r) { ax[r] = 0.f; ay[r] = 0.f; }
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+              const float f = mw[w] == -INFINITY ? 0.f : ex2(mw[w] - M);
+              ll += ml[w * 16 + 8 + h] * f;
+#pragma unroll
+              for (int r = 0; r < UR; ++r) {
+                const float2 v = *reinterpret_cast<const float2*>(dump + w * dump_warp_floats + h * DP + 2 * dump_pos(lane + 32 * r));
+                ax[r] += v.x * f;
+                ay[r] += v.y * f;
+              }
+            }
+            if (complete) {
+              const float inv = ll > 0.f ? vs / ll : 0.f;
+#pragma unroll
+              for (int r = 0; r < UR; ++r) {
+                __nv_bfloat162 ob = __floats2bfloat162_rn(ax[r] * inv, ay[r] * inv);
+                *reinterpret_cast<uint32_t*>(orow + h * D + 2 * (lane + 32 * r)) = *reinterpret_cast<uint32_t*>(&ob);
+              }
+            } else {
+#pragma unroll
+              for (int r = 0; r < UR; ++r)
+                *reinterpret_cast<float2*>(pacc + h * D + 2 * (lane + 32 * r)) = make_float2(ax[r], ay[r]);
+              if (lane == 0) { pml[h] = M; pml[8 + h] = ll; }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dempty0 + 8u * db);   // the dump buffer may be overwritten
+        if (!complete && ok) {
+          // ---- fused combine: the last owner of the pair to arrive merges all partials ----
+          const int c_first = owner_of(pair_start, total, n_eff), c_last = owner_of(pair_end - 1, total, n_eff);
+          int last = 0;
+          if (lane == 0) {
+            __threadfence();
+            last = atomicAdd(p.tickets + pair, 1) == c_last - c_first;
+          }
+          last = __shfl_sync(0xffffffffu, last, 0);
+          if (last) {
+            __threadfence();
+            const int first_slot = (long long)c_first * total / n_eff < pair_start ? 1 : 0;
+            float M[kMaxGroup];
+#pragma unroll
+            for (int h = 0; h < kMaxGroup; ++h) M[h] = -INFINITY;
+#pragma unroll 4
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const float* cml = p.ws_ml + ((long long)cc * 2 + (cc == c_first ? first_slot : 0)) * 16;
+#pragma unroll
+              for (int h = 0; h < kMaxGroup; ++h)
+                if (h < G) M[h] = fmaxf(M[h], __ldcg(cml + h));
+            }
+            float ll[kMaxGroup], ax[kMaxGroup][UR], ay[kMaxGroup][UR];
+#pragma unroll
+            for (int h = 0; h < kMaxGroup; ++h) {
+              ll[h] = 0.f;
+#pragma unroll
+              for (int r = 0; r < UR; ++r) { ax[h][r] = 0.f; ay[h][r] = 0.f; }
+            }
+#pragma unroll 2
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const int sl = cc == c_first ? first_slot : 0;
+              const float* cml = p.ws_ml + ((long long)cc * 2 + sl) * 16;
+              const float* cacc = p.ws_acc + ((long long)cc * 2 + sl) * G * D;
+#pragma unroll
+              for (int h = 0; h < kMaxGroup; ++h) {
+                if (h < G) {
+                  const float mc = __ldcg(cml + h);
+                  const float f = mc == -INFINITY ? 0.f : ex2(mc - M[h]);
+                  ll[h] += __ldcg(cml + 8 + h) * f;
+#pragma unroll
+                  for (int r = 0; r < UR; ++r) {
+                    const float2 v = __ldcg(reinterpret_cast<const float2*>(cacc + h * D + 2 * (lane + 32 * r)));
+                    ax[h][r] += v.x * f;
+                    ay[h][r] += v.y * f;
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int h = 0; h < kMaxGroup; ++h) {
+              if (h < G) {
+                const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
+#pragma unroll
+                for (int r = 0; r < UR; ++r) {
+                  __nv_bfloat162 ob = __floats2bfloat162_rn(ax[h][r] * inv, ay[h][r] * inv);
+                  *reinterpret_cast<uint32_t*>(orow + h * D + 2 * (lane + 32 * r)) = *reinterpret_cast<uint32_t*>(&ob);
+                }
+              }
+            }
+            if (lane == 0) p.tickets[pair] = 0;   // ready for the next launch
+          }
+        }
+        ++seg;
+        cur = seg_end;
+        if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+      }
+      TRACE_LANE0(7);
     }
   } else if (has_work) {
     // ================================ consumer warps ================================
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
     long long cur = r0;
-    int it = 0;
+    int it = 0, seg = 0;
     const uint32_t sK_addr = smem_u32(sK), sV_addr = smem_u32(sV);
     const int row_lo = warp * 16 + gq;   // K row of this thread inside a tile (and row_lo + 8)
 
@@ -300,8 +482,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
       const long long seg_end = pair_end < r1 ? pair_end : r1;
       const int ntiles = (int)(seg_end - cur);
-      const long long lb = (long long)c.layer * g.batch + c.b;
-      const long long pair = lb * g.h_kv + c.h;
+      const int qb = seg & 1;
 
       // ---- query fragments (B operand of S^T = K q^T): head gq, dims hf*128 + 32*tq + 4*ks' ----
       // Each head is rescaled by a power of two so that its largest |q| lies in [1, 2): exact,
@@ -309,15 +490,16 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       uint32_t qf[KSTEPS][2];
       float sc0, sc1;   // score multipliers of heads 2*tq and 2*tq+1 (this thread's S columns)
       {
+        const bool qok = mbar_wait(qfull0 + 8u * qb, (seg >> 1) & 1, timed_out, p.status);
         float qv[DH][32];
         float amax = 0.f;
-        if (gq < G) {
-          const uint16_t* qp = p.q + (lb * g.h_q + c.h * G + gq) * D + 32 * tq;
+        if (gq < G && qok) {
+          const uint32_t qaddr = smem_u32(sQ + qb * q_bytes) + (gq * D + 32 * tq) * 2;
 #pragma unroll
           for (int hf = 0; hf < DH; ++hf) {
 #pragma unroll
             for (int v4 = 0; v4 < 4; ++v4) {
-              const uint4 raw = *reinterpret_cast<const uint4*>(qp + hf * 128 + v4 * 8);
+              const uint4 raw = lds128(qaddr + hf * 256 + v4 * 16);
               const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -336,6 +518,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 #pragma unroll
             for (int i = 0; i < 32; ++i) qv[hf][i] = 0.f;
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(qempty0 + 8u * qb);   // the query buffer may be refilled
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
         int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF);
@@ -365,10 +549,13 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       for (int ti = 0; ti < ntiles; ++ti, ++it) {
         const int s = it % stages;
         const bool ok = mbar_wait(full0 + 8u * s, (it / stages) & 1, timed_out, p.status);
+#ifdef B200ATTN_TRACE
+        if (it == 0) TRACE(2);
+#endif
         const int tok0 = (c.tile + ti) * kTileT + warp * 16;   // first token of this warp's 16
         if (ok && tok0 < c.len_b) {
           // ---------------- S^T[16 tokens x 8 heads] = K q^T ----------------
-          float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+          float sacc[4] = {0.f, 0.f, 0.f, 0.f}, sacc2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains
           const uint32_t kt = sK_addr + s * TILE_BYTES;
 #pragma unroll
           for (int hf = 0; hf < DH; ++hf) {
@@ -382,12 +569,16 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 #pragma unroll
               for (int wi = 0; wi < 4; ++wi) {
                 const int ks = hf * 8 + ch * 4 + wi;
-                mma_f16(sacc, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
+                if (wi & 1)
+                  mma_f16(sacc2, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
+                else
+                  mma_f16(sacc, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
               }
             }
           }
           // ---------------- online softmax (log2 domain) ----------------
-          float s0 = sacc[0] * sc0, s1 = sacc[1] * sc1, s2 = sacc[2] * sc0, s3 = sacc[3] * sc1;
+          float s0 = (sacc[0] + sacc2[0]) * sc0, s1 = (sacc[1] + sacc2[1]) * sc1;
+          float s2 = (sacc[2] + sacc2[2]) * sc0, s3 = (sacc[3] + sacc2[3]) * sc1;
           if (tok0 + gq >= c.len_b) { s0 = -INFINITY; s1 = -INFINITY; }
           if (tok0 + gq + 8 >= c.len_b) { s2 = -INFINITY; s3 = -INFINITY; }
           float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
@@ -445,119 +636,61 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8u * s);
       }
+#ifdef B200ATTN_TRACE
+      if (cur == r0) TRACE(3);
+      if (seg_end == r1) TRACE(5);
+#endif
 
-      // ---------------- end of segment: merge the four warps ----------------
+      // ---------------- end of segment: hand the warp's state to the epilogue warp ----------------
 #pragma unroll
       for (int off = 4; off < 32; off <<= 1) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, off);
         l1 += __shfl_xor_sync(0xffffffffu, l1, off);
       }
-      if (gq == 0) {
-        sM[warp * 8 + 2 * tq] = m0; sM[warp * 8 + 2 * tq + 1] = m1;
-        sL[warp * 8 + 2 * tq] = l0; sL[warp * 8 + 2 * tq + 1] = l1;
-      }
-      bar_consumers();
-      {
-        float M0 = -INFINITY, M1 = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) {
-          M0 = fmaxf(M0, sM[w * 8 + 2 * tq]);
-          M1 = fmaxf(M1, sM[w * 8 + 2 * tq + 1]);
+      const int db = seg & 1;
+      if (seg < 2 || mbar_wait(dempty0 + 8u * db, ((seg >> 1) - 1) & 1, timed_out, p.status)) {
+        float* ml = sML + (db * kConsumerWarps + warp) * 16;
+        if (gq == 0) {
+          ml[2 * tq] = m0; ml[2 * tq + 1] = m1;
+          ml[8 + 2 * tq] = l0; ml[8 + 2 * tq + 1] = l1;
         }
-        const float f0 = m0 == -INFINITY ? 0.f : ex2(m0 - M0), f1 = m1 == -INFINITY ? 0.f : ex2(m1 - M1);
-        // o[hf*8 + 2*wi + e]: regs 0,1 -> dim hf*128 + 16*gq + 4*wi + 2*e, regs 2,3 -> that dim + 1
+        // o[j]: regs 0,1 -> dim (j>>3)*128 + 16*gq + 2*(j&7) of heads 2*tq, 2*tq+1; regs 2,3 -> that dim + 1
+        const uint32_t dbase = smem_u32(sDump + (db * kConsumerWarps + warp) * dump_warp_floats);
         const int h0 = 2 * tq, h1 = 2 * tq + 1;
 #pragma unroll
         for (int j = 0; j < KSTEPS; ++j) {
-          const int dim = (j >> 3) * 128 + 16 * gq + 2 * (j & 7);
-          if (h0 < G) {
-            sO[(warp * G + h0) * D + dim] = o[j][0] * f0;
-            sO[(warp * G + h0) * D + dim + 1] = o[j][2] * f0;
-          }
-          if (h1 < G) {
-            sO[(warp * G + h1) * D + dim] = o[j][1] * f1;
-            sO[(warp * G + h1) * D + dim + 1] = o[j][3] * f1;
-          }
+          const int u = (j >> 3) * 64 + 8 * gq + (j & 7);
+          const uint32_t pos8 = 8u * (uint32_t)((u & ~7) | ((j & 7) ^ gq));
+          if (h0 < G) sts64(dbase + h0 * DP * 4 + pos8, o[j][0], o[j][2]);
+          if (h1 < G) sts64(dbase + h1 * DP * 4 + pos8, o[j][1], o[j][3]);
         }
       }
-      bar_consumers();
-      const bool complete = cur == pair_start && seg_end == pair_end;
-      const float vs = p.v_scale[c.layer * g.h_kv + c.h];
-      const int slot = cur == r0 ? 0 : 1;
-      float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
-      float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
-      for (int idx = tid; idx < G * D; idx += kConsumerThreads) {
-        const int head = idx / D, dim = idx - head * D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, sM[w * 8 + head]);
-        float a = 0.f, ll = 0.f;
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) {
-          const float mw = sM[w * 8 + head];
-          ll += sL[w * 8 + head] * (mw == -INFINITY ? 0.f : ex2(mw - M));
-          a += sO[(w * G + head) * D + dim];
-        }
-        if (complete) {
-          const float ov = ll > 0.f ? a * vs / ll : 0.f;
-          __nv_bfloat16 ob = __float2bfloat16_rn(ov);
-          p.out[(lb * g.h_q + c.h * G + head) * D + dim] = *reinterpret_cast<uint16_t*>(&ob);
-        } else {
-          pacc[idx] = a;
-          if (dim == 0) { pml[head] = M; pml[8 + head] = ll; }
-        }
-      }
-      if (!complete) {
-        // ---- fused combine: the last owner of the pair to arrive merges all partials ----
-        const int c_first = owner_of(pair_start, total, n_eff), c_last = owner_of(pair_end - 1, total, n_eff);
-        bar_consumers();
-        if (tid == 0) {
-          __threadfence();
-          const int ticket = atomicAdd(p.tickets + pair, 1);
-          sFlags[1] = ticket == c_last - c_first;
-        }
-        bar_consumers();
-        if (sFlags[1]) {
-          __threadfence();
-          for (int idx = tid; idx < G * D; idx += kConsumerThreads) {
-            const int head = idx / D;
-            float M = -INFINITY;
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const int sl = (cc == c_first && (long long)cc * total / n_eff < pair_start) ? 1 : 0;
-              M = fmaxf(M, __ldcg(p.ws_ml + ((long long)cc * 2 + sl) * 16 + head));
-            }
-            float a = 0.f, ll = 0.f;
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const int sl = (cc == c_first && (long long)cc * total / n_eff < pair_start) ? 1 : 0;
-              const float* ml = p.ws_ml + ((long long)cc * 2 + sl) * 16;
-              const float mc = __ldcg(ml + head);
-              const float f = mc == -INFINITY ? 0.f : ex2(mc - M);
-              ll += __ldcg(ml + 8 + head) * f;
-              a += __ldcg(p.ws_acc + ((long long)cc * 2 + sl) * G * D + idx) * f;
-            }
-            const float ov = ll > 0.f ? a * vs / ll : 0.f;
-            __nv_bfloat16 ob = __float2bfloat16_rn(ov);
-            p.out[(lb * g.h_q + c.h * G + head) * D + (idx - head * D)] = *reinterpret_cast<uint16_t*>(&ob);
-          }
-          if (tid == 0) p.tickets[pair] = 0;   // ready for the next launch
-        }
-      }
-      bar_consumers();   // sM / sL / sO / sFlags[1] are reused by the next segment
-
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dfull0 + 8u * db);
+#ifdef B200ATTN_TRACE
+      if (cur == r0) TRACE(4);
+#endif
+      ++seg;
       cur = seg_end;
       if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
     }
   }
   __syncthreads();
+  TRACE(6);
   if (sFlags[0] && tid == kConsumerThreads) {
     // A wait gave up.  Copies already issued still land in this CTA's shared memory: wait for
     // them (bounded) so the CTA does not retire underneath them.
-    const int it = sFlags[3];
+    const int it = sFlags[3], segs = sFlags[1];
     for (int s = 0; s < stages && s < it; ++s) {
       const int last_it = ((it - 1 - s) / stages) * stages + s;   // last iteration that used stage s
       const uint32_t par = (last_it / stages) & 1;
       const unsigned long long t0 = global_timer_ns();
       while (!mbar_try_wait(full0 + 8u * s, par) && global_timer_ns() - t0 < kWaitBudgetNs) {}
+    }
+    for (int qb = 0; qb < 2 && qb < segs; ++qb) {
+      const int last_seg = ((segs - 1 - qb) / 2) * 2 + qb;
+      const unsigned long long t0 = global_timer_ns();
+      while (!mbar_try_wait(qfull0 + 8u * qb, (last_seg >> 1) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
     }
   }
 }
@@ -595,14 +728,15 @@ bool encode_cache_map(CUtensorMap* map, const void* base, const Geometry& g, lon
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int stages_for(const Geometry& g) { return g.head_dim == 128 ? 4 : 3; }
+int stages_for(const Geometry& g) { return g.head_dim == 128 ? 5 : 3; }
 
 size_t smem_bytes_for(const Geometry& g, int stages) {
   size_t b = 1024;                                            // alignment slack
   b += (size_t)2 * stages * kTileT * g.head_dim;              // K and V rings
-  b += (size_t)kConsumerWarps * g.group * g.head_dim * 4;     // sO
-  b += (size_t)2 * kConsumerWarps * 8 * 4;                    // sM, sL
-  b += (size_t)2 * stages * 8;                                // barriers
+  b += (size_t)2 * g.group * g.head_dim * 2;                  // query rows, double buffered
+  b += (size_t)2 * kConsumerWarps * g.group * (g.head_dim + 4) * 4;   // dumped warp states, double buffered
+  b += (size_t)2 * kConsumerWarps * 16 * 4;                   // their m, l
+  b += (size_t)(2 * stages + 8) * 8;                          // barriers
   b += 16;                                                    // flags
   b += (size_t)(2 * g.batch + 1) * 4;                         // sLen, sCum
   return (b + 15) & ~(size_t)15;
@@ -662,3 +796,13 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
 }
 
 }  // namespace b200attn
+
+#ifdef B200ATTN_TRACE
+extern "C" int b200attn_debug_trace(unsigned long long* host_out, int n_ctas, int clear) {
+  if (clear) {
+    static unsigned long long zeros[4096 * 8];
+    return (int)cudaMemcpyToSymbol(b200attn::g_trace, zeros, sizeof(zeros));
+  }
+  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_trace, (size_t)n_ctas * 8 * sizeof(unsigned long long));
+}
+#endif
