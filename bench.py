@@ -192,7 +192,8 @@ class StepRunner:
         self.k_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
         self.v_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
         self.out = torch.empty_like(self.q)
-        self.full_out = torch.empty(world, N_LAYERS, 1, h_q, D, device=device, dtype=torch.bfloat16) if world > 1 else None
+        self.gatherer = importlib.import_module("qwen38-5080_b200.dist").HeadGather(self.out, world) if world > 1 else None
+        self.full_out = self.gatherer.full if world > 1 else None
         self.graph = None
 
     def launch_step(self):
@@ -202,7 +203,7 @@ class StepRunner:
 
     def gather(self):
         if self.world > 1:
-            self.dist.all_gather_into_tensor(self.full_out, self.out)
+            self.gatherer.gather(self.out)     # NCCL all-gather + one strided copy into [n, b, h_q, D]
 
     def capture(self):
         torch = self.torch
@@ -433,7 +434,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
-    ap.add_argument("--variant", choices=["auto", "mma", "simt"], default="auto", help="attention kernel variant")
+    ap.add_argument("--variant", choices=["auto", "mma", "mma_fp8", "simt"], default="auto", help="attention kernel variant")
     ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

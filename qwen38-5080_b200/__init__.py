@@ -1,5 +1,5 @@
 """B200-native FP8-KV decode attention (drop-in for the reference's decode attention path)."""
-from . import _lib, ops
+from . import _lib, dist, ops
 from ._lib import B200AttnError, B200AttnShape
 from .cache import FP8StaticCache
 from .ops import (Workspace, append_decode, calibrate_scales, decode_attention, dequant_prefix, kv_quant_append,
@@ -7,4 +7,4 @@ from .ops import (Workspace, append_decode, calibrate_scales, decode_attention, 
 
 __all__ = ["B200AttnError", "B200AttnShape", "FP8StaticCache", "Workspace", "append_decode", "calibrate_scales",
            "decode_attention", "dequant_prefix", "kv_quant_append", "make_shape", "pick_splits", "workspace_bytes",
-           "ops", "_lib"]
+           "ops", "dist", "_lib"]

@@ -42,7 +42,7 @@ int resolve_variant(int variant, const Geometry& g) {
   const bool mma_ok = g.scale_mode == B200ATTN_SCALE_PER_HEAD && g.batch <= 2048;
   if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
   if (variant == B200ATTN_VARIANT_SIMT) return variant;
-  if (variant == B200ATTN_VARIANT_MMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
+  if (variant == B200ATTN_VARIANT_MMA || variant == B200ATTN_VARIANT_MMA_FP8) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
   return B200ATTN_ERR_VARIANT;
 }
 
@@ -145,7 +145,7 @@ int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cac
   DecodeArgs a{q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                num_splits, workspace, workspace_bytes, out, status};
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
-                                             : launch_decode_mma(g, a, (cudaStream_t)stream);
+                                             : launch_decode_mma(g, a, v == B200ATTN_VARIANT_MMA_FP8, (cudaStream_t)stream);
   return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
 }
 

@@ -167,6 +167,24 @@ __device__ unsigned long long g_trace[4096 * 8];
 #define TRACE_LANE0(slot) do { } while (0)
 #endif
 
+// D(16x8,f32) += A(16x32,e4m3,row) * B(32x8,e4m3,col)
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Two floats -> two e4m3 bytes in a 16-bit register: `lo` in the low byte, `hi` in the high byte.
+__device__ __forceinline__ uint32_t pack_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return (uint32_t)r;
+}
+// Leading part of x that an e4m3 value holds exactly (sign, exponent, top three mantissa bits).
+__device__ __forceinline__ float e4m3_head(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFF00000u); }
+
 // ---------------------------------------------------------------------------------------------
 // the stream-K walk: linear tile index -> (layer, sequence, kv head, tile)
 // ---------------------------------------------------------------------------------------------
@@ -221,7 +239,12 @@ __device__ __forceinline__ int owner_of(long long x, long long total, int n) {
 // consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
 __device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
 
-template <int D>
+// FP8 = false: K, V widened to f16 in registers, probabilities in f16 (mma.m16n8k16.f16).
+// FP8 = true : K, V bytes feed mma.m16n8k32.e4m3 directly, no conversion at all; the query and
+//              the probabilities are each split into two e4m3 terms (head + remainder, 8
+//              significant bits together, the precision class of the reference's bf16 P) that sit
+//              in the two halves of the k dimension against a duplicated K / V fragment.
+template <int D, bool FP8>
 __global__ void __launch_bounds__(kThreads)
 attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                         const MmaParams p) {
@@ -523,17 +546,29 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
         int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF);
-        ex = ex < 1 ? 127 : (ex > 253 ? 253 : ex);   // zero / denormal / inf / NaN heads: no rescale worth doing
-        const float down = __uint_as_float((uint32_t)(254 - ex) << 23);   // 2^(127-ex)
-        const float up = __uint_as_float((uint32_t)ex << 23);             // 2^(ex-127)
+        // zero / denormal / inf / NaN heads: no rescale worth doing
+        ex = ex < 1 ? 127 : (ex < 8 ? 8 : (ex > 253 ? 253 : ex));
+        // f16 path: largest |q| in [1, 2); e4m3 path: in [128, 256) (e4m3 tops out at 448)
+        constexpr int kUp = FP8 ? 7 : 0;
+        const float down = __uint_as_float((uint32_t)(254 + kUp - ex) << 23);   // 2^(127+kUp-ex)
+        const float up = __uint_as_float((uint32_t)(ex - kUp) << 23);           // 2^(ex-127-kUp)
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf)
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
-            __half2 b0 = __floats2half2_rn(qv[hf][4 * w] * down, qv[hf][4 * w + 1] * down);
-            __half2 b1 = __floats2half2_rn(qv[hf][4 * w + 2] * down, qv[hf][4 * w + 3] * down);
-            qf[hf * 8 + w][0] = *reinterpret_cast<uint32_t*>(&b0);
-            qf[hf * 8 + w][1] = *reinterpret_cast<uint32_t*>(&b1);
+            const float x0 = qv[hf][4 * w] * down, x1 = qv[hf][4 * w + 1] * down;
+            const float x2 = qv[hf][4 * w + 2] * down, x3 = qv[hf][4 * w + 3] * down;
+            if constexpr (FP8) {
+              // q = head + remainder, both e4m3: [0] = heads of the four dims, [1] = remainders
+              const float h0 = e4m3_head(x0), h1 = e4m3_head(x1), h2 = e4m3_head(x2), h3 = e4m3_head(x3);
+              qf[hf * 8 + w][0] = pack_e4m3x2(h0, h1) | (pack_e4m3x2(h2, h3) << 16);
+              qf[hf * 8 + w][1] = pack_e4m3x2(x0 - h0, x1 - h1) | (pack_e4m3x2(x2 - h2, x3 - h3) << 16);
+            } else {
+              __half2 b0 = __floats2half2_rn(x0, x1);
+              __half2 b1 = __floats2half2_rn(x2, x3);
+              qf[hf * 8 + w][0] = *reinterpret_cast<uint32_t*>(&b0);
+              qf[hf * 8 + w][1] = *reinterpret_cast<uint32_t*>(&b1);
+            }
           }
         const float ks = p.k_scale[c.layer * g.h_kv + c.h] * p.score_scale;
         const float mult = up * ks;                       // held by the lanes of head gq
@@ -553,7 +588,11 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         if (it == 0) TRACE(2);
 #endif
         const int tok0 = (c.tile + ti) * kTileT + warp * 16;   // first token of this warp's 16
+#ifdef B200ATTN_NOCOMPUTE
+        if (false) {
+#else
         if (ok && tok0 < c.len_b) {
+#endif
           // ---------------- S^T[16 tokens x 8 heads] = K q^T ----------------
           float sacc[4] = {0.f, 0.f, 0.f, 0.f}, sacc2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains
           const uint32_t kt = sK_addr + s * TILE_BYTES;
@@ -569,10 +608,16 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 #pragma unroll
               for (int wi = 0; wi < 4; ++wi) {
                 const int ks = hf * 8 + ch * 4 + wi;
-                if (wi & 1)
-                  mma_f16(sacc2, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
-                else
-                  mma_f16(sacc, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
+                if constexpr (FP8) {
+                  // k = [4 dims | the same 4 dims] against [q head | q remainder]
+                  if (wi & 1) mma_e4m3(sacc2, wl[wi], wh[wi], wl[wi], wh[wi], qf[ks][0], qf[ks][1]);
+                  else mma_e4m3(sacc, wl[wi], wh[wi], wl[wi], wh[wi], qf[ks][0], qf[ks][1]);
+                } else {
+                  if (wi & 1)
+                    mma_f16(sacc2, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
+                  else
+                    mma_f16(sacc, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
+                }
               }
             }
           }
@@ -599,9 +644,20 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             for (int j = 0; j < KSTEPS; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
           }
           // P^T fragments (B operand of O^T += V^T P^T): transpose [token x head] -> [head x token]
-          __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
-          const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pa));
-          const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pb));
+          uint32_t pb0, pb1;
+          if constexpr (FP8) {
+            // p * 2^8 = head + remainder in e4m3.  One 16-bit element = (token gq, token gq+8) of a
+            // head; after the transpose a thread holds tokens (2tq, 2tq+8, 2tq+1, 2tq+9) of head gq,
+            // the token order the V fragments below use.  pb0 = heads, pb1 = remainders.
+            const float q0 = p0 * 256.f, q1 = p1 * 256.f, q2 = p2 * 256.f, q3 = p3 * 256.f;
+            const float h0 = e4m3_head(q0), h1 = e4m3_head(q1), h2 = e4m3_head(q2), h3 = e4m3_head(q3);
+            pb0 = movmatrix_trans(pack_e4m3x2(h0, h2) | (pack_e4m3x2(h1, h3) << 16));
+            pb1 = movmatrix_trans(pack_e4m3x2(q0 - h0, q2 - h2) | (pack_e4m3x2(q1 - h1, q3 - h3) << 16));
+          } else {
+            __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
+            pb0 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pa));
+            pb1 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pb));
+          }
 
           // ---------------- O^T[D dims x 8 heads] += V^T P^T ----------------
           const uint32_t vt = sV_addr + s * TILE_BYTES;
@@ -626,10 +682,21 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
-              const uint32_t x01 = prmt(wa[wi], wb[wi], 0x5140), x23 = prmt(wa[wi], wb[wi], 0x7362);
-              const uint32_t y01 = prmt(wc[wi], wd[wi], 0x5140), y23 = prmt(wc[wi], wd[wi], 0x7362);
-              mma_f16(o[hf * 8 + 2 * wi], cvt_lo(x01), cvt_hi(x01), cvt_lo(y01), cvt_hi(y01), pb0, pb1);
-              mma_f16(o[hf * 8 + 2 * wi + 1], cvt_lo(x23), cvt_hi(x23), cvt_lo(y23), cvt_hi(y23), pb0, pb1);
+              if constexpr (FP8) {
+                // 4x4 byte transpose: one register per dim holding tokens (2tq, 2tq+8, 2tq+1, 2tq+9)
+                const uint32_t ac01 = prmt(wa[wi], wc[wi], 0x5140), ac23 = prmt(wa[wi], wc[wi], 0x7362);
+                const uint32_t bd01 = prmt(wb[wi], wd[wi], 0x5140), bd23 = prmt(wb[wi], wd[wi], 0x7362);
+                const uint32_t d0 = prmt(ac01, bd01, 0x5410), d1 = prmt(ac01, bd01, 0x7632);
+                const uint32_t d2 = prmt(ac23, bd23, 0x5410), d3 = prmt(ac23, bd23, 0x7632);
+                // k = [16 tokens | the same 16 tokens] against [p head | p remainder]
+                mma_e4m3(o[hf * 8 + 2 * wi], d0, d1, d0, d1, pb0, pb1);
+                mma_e4m3(o[hf * 8 + 2 * wi + 1], d2, d3, d2, d3, pb0, pb1);
+              } else {
+                const uint32_t x01 = prmt(wa[wi], wb[wi], 0x5140), x23 = prmt(wa[wi], wb[wi], 0x7362);
+                const uint32_t y01 = prmt(wc[wi], wd[wi], 0x5140), y23 = prmt(wc[wi], wd[wi], 0x7362);
+                mma_f16(o[hf * 8 + 2 * wi], cvt_lo(x01), cvt_hi(x01), cvt_lo(y01), cvt_hi(y01), pb0, pb1);
+                mma_f16(o[hf * 8 + 2 * wi + 1], cvt_lo(x23), cvt_hi(x23), cvt_lo(y23), cvt_hi(y23), pb0, pb1);
+              }
             }
           }
         }
@@ -661,8 +728,9 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         for (int j = 0; j < KSTEPS; ++j) {
           const int u = (j >> 3) * 64 + 8 * gq + (j & 7);
           const uint32_t pos8 = 8u * (uint32_t)((u & ~7) | ((j & 7) ^ gq));
-          if (h0 < G) sts64(dbase + h0 * DP * 4 + pos8, o[j][0], o[j][2]);
-          if (h1 < G) sts64(dbase + h1 * DP * 4 + pos8, o[j][1], o[j][3]);
+          constexpr float kOut = FP8 ? 1.f / 256.f : 1.f;   // undo the 2^8 carried by the e4m3 probabilities
+          if (h0 < G) sts64(dbase + h0 * DP * 4 + pos8, o[j][0] * kOut, o[j][2] * kOut);
+          if (h1 < G) sts64(dbase + h1 * DP * 4 + pos8, o[j][1] * kOut, o[j][3] * kOut);
         }
       }
       __syncwarp();
@@ -677,6 +745,9 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   }
   __syncthreads();
   TRACE(6);
+#ifdef B200ATTN_TRACE
+  if (tid == 0) { unsigned smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid)); g_trace[blockIdx.x * 8 + 4] = smid; }
+#endif
   if (sFlags[0] && tid == kConsumerThreads) {
     // A wait gave up.  Copies already issued still land in this CTA's shared memory: wait for
     // them (bounded) so the CTA does not retire underneath them.
@@ -761,7 +832,7 @@ int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
   return num_sms * per_sm;
 }
 
-cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream) {
+cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, bool fp8, cudaStream_t stream) {
   if (g.scale_mode != B200ATTN_SCALE_PER_HEAD || g.batch > kMaxBatchMma) return cudaErrorNotSupported;
   CUtensorMap kmap, vmap;
   if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride) || !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride))
@@ -782,20 +853,18 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.status = a.status;
   p.stages = stages_for(g);
   const size_t smem = smem_bytes_for(g, p.stages);
-  cudaError_t e;
-  if (g.head_dim == 128) {
-    e = cudaFuncSetAttribute(attn_streamk_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto launch = [&](auto kernel) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attn_streamk_mma_kernel<128><<<n, kThreads, smem, stream>>>(kmap, vmap, p);
-  } else {
-    e = cudaFuncSetAttribute(attn_streamk_mma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    attn_streamk_mma_kernel<256><<<n, kThreads, smem, stream>>>(kmap, vmap, p);
-  }
-  return cudaGetLastError();
+    kernel<<<n, kThreads, smem, stream>>>(kmap, vmap, p);
+    return cudaGetLastError();
+  };
+  if (g.head_dim == 128) return fp8 ? launch(attn_streamk_mma_kernel<128, true>) : launch(attn_streamk_mma_kernel<128, false>);
+  return fp8 ? launch(attn_streamk_mma_kernel<256, true>) : launch(attn_streamk_mma_kernel<256, false>);
 }
 
 }  // namespace b200attn
+
 
 #ifdef B200ATTN_TRACE
 extern "C" int b200attn_debug_trace(unsigned long long* host_out, int n_ctas, int clear) {

@@ -1,0 +1,79 @@
+"""Multi-GPU partitioning of the decode-attention path (one process per GPU, torch.distributed).
+
+The reference is single-GPU; these shardings follow the benchmark's configurations:
+
+* KV-head tensor parallel for one long sequence: rank r owns KV heads
+  [r*h_kv/P, (r+1)*h_kv/P) and the query heads of those groups, for every layer.  Attention per
+  KV head is independent (softmax is per query head), so ranks never exchange partials; the one
+  exchange per step is an all-gather of the bf16 output.
+* sequence sharding for batched decode: whole sequences per rank, balanced on total depth; no
+  collective on the data path.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def head_shard(h_q: int, h_kv: int, world: int, rank: int) -> tuple[slice, slice]:
+    """(kv-head slice, query-head slice) owned by `rank`."""
+    if h_kv % world or h_q % h_kv:
+        raise ValueError(f"cannot shard {h_kv} KV heads over {world} ranks")
+    per = h_kv // world
+    group = h_q // h_kv
+    return slice(rank * per, (rank + 1) * per), slice(rank * per * group, (rank + 1) * per * group)
+
+
+def assign_sequences(depths: list[int], world: int) -> list[list[int]]:
+    """Greedy longest-first assignment of sequence indices to ranks, balancing total depth
+    (ties broken by rank index, so every rank computes the same plan)."""
+    load = [0] * world
+    plan: list[list[int]] = [[] for _ in range(world)]
+    for idx in sorted(range(len(depths)), key=lambda i: (-depths[i], i)):
+        r = min(range(world), key=lambda j: (load[j], len(plan[j]), j))
+        plan[r].append(idx)
+        load[r] += depths[idx]
+    for p in plan:
+        p.sort()
+    return plan
+
+
+class HeadGather:
+    """All-gather of per-rank outputs [n_layers, batch, h_q/P, D] into [n_layers, batch, h_q, D].
+
+    Buffers are allocated once; `gather()` issues one collective on the current stream plus one
+    strided copy that puts every rank's heads in place (query head order = rank order).
+    """
+
+    def __init__(self, local_like: torch.Tensor, world: int, group=None):
+        import torch.distributed as dist
+        self.dist, self.world, self.group = dist, world, group
+        n, b, hq, d = local_like.shape
+        self.staging = torch.empty(world, n, b, hq, d, dtype=local_like.dtype, device=local_like.device)
+        self.full = torch.empty(n, b, world * hq, d, dtype=local_like.dtype, device=local_like.device)
+
+    def gather(self, local: torch.Tensor) -> torch.Tensor:
+        n, b, hq, d = local.shape
+        self.dist.all_gather_into_tensor(self.staging.view(self.world * n, b, hq, d), local.contiguous(), group=self.group)
+        self.full.view(n, b, self.world, hq, d).copy_(self.staging.permute(1, 2, 0, 3, 4))
+        return self.full
+
+
+def gather_sequences(local: torch.Tensor, plan: list[list[int]], batch: int, group=None) -> torch.Tensor:
+    """Off-clock gather for parity checks of the sequence-sharded path: every rank contributes
+    [n_layers, len(plan[rank]), h_q, D]; returns [n_layers, batch, h_q, D] in original order."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    n, _, hq, d = local.shape
+    width = max(len(p) for p in plan)
+    padded = torch.zeros(n, width, hq, d, dtype=local.dtype, device=local.device)
+    padded[:, : local.shape[1]] = local
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded, group=group)
+    out = torch.empty(n, batch, hq, d, dtype=local.dtype, device=local.device)
+    for r, idxs in enumerate(plan):
+        for j, b in enumerate(idxs):
+            out[:, b] = parts[r][:, j]
+    return out
+
+
+__all__ = ["head_shard", "assign_sequences", "HeadGather", "gather_sequences"]
