@@ -434,7 +434,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
-    ap.add_argument("--variant", choices=["auto", "mma", "mma_fp8", "simt"], default="auto", help="attention kernel variant")
+    ap.add_argument("--variant", choices=["auto", "mma", "umma", "simt"], default="auto", help="attention kernel variant")
     ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

@@ -49,7 +49,8 @@ extern "C" {
 #define B200ATTN_VARIANT_AUTO     0   /* the library's default (the fastest validated variant) */
 #define B200ATTN_VARIANT_SIMT     1   /* CUDA-core split-K partial kernel + separate combine kernel */
 #define B200ATTN_VARIANT_MMA      2   /* TMA/mbarrier staged, tensor-core (mma.sync f16) stream-K kernel with fused combine */
-#define B200ATTN_VARIANT_MMA_FP8  3   /* the same kernel with mma.sync e4m3 operands: K/V bytes feed the tensor cores unconverted */
+#define B200ATTN_VARIANT_UMMA     3   /* the same stream-K kernel with S = K q^T on tcgen05.mma kind::f8f6f4: K tiles feed the
+                                         tensor cores from shared memory unconverted, scores in tensor memory */
 
 /* scale granularity of the FP8 cache */
 #define B200ATTN_SCALE_PER_HEAD   0   /* fp32 scale per (layer, kv_head): [n_layers][h_kv] */

@@ -18,8 +18,8 @@ c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes
 OK = 0
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_SPLITS, ERR_CUDA, ERR_CAPACITY, ERR_VARIANT = range(-1, -9, -1)
 STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEGATIVE = 1, 2, 4, 8
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_MMA_FP8 = 0, 1, 2, 3
-VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "mma_fp8": VARIANT_MMA_FP8}
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA = 0, 1, 2, 3
+VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma": VARIANT_UMMA}
 SCALE_PER_HEAD, SCALE_PER_TOKEN = 0, 1
 
 

@@ -42,8 +42,14 @@ int resolve_variant(int variant, const Geometry& g) {
   const bool mma_ok = g.scale_mode == B200ATTN_SCALE_PER_HEAD && g.batch <= 2048;
   if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
   if (variant == B200ATTN_VARIANT_SIMT) return variant;
-  if (variant == B200ATTN_VARIANT_MMA || variant == B200ATTN_VARIANT_MMA_FP8) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
+  if (variant == B200ATTN_VARIANT_MMA || variant == B200ATTN_VARIANT_UMMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
   return B200ATTN_ERR_VARIANT;
+}
+
+int pick(const Geometry& g, int v, int max_seq_len, int num_sms) {
+  if (v == B200ATTN_VARIANT_SIMT) return simt_pick_splits(g, max_seq_len, num_sms);
+  if (v == B200ATTN_VARIANT_UMMA) return umma_pick_ctas(g, max_seq_len, num_sms);
+  return mma_pick_ctas(g, max_seq_len, num_sms);
 }
 
 }  // namespace
@@ -77,8 +83,7 @@ int b200attn_pick_splits(const B200AttnShape* shape, int max_seq_len, int num_sm
   if (num_sms < 1) num_sms = 148;
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
-  return v == B200ATTN_VARIANT_SIMT ? simt_pick_splits(g, max_seq_len, num_sms)
-                                    : mma_pick_ctas(g, max_seq_len, num_sms);
+  return pick(g, v, max_seq_len, num_sms);
 }
 
 int b200attn_workspace_bytes(const B200AttnShape* shape, int num_splits, int variant, size_t* bytes) {
@@ -133,7 +138,7 @@ int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cac
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
   if (num_splits == 0)
-    num_splits = v == B200ATTN_VARIANT_SIMT ? simt_pick_splits(g, g.capacity, 148) : mma_pick_ctas(g, g.capacity, 148);
+    num_splits = pick(g, v, g.capacity, 148);
   if (num_splits < 1 || num_splits > 65535) return B200ATTN_ERR_SPLITS;
   const size_t need = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(g, num_splits) : mma_workspace_bytes(g, num_splits);
   const bool needs_ws = !(v == B200ATTN_VARIANT_SIMT && num_splits == 1);
@@ -145,7 +150,8 @@ int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cac
   DecodeArgs a{q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                num_splits, workspace, workspace_bytes, out, status};
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
-                                             : launch_decode_mma(g, a, v == B200ATTN_VARIANT_MMA_FP8, (cudaStream_t)stream);
+                                             : v == B200ATTN_VARIANT_UMMA ? launch_decode_umma(g, a, (cudaStream_t)stream)
+                                             : launch_decode_mma(g, a, (cudaStream_t)stream);
   return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
 }
 
@@ -161,7 +167,7 @@ int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
   if (num_splits == 0)
-    num_splits = v == B200ATTN_VARIANT_SIMT ? simt_pick_splits(g, g.capacity, 148) : mma_pick_ctas(g, g.capacity, 148);
+    num_splits = pick(g, v, g.capacity, 148);
   if (num_splits < 1 || num_splits > 65535) return B200ATTN_ERR_SPLITS;
   const size_t need = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(g, num_splits) : mma_workspace_bytes(g, num_splits);
   if (!(v == B200ATTN_VARIANT_SIMT && num_splits == 1)) {

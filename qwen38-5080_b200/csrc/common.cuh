@@ -103,6 +103,10 @@ cudaError_t launch_decode_simt(const Geometry& g, const DecodeArgs& a, cudaStrea
 // MMA variant: TMA-staged, tensor-core stream-K kernel with fused combine.
 size_t mma_workspace_bytes(const Geometry& g, int num_ctas);
 int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
-cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, bool fp8, cudaStream_t stream);
+cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
+
+// UMMA variant: the same stream-K kernel with the score GEMM on tcgen05.mma (FP8 bytes from shared memory).
+int umma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
+cudaError_t launch_decode_umma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
 
 }  // namespace b200attn

@@ -28,223 +28,16 @@
 // (bench/micro/attn_length_effect.py:41-66, runner/model/static_cache.py:79-82) and follows the
 // split/combine structure of its fused kernel
 // (docs/journal/2026-10-23-phase2-r3-coordinator.md:137-141).
-#include <cuda.h>
-
-#include <mutex>
-
-#include "common.cuh"
+#include "streamk.cuh"
 
 namespace b200attn {
 
 namespace {
 
-constexpr int kTileT = 64;                 // tokens per tile
-constexpr int kConsumerWarps = 4;          // 16 tokens each
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kProducerWarp = kConsumerWarps;          // warp 4: TMA issue
-constexpr int kEpilogueWarp = kConsumerWarps + 1;      // warp 5: merge, output, fused combine
-constexpr int kThreads = kConsumerThreads + 64;
-constexpr int kMaxBatchMma = 2048;
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait
+constexpr int kTileT = 64;                 // tokens per tile (16 per consumer warp)
+constexpr int kThreads = kConsumerThreads + 64;   // + producer warp + epilogue warp
 
-struct MmaParams {
-  Geometry g;
-  const uint16_t* q;
-  const float* k_scale;
-  const float* v_scale;
-  const int* seq_len;
-  int seq_len_offset;
-  float score_scale;     // softmax_scale * log2(e)
-  float* ws_acc;         // [num_ctas][2][G][D]
-  float* ws_ml;          // [num_ctas][2][2][8]
-  int* tickets;          // [pairs]
-  uint16_t* out;
-  int* status;
-  int stages;
-};
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait.  Returns false (and raises the CTA's timeout flag) when the budget runs out or
-// when another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* timed_out, int* status) {
-  if (*timed_out) return false;
-#pragma unroll 1
-  for (int i = 0; i < 64; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
-#pragma unroll 1
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*timed_out) return false;
-    if (global_timer_ns() - t0 > kWaitBudgetNs) {
-      *timed_out = 1;
-      atomicOr(status, B200ATTN_STATUS_WAIT_TIMEOUT);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void sts64(uint32_t addr, float x, float y) {
-  asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(x), "f"(y) : "memory");
-}
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t cvt_lo(uint32_t w) { return e4m3x2_to_f16x2((uint16_t)(w & 0xFFFFu)); }
-__device__ __forceinline__ uint32_t cvt_hi(uint32_t w) { return e4m3x2_to_f16x2((uint16_t)(w >> 16)); }
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-  return d;
-}
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
-  uint32_t d;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
-  return d;
-}
-// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-#ifdef B200ATTN_TRACE
-// Development-only timeline: per CTA, globaltimer stamps of (0) kernel entry, (1) prologue done,
-// (2) first tile landed, (3) first segment's tiles consumed, (4) first segment's state dumped,
-// (5) last tile consumed, (6) exit, (7) epilogue warp done.
-__device__ unsigned long long g_trace[4096 * 8];
-#define TRACE(slot) do { if (tid == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
-#define TRACE_LANE0(slot) do { if (lane == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#define TRACE_LANE0(slot) do { } while (0)
-#endif
-
-// D(16x8,f32) += A(16x32,e4m3,row) * B(32x8,e4m3,col)
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Two floats -> two e4m3 bytes in a 16-bit register: `lo` in the low byte, `hi` in the high byte.
-__device__ __forceinline__ uint32_t pack_e4m3x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return (uint32_t)r;
-}
-// Leading part of x that an e4m3 value holds exactly (sign, exponent, top three mantissa bits).
-__device__ __forceinline__ float e4m3_head(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFF00000u); }
-
-// ---------------------------------------------------------------------------------------------
-// the stream-K walk: linear tile index -> (layer, sequence, kv head, tile)
-// ---------------------------------------------------------------------------------------------
-struct Cursor {
-  int layer, b, h, tile;   // position of the current tile
-  int tiles_b;             // tiles of sequence b
-  int len_b;               // valid tokens of sequence b
-};
-
-// cum[b] = tiles of sequences < b; len[] clamped lengths.  Both in shared memory.
-__device__ __forceinline__ Cursor locate(long long idx, const int* cum, const int* len, int batch, int h_kv) {
-  const long long per_layer = (long long)cum[batch] * h_kv;
-  Cursor c;
-  c.layer = (int)(idx / per_layer);
-  const long long r = idx - (long long)c.layer * per_layer;
-  int lo = 0, hi = batch - 1;   // largest b with cum[b]*h_kv <= r (and tiles_b > 0 follows from r < cum[b+1]*h_kv)
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if ((long long)cum[mid] * h_kv <= r) lo = mid; else hi = mid - 1;
-  }
-  // sequences with zero tiles share cum[] with their successor: step forward to the one that owns r
-  while (cum[lo + 1] == cum[lo]) ++lo;
-  c.b = lo;
-  c.tiles_b = cum[lo + 1] - cum[lo];
-  c.len_b = len[lo];
-  const long long rr = r - (long long)cum[lo] * h_kv;
-  c.h = (int)(rr / c.tiles_b);
-  c.tile = (int)(rr - (long long)c.h * c.tiles_b);
-  return c;
-}
-
-// Move to the first tile of the next pair.
-__device__ __forceinline__ void next_pair(Cursor& c, const int* cum, const int* len, int batch, int h_kv) {
-  c.tile = 0;
-  if (++c.h < h_kv) return;
-  c.h = 0;
-  for (;;) {
-    if (++c.b == batch) { c.b = 0; ++c.layer; }
-    if (cum[c.b + 1] != cum[c.b]) break;   // at least one sequence is non-empty when total > 0
-  }
-  c.tiles_b = cum[c.b + 1] - cum[c.b];
-  c.len_b = len[c.b];
-}
-
-// CTA that owns linear tile x when `total` tiles are divided over n CTAs as [c*total/n, (c+1)*total/n).
-__device__ __forceinline__ int owner_of(long long x, long long total, int n) {
-  return (int)(((x + 1) * n - 1) / total);
-}
-
-
-// Position (in float2 units) of dim pair u inside a dumped head row.  The xor spreads the
-// consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
-__device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
-
-// FP8 = false: K, V widened to f16 in registers, probabilities in f16 (mma.m16n8k16.f16).
-// FP8 = true : K, V bytes feed mma.m16n8k32.e4m3 directly, no conversion at all; the query and
-//              the probabilities are each split into two e4m3 terms (head + remainder, 8
-//              significant bits together, the precision class of the reference's bf16 P) that sit
-//              in the two halves of the k dimension against a duplicated K / V fragment.
-template <int D, bool FP8>
+template <int D>
 __global__ void __launch_bounds__(kThreads)
 attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                         const MmaParams p) {
@@ -252,7 +45,6 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   constexpr int KSTEPS = D / 16;           // mma k-steps for QK^T == mma tiles for PV
   constexpr int TILE_BYTES = kTileT * D;   // one K (or V) tile
   constexpr int DP = D + 4;                // padded head row of a dumped state, in floats
-  constexpr int UR = D / 64;               // dim pairs per epilogue lane
   const Geometry& g = p.g;
   const int G = g.group;
   const int stages = p.stages;
@@ -368,131 +160,9 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       sFlags[1] = seg;  // query copies issued
     }
   } else if (warp == kEpilogueWarp) {
-    // ===================== epilogue warp: merge dumped states, write, fused combine =====================
-    if (has_work) {
-      Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
-      long long cur = r0;
-      int seg = 0;
-      while (cur < r1) {
-        const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
-        const long long seg_end = pair_end < r1 ? pair_end : r1;
-        const long long lb = (long long)c.layer * g.batch + c.b;
-        const long long pair = lb * g.h_kv + c.h;
-        const bool complete = cur == pair_start && seg_end == pair_end;
-        const float vs = p.v_scale[c.layer * g.h_kv + c.h];
-        const int db = seg & 1;
-        const bool ok = mbar_wait(dfull0 + 8u * db, (seg >> 1) & 1, timed_out, p.status);
-        const float* dump = sDump + db * kConsumerWarps * dump_warp_floats;
-        const float* ml = sML + db * kConsumerWarps * 16;
-        const int slot = cur == r0 ? 0 : 1;
-        float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
-        float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
-        uint16_t* orow = p.out + (lb * g.h_q + c.h * G) * D;
-        if (ok) {
-          for (int h = 0; h < G; ++h) {
-            float mw[kConsumerWarps], M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) { mw[w] = ml[w * 16 + h]; M = fmaxf(M, mw[w]); }
-            float ll = 0.f, ax[UR], ay[UR];
-#pragma unroll
-            for (int r = 0; r < UR; ++r) { ax[r] = 0.f; ay[r] = 0.f; }
-#pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) {
-              const float f = mw[w] == -INFINITY ? 0.f : ex2(mw[w] - M);
-              ll += ml[w * 16 + 8 + h] * f;
-#pragma unroll
-              for (int r = 0; r < UR; ++r) {
-                const float2 v = *reinterpret_cast<const float2*>(dump + w * dump_warp_floats + h * DP + 2 * dump_pos(lane + 32 * r));
-                ax[r] += v.x * f;
-                ay[r] += v.y * f;
-              }
-            }
-            if (complete) {
-              const float inv = ll > 0.f ? vs / ll : 0.f;
-#pragma unroll
-              for (int r = 0; r < UR; ++r) {
-                __nv_bfloat162 ob = __floats2bfloat162_rn(ax[r] * inv, ay[r] * inv);
-                *reinterpret_cast<uint32_t*>(orow + h * D + 2 * (lane + 32 * r)) = *reinterpret_cast<uint32_t*>(&ob);
-              }
-            } else {
-#pragma unroll
-              for (int r = 0; r < UR; ++r)
-                *reinterpret_cast<float2*>(pacc + h * D + 2 * (lane + 32 * r)) = make_float2(ax[r], ay[r]);
-              if (lane == 0) { pml[h] = M; pml[8 + h] = ll; }
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(dempty0 + 8u * db);   // the dump buffer may be overwritten
-        if (!complete && ok) {
-          // ---- fused combine: the last owner of the pair to arrive merges all partials ----
-          const int c_first = owner_of(pair_start, total, n_eff), c_last = owner_of(pair_end - 1, total, n_eff);
-          int last = 0;
-          if (lane == 0) {
-            __threadfence();
-            last = atomicAdd(p.tickets + pair, 1) == c_last - c_first;
-          }
-          last = __shfl_sync(0xffffffffu, last, 0);
-          if (last) {
-            __threadfence();
-            const int first_slot = (long long)c_first * total / n_eff < pair_start ? 1 : 0;
-            float M[kMaxGroup];
-#pragma unroll
-            for (int h = 0; h < kMaxGroup; ++h) M[h] = -INFINITY;
-#pragma unroll 4
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const float* cml = p.ws_ml + ((long long)cc * 2 + (cc == c_first ? first_slot : 0)) * 16;
-#pragma unroll
-              for (int h = 0; h < kMaxGroup; ++h)
-                if (h < G) M[h] = fmaxf(M[h], __ldcg(cml + h));
-            }
-            float ll[kMaxGroup], ax[kMaxGroup][UR], ay[kMaxGroup][UR];
-#pragma unroll
-            for (int h = 0; h < kMaxGroup; ++h) {
-              ll[h] = 0.f;
-#pragma unroll
-              for (int r = 0; r < UR; ++r) { ax[h][r] = 0.f; ay[h][r] = 0.f; }
-            }
-#pragma unroll 2
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const int sl = cc == c_first ? first_slot : 0;
-              const float* cml = p.ws_ml + ((long long)cc * 2 + sl) * 16;
-              const float* cacc = p.ws_acc + ((long long)cc * 2 + sl) * G * D;
-#pragma unroll
-              for (int h = 0; h < kMaxGroup; ++h) {
-                if (h < G) {
-                  const float mc = __ldcg(cml + h);
-                  const float f = mc == -INFINITY ? 0.f : ex2(mc - M[h]);
-                  ll[h] += __ldcg(cml + 8 + h) * f;
-#pragma unroll
-                  for (int r = 0; r < UR; ++r) {
-                    const float2 v = __ldcg(reinterpret_cast<const float2*>(cacc + h * D + 2 * (lane + 32 * r)));
-                    ax[h][r] += v.x * f;
-                    ay[h][r] += v.y * f;
-                  }
-                }
-              }
-            }
-#pragma unroll
-            for (int h = 0; h < kMaxGroup; ++h) {
-              if (h < G) {
-                const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
-#pragma unroll
-                for (int r = 0; r < UR; ++r) {
-                  __nv_bfloat162 ob = __floats2bfloat162_rn(ax[h][r] * inv, ay[h][r] * inv);
-                  *reinterpret_cast<uint32_t*>(orow + h * D + 2 * (lane + 32 * r)) = *reinterpret_cast<uint32_t*>(&ob);
-                }
-              }
-            }
-            if (lane == 0) p.tickets[pair] = 0;   // ready for the next launch
-          }
-        }
-        ++seg;
-        cur = seg_end;
-        if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
-      }
-      TRACE_LANE0(7);
-    }
+    if (has_work)
+      epilogue_warp<D, 2>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+    TRACE_LANE0(7);
   } else if (has_work) {
     // ================================ consumer warps ================================
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
@@ -547,28 +217,19 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
         int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF);
         // zero / denormal / inf / NaN heads: no rescale worth doing
-        ex = ex < 1 ? 127 : (ex < 8 ? 8 : (ex > 253 ? 253 : ex));
-        // f16 path: largest |q| in [1, 2); e4m3 path: in [128, 256) (e4m3 tops out at 448)
-        constexpr int kUp = FP8 ? 7 : 0;
-        const float down = __uint_as_float((uint32_t)(254 + kUp - ex) << 23);   // 2^(127+kUp-ex)
-        const float up = __uint_as_float((uint32_t)(ex - kUp) << 23);           // 2^(ex-127-kUp)
+        ex = ex < 1 ? 127 : (ex > 253 ? 253 : ex);
+        const float down = __uint_as_float((uint32_t)(254 - ex) << 23);   // 2^(127-ex)
+        const float up = __uint_as_float((uint32_t)ex << 23);             // 2^(ex-127)
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf)
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
             const float x0 = qv[hf][4 * w] * down, x1 = qv[hf][4 * w + 1] * down;
             const float x2 = qv[hf][4 * w + 2] * down, x3 = qv[hf][4 * w + 3] * down;
-            if constexpr (FP8) {
-              // q = head + remainder, both e4m3: [0] = heads of the four dims, [1] = remainders
-              const float h0 = e4m3_head(x0), h1 = e4m3_head(x1), h2 = e4m3_head(x2), h3 = e4m3_head(x3);
-              qf[hf * 8 + w][0] = pack_e4m3x2(h0, h1) | (pack_e4m3x2(h2, h3) << 16);
-              qf[hf * 8 + w][1] = pack_e4m3x2(x0 - h0, x1 - h1) | (pack_e4m3x2(x2 - h2, x3 - h3) << 16);
-            } else {
-              __half2 b0 = __floats2half2_rn(x0, x1);
-              __half2 b1 = __floats2half2_rn(x2, x3);
-              qf[hf * 8 + w][0] = *reinterpret_cast<uint32_t*>(&b0);
-              qf[hf * 8 + w][1] = *reinterpret_cast<uint32_t*>(&b1);
-            }
+            __half2 b0 = __floats2half2_rn(x0, x1);
+            __half2 b1 = __floats2half2_rn(x2, x3);
+            qf[hf * 8 + w][0] = *reinterpret_cast<uint32_t*>(&b0);
+            qf[hf * 8 + w][1] = *reinterpret_cast<uint32_t*>(&b1);
           }
         const float ks = p.k_scale[c.layer * g.h_kv + c.h] * p.score_scale;
         const float mult = up * ks;                       // held by the lanes of head gq
@@ -608,16 +269,10 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 #pragma unroll
               for (int wi = 0; wi < 4; ++wi) {
                 const int ks = hf * 8 + ch * 4 + wi;
-                if constexpr (FP8) {
-                  // k = [4 dims | the same 4 dims] against [q head | q remainder]
-                  if (wi & 1) mma_e4m3(sacc2, wl[wi], wh[wi], wl[wi], wh[wi], qf[ks][0], qf[ks][1]);
-                  else mma_e4m3(sacc, wl[wi], wh[wi], wl[wi], wh[wi], qf[ks][0], qf[ks][1]);
-                } else {
-                  if (wi & 1)
-                    mma_f16(sacc2, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
-                  else
-                    mma_f16(sacc, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
-                }
+                if (wi & 1)
+                  mma_f16(sacc2, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
+                else
+                  mma_f16(sacc, cvt_lo(wl[wi]), cvt_lo(wh[wi]), cvt_hi(wl[wi]), cvt_hi(wh[wi]), qf[ks][0], qf[ks][1]);
               }
             }
           }
@@ -644,20 +299,9 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             for (int j = 0; j < KSTEPS; ++j) { o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1; }
           }
           // P^T fragments (B operand of O^T += V^T P^T): transpose [token x head] -> [head x token]
-          uint32_t pb0, pb1;
-          if constexpr (FP8) {
-            // p * 2^8 = head + remainder in e4m3.  One 16-bit element = (token gq, token gq+8) of a
-            // head; after the transpose a thread holds tokens (2tq, 2tq+8, 2tq+1, 2tq+9) of head gq,
-            // the token order the V fragments below use.  pb0 = heads, pb1 = remainders.
-            const float q0 = p0 * 256.f, q1 = p1 * 256.f, q2 = p2 * 256.f, q3 = p3 * 256.f;
-            const float h0 = e4m3_head(q0), h1 = e4m3_head(q1), h2 = e4m3_head(q2), h3 = e4m3_head(q3);
-            pb0 = movmatrix_trans(pack_e4m3x2(h0, h2) | (pack_e4m3x2(h1, h3) << 16));
-            pb1 = movmatrix_trans(pack_e4m3x2(q0 - h0, q2 - h2) | (pack_e4m3x2(q1 - h1, q3 - h3) << 16));
-          } else {
-            __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
-            pb0 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pa));
-            pb1 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pb));
-          }
+          __half2 pa = __floats2half2_rn(p0, p1), pb = __floats2half2_rn(p2, p3);
+          const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pa));
+          const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<uint32_t*>(&pb));
 
           // ---------------- O^T[D dims x 8 heads] += V^T P^T ----------------
           const uint32_t vt = sV_addr + s * TILE_BYTES;
@@ -682,21 +326,10 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
             const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
-              if constexpr (FP8) {
-                // 4x4 byte transpose: one register per dim holding tokens (2tq, 2tq+8, 2tq+1, 2tq+9)
-                const uint32_t ac01 = prmt(wa[wi], wc[wi], 0x5140), ac23 = prmt(wa[wi], wc[wi], 0x7362);
-                const uint32_t bd01 = prmt(wb[wi], wd[wi], 0x5140), bd23 = prmt(wb[wi], wd[wi], 0x7362);
-                const uint32_t d0 = prmt(ac01, bd01, 0x5410), d1 = prmt(ac01, bd01, 0x7632);
-                const uint32_t d2 = prmt(ac23, bd23, 0x5410), d3 = prmt(ac23, bd23, 0x7632);
-                // k = [16 tokens | the same 16 tokens] against [p head | p remainder]
-                mma_e4m3(o[hf * 8 + 2 * wi], d0, d1, d0, d1, pb0, pb1);
-                mma_e4m3(o[hf * 8 + 2 * wi + 1], d2, d3, d2, d3, pb0, pb1);
-              } else {
-                const uint32_t x01 = prmt(wa[wi], wb[wi], 0x5140), x23 = prmt(wa[wi], wb[wi], 0x7362);
-                const uint32_t y01 = prmt(wc[wi], wd[wi], 0x5140), y23 = prmt(wc[wi], wd[wi], 0x7362);
-                mma_f16(o[hf * 8 + 2 * wi], cvt_lo(x01), cvt_hi(x01), cvt_lo(y01), cvt_hi(y01), pb0, pb1);
-                mma_f16(o[hf * 8 + 2 * wi + 1], cvt_lo(x23), cvt_hi(x23), cvt_lo(y23), cvt_hi(y23), pb0, pb1);
-              }
+              const uint32_t x01 = prmt(wa[wi], wb[wi], 0x5140), x23 = prmt(wa[wi], wb[wi], 0x7362);
+              const uint32_t y01 = prmt(wc[wi], wd[wi], 0x5140), y23 = prmt(wc[wi], wd[wi], 0x7362);
+              mma_f16(o[hf * 8 + 2 * wi], cvt_lo(x01), cvt_hi(x01), cvt_lo(y01), cvt_hi(y01), pb0, pb1);
+              mma_f16(o[hf * 8 + 2 * wi + 1], cvt_lo(x23), cvt_hi(x23), cvt_lo(y23), cvt_hi(y23), pb0, pb1);
             }
           }
         }
@@ -728,9 +361,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         for (int j = 0; j < KSTEPS; ++j) {
           const int u = (j >> 3) * 64 + 8 * gq + (j & 7);
           const uint32_t pos8 = 8u * (uint32_t)((u & ~7) | ((j & 7) ^ gq));
-          constexpr float kOut = FP8 ? 1.f / 256.f : 1.f;   // undo the 2^8 carried by the e4m3 probabilities
-          if (h0 < G) sts64(dbase + h0 * DP * 4 + pos8, o[j][0] * kOut, o[j][2] * kOut);
-          if (h1 < G) sts64(dbase + h1 * DP * 4 + pos8, o[j][1] * kOut, o[j][3] * kOut);
+          if (h0 < G) sts64(dbase + h0 * DP * 4 + pos8, o[j][0], o[j][2]);
+          if (h1 < G) sts64(dbase + h1 * DP * 4 + pos8, o[j][1], o[j][3]);
         }
       }
       __syncwarp();
@@ -766,39 +398,6 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   }
 }
 
-// ---------------------------------------------------------------------------------------------
-// host side
-// ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
-  return fn;
-}
-
-// u8 view [n_layers][rows = batch*h_kv*capacity][D], box = 128 bytes x kTileT rows, 128-byte swizzle.
-bool encode_cache_map(CUtensorMap* map, const void* base, const Geometry& g, long long layer_stride) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)g.head_dim, (cuuint64_t)g.batch * g.h_kv * g.capacity, (cuuint64_t)g.n_layers};
-  const cuuint64_t strides[2] = {(cuuint64_t)g.head_dim, (cuuint64_t)layer_stride};
-  const cuuint32_t box[3] = {128, (cuuint32_t)kTileT, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 int stages_for(const Geometry& g) { return g.head_dim == 128 ? 5 : 3; }
 
 size_t smem_bytes_for(const Geometry& g, int stages) {
@@ -832,10 +431,10 @@ int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
   return num_sms * per_sm;
 }
 
-cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, bool fp8, cudaStream_t stream) {
+cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream) {
   if (g.scale_mode != B200ATTN_SCALE_PER_HEAD || g.batch > kMaxBatchMma) return cudaErrorNotSupported;
   CUtensorMap kmap, vmap;
-  if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride) || !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride))
+  if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride, kTileT) || !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride, kTileT))
     return cudaErrorInvalidValue;
   MmaParams p;
   p.g = g;
@@ -859,8 +458,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, bool fp8, 
     kernel<<<n, kThreads, smem, stream>>>(kmap, vmap, p);
     return cudaGetLastError();
   };
-  if (g.head_dim == 128) return fp8 ? launch(attn_streamk_mma_kernel<128, true>) : launch(attn_streamk_mma_kernel<128, false>);
-  return fp8 ? launch(attn_streamk_mma_kernel<256, true>) : launch(attn_streamk_mma_kernel<256, false>);
+  return g.head_dim == 128 ? launch(attn_streamk_mma_kernel<128>) : launch(attn_streamk_mma_kernel<256>);
 }
 
 }  // namespace b200attn

@@ -8,7 +8,7 @@ import torch
 from helpers import TOL_COSINE, TOL_MAX_ABS, assert_parity, build_case, run_decode
 
 pytestmark = pytest.mark.gpu
-VARIANTS = ["simt", "mma", "mma_fp8"]
+VARIANTS = ["simt", "mma", "umma"]
 
 
 def _golden_case(oracle, m, fill_byte=0):
@@ -103,7 +103,7 @@ def test_split_counts_agree(pkg, oracle, cuda_device):
                                        case["lens"], 1024)
     outs = []
     for variant, counts in (("simt", [1, 2, 3, 4, 7, 8, 16]), ("mma", [1, 2, 3, 16, 37, 148, 296, 500, 2000]),
-                            ("mma_fp8", [1, 5, 148, 296, 1000])):
+                            ("umma", [1, 5, 148, 296, 1000])):
         for n in counts:
             out, status = run_decode(pkg, case, cuda_device, variant, num_splits=n)
             assert status == 0
@@ -287,7 +287,7 @@ def test_full_size_properties(pkg, oracle, cuda_device):
         outs[variant] = pkg.decode_attention(q, kc, vc, ks, vs, seq, workspace=ws)
         torch.cuda.synchronize()
         assert ws.read_status() == 0
-    for variant in ("mma", "mma_fp8"):
+    for variant in ("mma", "umma"):
         m = oracle.error_metrics(outs[variant].cpu(), outs["simt"].cpu())
         assert m["max_abs"] <= 2.0 ** -7 and m["cosine"] >= 0.99999, (variant, m)
     for layer in (0, 63):
@@ -297,7 +297,7 @@ def test_full_size_properties(pkg, oracle, cuda_device):
     const = torch.arange(h_kv, device=cuda_device).view(1, 1, h_kv, 1, 1).expand_as(vc)
     vconst = (0x30 + const).to(torch.uint8).contiguous()            # e4m3 0x30.. = 0.5, 0.5625, ...
     want = (vconst[0, 0, :, 0, 0].cpu().view(torch.float8_e4m3fn).float() * (4.5 / 448)).repeat_interleave(5)
-    for variant in ("mma", "mma_fp8"):
+    for variant in ("mma", "umma"):
         ws = pkg.Workspace(shape, cuda_device, variant=variant)
         out = pkg.decode_attention(q, kc, vconst, ks, vs, seq, workspace=ws).cpu().float()
         assert (out - want.view(1, 1, h_q, 1)).abs().max().item() <= 2.0 ** -8 * want.max().item(), variant
