@@ -38,7 +38,7 @@ constexpr int kTileT = 64;                 // tokens per tile (16 per consumer w
 constexpr int kThreads = kConsumerThreads + 64;   // + producer warp + epilogue warp
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, D == 128 ? 3 : 1)
 attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                         const MmaParams p) {
   constexpr int DH = D / 128;              // 128-byte column blocks per row
@@ -398,7 +398,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   }
 }
 
-int stages_for(const Geometry& g) { return g.head_dim == 128 ? 5 : 3; }
+int stages_for(const Geometry& g) { return 3; }
 
 size_t smem_bytes_for(const Geometry& g, int stages) {
   size_t b = 1024;                                            // alignment slack
@@ -427,7 +427,7 @@ int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
   const size_t smem = smem_bytes_for(g, stages_for(g));
   int per_sm = (int)((227 * 1024) / (smem + 1024));   // + per-CTA reservation
   if (per_sm < 1) per_sm = 1;
-  if (per_sm > 2) per_sm = 2;
+  if (per_sm > 3) per_sm = 3;
   return num_sms * per_sm;
 }
 
