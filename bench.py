@@ -173,11 +173,13 @@ def workload_name(key: str, depth: int, cap: int) -> str:
 class StepRunner:
     """One workload resident on one GPU: cache, static step buffers, captured graph."""
 
-    def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto"):
+    def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto",
+                 num_splits=0):
         self.pkg, self.torch, self.device, self.depth, self.advance = pkg, torch, device, depth, advance
         self.h_q, self.h_kv, self.dist, self.world = h_q, h_kv, dist, world
         g = torch.Generator(device=device).manual_seed(seed)
-        self.cache = pkg.FP8StaticCache(N_LAYERS, 1, h_q, h_kv, D, cap, device=device, variant=variant)
+        self.cache = pkg.FP8StaticCache(N_LAYERS, 1, h_q, h_kv, D, cap, device=device, variant=variant,
+                                        num_splits=num_splits)
         prefix = depth if advance else depth - 1      # cfg2: slot depth-1 is rewritten by every step
         chunk = 8192
         scales_done = False
@@ -368,7 +370,7 @@ def run_ours(args) -> int:
         room = cap - depth - args.warmup - 4 if advance else 1 << 30   # the cache must not overflow
         steps = max(1, min(args.steps, room))
         runner = StepRunner(pkg, torch, device, depth, cap, advance, h_q, h_kv, seed=rank, dist=dist, world=world,
-                            variant=args.variant)
+                            variant=args.variant, num_splits=args.ctas)
         runner.capture()
         if world > 1:   # communicator warm-up outside the timed region
             runner.gather()
@@ -435,6 +437,7 @@ def main() -> int:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
     ap.add_argument("--variant", choices=["auto", "mma", "umma", "simt"], default="auto", help="attention kernel variant")
+    ap.add_argument("--ctas", type=int, default=0, help="override the split / CTA count (0 = library default)")
     ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

@@ -36,9 +36,12 @@ namespace {
 
 constexpr int kTileT = 64;                 // tokens per tile (16 per consumer warp)
 constexpr int kThreads = kConsumerThreads + 64;   // + producer warp + epilogue warp
+constexpr int kCtasPerSm = 3;                      // D = 128: the kernel is latency bound, three CTAs per SM hide it best
+                                                   // (measured: 2 CTAs x 5 stages 187 us, 3 x 3 176 us, 4 x 2 with spills 191 us at depth 8192)
+constexpr int kDumpBufs = 2;                       // dump buffers per CTA
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, D == 128 ? 3 : 1)
+__global__ void __launch_bounds__(kThreads, D == 128 ? kCtasPerSm : 1)
 attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                         const MmaParams p) {
   constexpr int DH = D / 128;              // 128-byte column blocks per row
@@ -61,8 +64,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   uint8_t* sV = sK + (size_t)stages * TILE_BYTES;
   uint8_t* sQ = sV + (size_t)stages * TILE_BYTES;                                     // [2][G*D] bf16
   float* sDump = reinterpret_cast<float*>(sQ + 2 * q_bytes);                          // [2][4][G][DP]
-  float* sML = sDump + 2 * kConsumerWarps * dump_warp_floats;                         // [2][4][16]: m[8], l[8]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + 2 * kConsumerWarps * 16);
+  float* sML = sDump + kDumpBufs * kConsumerWarps * dump_warp_floats;                         // [2][4][16]: m[8], l[8]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + kDumpBufs * kConsumerWarps * 16);
   int* sFlags = reinterpret_cast<int*>(bars + 2 * stages + 8);                        // [0] timed_out [2] any_empty [3] copies
   int* sLen = sFlags + 4;                                                             // [batch]
   int* sCum = sLen + g.batch;                                                         // [batch+1]
@@ -161,7 +164,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     }
   } else if (warp == kEpilogueWarp) {
     if (has_work)
-      epilogue_warp<D, 2>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+      epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
     TRACE_LANE0(7);
   } else if (has_work) {
     // ================================ consumer warps ================================
@@ -347,8 +350,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         l0 += __shfl_xor_sync(0xffffffffu, l0, off);
         l1 += __shfl_xor_sync(0xffffffffu, l1, off);
       }
-      const int db = seg & 1;
-      if (seg < 2 || mbar_wait(dempty0 + 8u * db, ((seg >> 1) - 1) & 1, timed_out, p.status)) {
+      const int db = seg % kDumpBufs;
+      if (seg < kDumpBufs || mbar_wait(dempty0 + 8u * db, ((seg / kDumpBufs) - 1) & 1, timed_out, p.status)) {
         float* ml = sML + (db * kConsumerWarps + warp) * 16;
         if (gq == 0) {
           ml[2 * tq] = m0; ml[2 * tq + 1] = m1;
@@ -404,8 +407,8 @@ size_t smem_bytes_for(const Geometry& g, int stages) {
   size_t b = 1024;                                            // alignment slack
   b += (size_t)2 * stages * kTileT * g.head_dim;              // K and V rings
   b += (size_t)2 * g.group * g.head_dim * 2;                  // query rows, double buffered
-  b += (size_t)2 * kConsumerWarps * g.group * (g.head_dim + 4) * 4;   // dumped warp states, double buffered
-  b += (size_t)2 * kConsumerWarps * 16 * 4;                   // their m, l
+  b += (size_t)kDumpBufs * kConsumerWarps * g.group * (g.head_dim + 4) * 4;   // dumped warp states
+  b += (size_t)kDumpBufs * kConsumerWarps * 16 * 4;                   // their m, l
   b += (size_t)(2 * stages + 8) * 8;                          // barriers
   b += 16;                                                    // flags
   b += (size_t)(2 * g.batch + 1) * 4;                         // sLen, sCum
@@ -427,7 +430,7 @@ int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
   const size_t smem = smem_bytes_for(g, stages_for(g));
   int per_sm = (int)((227 * 1024) / (smem + 1024));   // + per-CTA reservation
   if (per_sm < 1) per_sm = 1;
-  if (per_sm > 3) per_sm = 3;
+  if (per_sm > kCtasPerSm) per_sm = kCtasPerSm;
   return num_sms * per_sm;
 }
 

@@ -278,12 +278,16 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
       const int c_first = owner_of(pair_start, total, n_eff), c_last = owner_of(pair_end - 1, total, n_eff);
       int last = 0;
       if (lane == 0) {
-        __threadfence();
-        last = atomicAdd(p.tickets + pair, 1) == c_last - c_first;
+        // release: the warp's partial (ordered before this by __syncwarp) is visible to whoever
+        // reads the ticket after us; acquire: if we are last, the other owners' partials are
+        // visible to the loads below (passed on to the other lanes by the shuffle).
+        int ticket;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.tickets + pair) : "memory");
+        last = ticket == c_last - c_first;
       }
       last = __shfl_sync(0xffffffffu, last, 0);
+      __syncwarp();   // orders lane 0's acquire before the other lanes' loads
       if (last) {
-        __threadfence();
         const int first_slot = (long long)c_first * total / n_eff < pair_start ? 1 : 0;
         float M[kMaxGroup];
 #pragma unroll
