@@ -38,6 +38,7 @@ extern "C" {
 #define B200ATTN_ERR_CUDA          -6   /* a CUDA runtime / driver call failed (see b200attn_last_cuda_error) */
 #define B200ATTN_ERR_CAPACITY      -7   /* host-known length exceeds capacity */
 #define B200ATTN_ERR_VARIANT       -8   /* unknown kernel variant */
+#define B200ATTN_ERR_TOO_LARGE     -9   /* request exceeds the fixed scratch of b200attn_decode_static */
 
 /* device status bits (OR-ed into *status) */
 #define B200ATTN_STATUS_POS_AT_CAPACITY  1  /* append skipped: seq_pos[b] >= capacity */
@@ -172,6 +173,33 @@ int b200attn_decode(const B200AttnShape* shape,
                     void* workspace, size_t workspace_bytes,
                     void* out_bf16,
                     int* status, void* stream);
+
+/*
+ * b200attn_decode without a caller workspace (no counterpart in the reference: its fused kernel
+ * takes its scratch from torch's allocator).  For hosts that may not allocate device memory where
+ * they call the library — memory owned and budgeted by a framework pool, or a step that cannot
+ * afford cudaMalloc's device synchronisation.  The split-K partials and tickets of the tensor-core
+ * stream-K kernel (B200ATTN_VARIANT_MMA) live in a fixed 4 MiB array inside the library image
+ * (b200attn_static_scratch_bytes()), held by every GPU that loads the library until exit.
+ *   - a request whose workspace would not fit returns B200ATTN_ERR_TOO_LARGE, nothing launched
+ *     (fits: 64 layers x bs 1 with the default CTA count; check b200attn_workspace_bytes);
+ *   - all calls on a GPU share the array: calls that overlap on the device race — serialise them;
+ *   - the first call on each device looks up the array's device address; make that first call
+ *     before any stream capture;
+ *   - nothing is allocated or freed, here or in any routine it calls.
+ * Arguments as b200attn_decode, minus variant / workspace.
+ */
+int b200attn_decode_static(const B200AttnShape* shape,
+                           const void* q_bf16,
+                           const void* k_cache_u8, const void* v_cache_u8,
+                           const float* k_scale, const float* v_scale,
+                           const int* seq_len, int seq_len_offset,
+                           float softmax_scale, int num_splits,
+                           void* out_bf16,
+                           int* status, void* stream);
+
+/* Size in bytes of the fixed scratch array behind b200attn_decode_static. */
+size_t b200attn_static_scratch_bytes(void);
 
 /*
  * Fused convenience for one decode step: A (append at seq_pos) then B+C attending

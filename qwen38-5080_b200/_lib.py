@@ -16,7 +16,7 @@ c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes
 
 # host-side error codes / status bits / variants (include/b200attn.h)
 OK = 0
-ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_SPLITS, ERR_CUDA, ERR_CAPACITY, ERR_VARIANT = range(-1, -9, -1)
+ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_SPLITS, ERR_CUDA, ERR_CAPACITY, ERR_VARIANT, ERR_TOO_LARGE = range(-1, -10, -1)
 STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEGATIVE = 1, 2, 4, 8
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA = 0, 1, 2, 3
 VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma": VARIANT_UMMA}
@@ -46,6 +46,9 @@ PROTOTYPES = {
     "b200attn_decode": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p,
                                 c_void_p]),
+    "b200attn_decode_static": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200attn_static_scratch_bytes": (c_size_t, []),
     "b200attn_append_decode": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                        c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),

@@ -1,0 +1,77 @@
+// Decode attention for callers that cannot hand the library a workspace.
+//
+// Some hosts of this library may not allocate device memory at the point where they call it: a
+// serving loop whose device memory is owned and budgeted by the framework's pool (an extra
+// cudaMalloc would bypass the accounting and can fail under fragmentation), or a latency-critical
+// step where cudaMalloc's implicit device synchronisation is not acceptable.  For them the
+// split-K partials and arrival tickets of the tensor-core stream-K kernel live in a fixed
+// array inside the library image instead of a caller-provided workspace.
+//
+// The array is per GPU (every device that loads the library holds kStaticScratchBytes until the
+// process exits) and shared by all calls on that GPU: two calls that overlap on the device (two
+// streams, two threads) would race on it — serialise them.  It keeps the previous call's
+// contents; the only part that must start at zero, the ticket area, is cleared on the caller's
+// stream by every call.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr size_t kStaticScratchBytes = 4u << 20;   // 4 MiB: 444 CTAs x 2 partials x (5 x 128 + 16) floats = 2.3 MiB + tickets
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_mu;
+void* g_scratch_ptr[kMaxDevices] = {};   // device address of g_static_scratch, per device
+
+// The array's name is only a host-side handle here: the device address has to be asked for, once
+// per device, with that device current.
+cudaError_t scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!g_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    if (!ptr) return cudaErrorInvalidSymbol;
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int b200attn_decode_static(const B200AttnShape* shape, const void* q, const void* k_cache,
+                                      const void* v_cache, const float* k_scale, const float* v_scale,
+                                      const int* seq_len, int seq_len_offset, float softmax_scale,
+                                      int num_splits, void* out, int* status, void* stream) {
+  // Size check first, with the public helpers, so that an oversized request fails before any CUDA call.
+  size_t need = 0;
+  if (num_splits == 0) {
+    num_splits = b200attn_pick_splits(shape, shape ? shape->capacity : 0, 148, B200ATTN_VARIANT_MMA);
+    if (num_splits < 0) return num_splits;
+  }
+  int rc = b200attn_workspace_bytes(shape, num_splits, B200ATTN_VARIANT_MMA, &need);
+  if (rc) return rc;
+  if (need > kStaticScratchBytes) return B200ATTN_ERR_TOO_LARGE;
+  if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !seq_len || !out || !status) return B200ATTN_ERR_NULL;
+
+  void* scratch = nullptr;
+  cudaError_t e = scratch_address(&scratch);   // first call on a device: looks the address up
+  if (e != cudaSuccess) return B200ATTN_ERR_CUDA;
+  // tickets sit at the end of the workspace layout: one int per (layer, sequence, kv head)
+  const size_t tickets = (size_t)shape->n_layers * shape->batch * shape->h_kv * sizeof(int);
+  const size_t ticket_off = (size_t)num_splits * 2 * ((size_t)(shape->h_q / shape->h_kv) * shape->head_dim + 16) * sizeof(float);
+  e = cudaMemsetAsync((char*)scratch + ticket_off, 0, tickets, (cudaStream_t)stream);
+  if (e != cudaSuccess) return B200ATTN_ERR_CUDA;
+  return b200attn_decode(shape, q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
+                         B200ATTN_VARIANT_MMA, num_splits, scratch, kStaticScratchBytes, out, status, stream);
+}
+
+extern "C" size_t b200attn_static_scratch_bytes(void) { return kStaticScratchBytes; }
