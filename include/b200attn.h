@@ -175,6 +175,24 @@ int b200attn_decode(const B200AttnShape* shape,
                     int* status, void* stream);
 
 /*
+ * b200attn_decode with the consumer-side fusion of the reference's attention block:
+ *     out = bf16( bf16(attention) * bf16(sigmoid(gate)) )
+ * i.e. `attn_output * sigmoid(gate)` with its two separate bf16 roundings
+ * (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150).  Tensor-core variants only.
+ *   gate : bf16 [n_layers][batch][h_q][head_dim]
+ */
+int b200attn_decode_gated(const B200AttnShape* shape,
+                          const void* q_bf16, const void* gate_bf16,
+                          const void* k_cache_u8, const void* v_cache_u8,
+                          const float* k_scale, const float* v_scale,
+                          const int* seq_len, int seq_len_offset,
+                          float softmax_scale,
+                          int variant, int num_splits,
+                          void* workspace, size_t workspace_bytes,
+                          void* out_bf16,
+                          int* status, void* stream);
+
+/*
  * b200attn_decode without a caller workspace (no counterpart in the reference: its fused kernel
  * takes its scratch from torch's allocator).  For hosts that may not allocate device memory where
  * they call the library — memory owned and budgeted by a framework pool, or a step that cannot

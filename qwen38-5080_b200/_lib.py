@@ -46,6 +46,9 @@ PROTOTYPES = {
     "b200attn_decode": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p,
                                 c_void_p]),
+    "b200attn_decode_gated": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p,
+                                      c_void_p, c_void_p]),
     "b200attn_decode_static": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "b200attn_static_scratch_bytes": (c_size_t, []),

@@ -127,10 +127,10 @@ int b200attn_kv_quant_append(const B200AttnShape* shape, const void* k_new, cons
                                        advance_pos, status, stream);
 }
 
-int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cache, const void* v_cache,
-                    const float* k_scale, const float* v_scale, const int* seq_len, int seq_len_offset,
-                    float softmax_scale, int variant, int num_splits, void* workspace,
-                    size_t workspace_bytes, void* out, int* status, void* stream) {
+static int decode_impl(const B200AttnShape* shape, const void* q, const void* gate, const void* k_cache,
+                       const void* v_cache, const float* k_scale, const float* v_scale, const int* seq_len,
+                       int seq_len_offset, float softmax_scale, int variant, int num_splits, void* workspace,
+                       size_t workspace_bytes, void* out, int* status, void* stream) {
   Geometry g;
   int rc = resolve(shape, &g);
   if (rc) return rc;
@@ -148,12 +148,30 @@ int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cac
     if (!aligned16(workspace)) return B200ATTN_ERR_ALIGN;
     if (workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
   }
+  if (gate && (v == B200ATTN_VARIANT_SIMT || !aligned16(gate))) return v == B200ATTN_VARIANT_SIMT ? B200ATTN_ERR_VARIANT : B200ATTN_ERR_ALIGN;
   DecodeArgs a{q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
-               num_splits, workspace, workspace_bytes, out, status};
+               num_splits, workspace, workspace_bytes, out, status, gate};
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
                                              : v == B200ATTN_VARIANT_UMMA ? launch_decode_umma(g, a, (cudaStream_t)stream)
                                              : launch_decode_mma(g, a, (cudaStream_t)stream);
   return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
+}
+
+int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cache, const void* v_cache,
+                    const float* k_scale, const float* v_scale, const int* seq_len, int seq_len_offset,
+                    float softmax_scale, int variant, int num_splits, void* workspace,
+                    size_t workspace_bytes, void* out, int* status, void* stream) {
+  return decode_impl(shape, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
+                     variant, num_splits, workspace, workspace_bytes, out, status, stream);
+}
+
+int b200attn_decode_gated(const B200AttnShape* shape, const void* q, const void* gate, const void* k_cache,
+                          const void* v_cache, const float* k_scale, const float* v_scale, const int* seq_len,
+                          int seq_len_offset, float softmax_scale, int variant, int num_splits, void* workspace,
+                          size_t workspace_bytes, void* out, int* status, void* stream) {
+  if (!gate) return B200ATTN_ERR_NULL;
+  return decode_impl(shape, q, gate, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
+                     variant, num_splits, workspace, workspace_bytes, out, status, stream);
 }
 
 int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void* k_new, const void* v_new,

@@ -93,6 +93,7 @@ struct DecodeArgs {
   size_t workspace_bytes;
   void* out;
   int* status;
+  const void* gate;   // optional (tensor-core variants only)
 };
 
 // SIMT variant: split-K partial kernel + combine kernel.

@@ -37,7 +37,10 @@ namespace {
 constexpr int kTileT = 64;                 // tokens per tile (16 per consumer warp)
 constexpr int kThreads = kConsumerThreads + 64;   // + producer warp + epilogue warp
 constexpr int kCtasPerSm = 3;                      // D = 128: the kernel is latency bound, three CTAs per SM hide it best
-                                                   // (measured: 2 CTAs x 5 stages 187 us, 3 x 3 176 us, 4 x 2 with spills 191 us at depth 8192)
+                                                   // (measured at depth 8192: 2 CTAs x 5 stages 187 us, 3 x 3 176 us, 4 x 2 with
+                                                   // spills 191 us).  Co-resident CTAs do not progress equally (the first resident
+                                                   // one ends ~10 % early); skewing the tile split per residency slot, or fusing the
+                                                   // three CTAs into one 576-thread CTA, was measured and did not help (182 us).
 constexpr int kDumpBufs = 2;                       // dump buffers per CTA
 
 template <int D>
@@ -452,6 +455,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.ws_ml = p.ws_acc + (size_t)n * 2 * g.group * g.head_dim;
   p.tickets = (int*)(p.ws_ml + (size_t)n * 2 * 16);
   p.out = (uint16_t*)a.out;
+  p.gate = (const uint16_t*)a.gate;
   p.status = a.status;
   p.stages = stages_for(g);
   const size_t smem = smem_bytes_for(g, p.stages);

@@ -548,6 +548,7 @@ cudaError_t launch_decode_umma(const Geometry& g, const DecodeArgs& a, cudaStrea
   p.ws_ml = p.ws_acc + (size_t)n * 2 * g.group * g.head_dim;
   p.tickets = (int*)(p.ws_ml + (size_t)n * 2 * 16);
   p.out = (uint16_t*)a.out;
+  p.gate = (const uint16_t*)a.gate;
   p.status = a.status;
   p.stages = vstages_for(g);
   const size_t smem = umma_smem_bytes(g, p.stages);

@@ -30,6 +30,7 @@ struct MmaParams {
   float* ws_ml;          // [num_ctas][2][2][8]
   int* tickets;          // [pairs]
   uint16_t* out;
+  const uint16_t* gate;  // optional bf16 [n_layers][batch][h_q][D]: out *= sigmoid(gate), see store_out
   int* status;
   int stages;
 };
@@ -201,6 +202,21 @@ __device__ __forceinline__ int owner_of(long long x, long long total, int n) {
 // consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
 __device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
 
+// Two adjacent outputs -> bf16.  With a gate, the consumer-side fusion of the reference's attention
+// block, attn_output * sigmoid(gate), with its two separate bf16 roundings
+// (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150): s = bf16(sigmoid(gate)), then
+// bf16(bf16(attn) * s).
+__device__ __forceinline__ void store_out(uint16_t* out, const uint16_t* gate, long long idx, float x, float y) {
+  __nv_bfloat162 ob = __floats2bfloat162_rn(x, y);
+  if (gate) {
+    const uint32_t gw = *reinterpret_cast<const uint32_t*>(gate + idx);
+    const float g0 = bf16_bits_to_float(gw & 0xFFFFu), g1 = bf16_bits_to_float(gw >> 16);
+    const __nv_bfloat162 s = __floats2bfloat162_rn(__fdiv_rn(1.f, 1.f + expf(-g0)), __fdiv_rn(1.f, 1.f + expf(-g1)));
+    ob = __floats2bfloat162_rn(__low2float(ob) * __low2float(s), __high2float(ob) * __high2float(s));
+  }
+  *reinterpret_cast<uint32_t*>(out + idx) = *reinterpret_cast<uint32_t*>(&ob);
+}
+
 // ---------------------------------------------------------------------------------------------
 // epilogue warp: walks the CTA's segments in the consumers' order.  For each it waits for the
 // four dumped warp states (m[8], l[8], acc[G][D] in the xor layout of dump_pos), merges them,
@@ -236,7 +252,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     const int slot = cur == r0 ? 0 : 1;
     float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
     float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
-    uint16_t* orow = p.out + (lb * g.h_q + c.h * G) * D;
+    const long long orow = (lb * g.h_q + c.h * G) * D;
     if (ok) {
       for (int h = 0; h < G; ++h) {
         float mw[kConsumerWarps], M = -INFINITY;
@@ -260,8 +276,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           const float inv = ll > 0.f ? vs / ll : 0.f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            __nv_bfloat162 ob = __floats2bfloat162_rn(ax[r] * inv, ay[r] * inv);
-            *reinterpret_cast<uint32_t*>(orow + h * D + 2 * (lane + 32 * r)) = *reinterpret_cast<uint32_t*>(&ob);
+            store_out(p.out, p.gate, orow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
           }
         } else {
 #pragma unroll
@@ -332,8 +347,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
             const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
 #pragma unroll
             for (int r = 0; r < UR; ++r) {
-              __nv_bfloat162 ob = __floats2bfloat162_rn(ax[h][r] * inv, ay[h][r] * inv);
-              *reinterpret_cast<uint32_t*>(orow + h * D + 2 * (lane + 32 * r)) = *reinterpret_cast<uint32_t*>(&ob);
+              store_out(p.out, p.gate, orow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
             }
           }
         }

@@ -134,8 +134,9 @@ def kv_quant_append(k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, *
 
 def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspace: Workspace,
                      softmax_scale: float | None = None, seq_len_offset: int = 0, out: torch.Tensor | None = None,
-                     variant: str | None = None) -> torch.Tensor:
-    """Split-K GQA decode attention over the FP8 cache; returns bf16 with q's shape."""
+                     variant: str | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
+    """Split-K GQA decode attention over the FP8 cache; returns bf16 with q's shape.
+    With `gate` (bf16, q's shape) the result is bf16(bf16(attention) * bf16(sigmoid(gate)))."""
     _need_cuda(q, k_scale, v_scale, seq_len)
     if q.dtype != torch.bfloat16:
         raise ValueError("q must be bf16")
@@ -148,10 +149,19 @@ def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspac
     if out is None:
         out = torch.empty_like(q)
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
-    rc = _lib.lib().b200attn_decode(
-        ctypes.byref(shape), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(seq_len),
-        seq_len_offset, scale, VARIANTS[variant or workspace.variant], workspace.num_splits, _ptr(workspace.buf),
-        workspace.nbytes, _ptr(out), _ptr(workspace.status), _stream())
+    if gate is not None:
+        _need_cuda(gate)
+        if gate.dtype != torch.bfloat16 or gate.numel() != q.numel():
+            raise ValueError("gate must be bf16 with q's shape")
+        rc = _lib.lib().b200attn_decode_gated(
+            ctypes.byref(shape), _ptr(q), _ptr(gate), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale),
+            _ptr(seq_len), seq_len_offset, scale, VARIANTS[variant or workspace.variant], workspace.num_splits,
+            _ptr(workspace.buf), workspace.nbytes, _ptr(out), _ptr(workspace.status), _stream())
+    else:
+        rc = _lib.lib().b200attn_decode(
+            ctypes.byref(shape), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(seq_len),
+            seq_len_offset, scale, VARIANTS[variant or workspace.variant], workspace.num_splits, _ptr(workspace.buf),
+            workspace.nbytes, _ptr(out), _ptr(workspace.status), _stream())
     check(rc, "b200attn_decode")
     return out
 

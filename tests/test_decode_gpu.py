@@ -146,6 +146,38 @@ def test_ragged_batch_with_empty_and_full_sequences(pkg, oracle, cuda_device, va
     assert bool((out[:, 0] == 0).all()) and bool((out[:, 5] == 0).all())   # empty sequences -> zeros
 
 
+@pytest.mark.parametrize("variant", ["mma", "umma"])
+def test_batched_ragged_decode_steps_bs16(pkg, oracle, cuda_device, variant):
+    """The batched configuration in miniature: bs=16 ragged depths (seeded), 8 layers, two decode
+    steps with a fused one-token append per sequence; bytes bit-exact, outputs within tolerance."""
+    n_layers, batch, h_q, h_kv, d, cap = 8, 16, 40, 8, 128, 1100
+    g = torch.Generator().manual_seed(0)
+    depths = torch.randint(64, 1025, (batch,), generator=g).tolist()
+    case = build_case(oracle, n_layers, batch, h_q, h_kv, d, depths, cap, seed=300)
+    cache = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant=variant)
+    cache.k_cache.copy_(case["k_cache"]); cache.v_cache.copy_(case["v_cache"])
+    cache.set_scales(case["k_scale"], case["v_scale"])
+    cache.seq_pos.copy_(torch.tensor(depths, dtype=torch.int32))
+    cache.host_len = list(depths)
+    kc, vc = case["k_cache"].clone(), case["v_cache"].clone()
+    for step in range(2):
+        q = torch.randn(n_layers, batch, h_q, d, generator=g).to(torch.bfloat16)
+        kn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16)
+        vn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16)
+        out = cache.step(q.to(cuda_device), kn.to(cuda_device), vn.to(cuda_device))
+        torch.cuda.synchronize()
+        wk = oracle.quantize_e4m3(kn, case["k_scale"].view(n_layers, 1, h_kv, 1))
+        wv = oracle.quantize_e4m3(vn, case["v_scale"].view(n_layers, 1, h_kv, 1))
+        for b in range(batch):
+            kc[:, b, :, depths[b] + step] = wk[:, b]
+            vc[:, b, :, depths[b] + step] = wv[:, b]
+        assert torch.equal(cache.k_cache.cpu(), kc) and torch.equal(cache.v_cache.cpu(), vc)
+        lens = [x + step + 1 for x in depths]
+        ref = oracle.decode_step_reference(q, kc, vc, case["k_scale"], case["v_scale"], lens, cap)
+        assert_parity(oracle, out.cpu(), ref, f"{variant}: step {step}")
+    assert cache.seq_pos.cpu().tolist() == [x + 2 for x in depths] and cache.workspace.read_status() == 0
+
+
 @pytest.mark.parametrize("variant", VARIANTS)
 def test_large_query_magnitudes(pkg, oracle, cuda_device, variant):
     """Queries far outside f16 range (1e6 and 1e-6 scales per head) still match the oracle."""
@@ -172,6 +204,29 @@ def test_length_beyond_capacity_is_clamped_and_flagged(pkg, oracle, cuda_device,
     out, status = run_decode(pkg, case, cuda_device, variant)
     assert status & pkg._lib.STATUS_LEN_OVER_CAP
     assert torch.equal(out.view(torch.int16), ok.view(torch.int16))
+
+
+@pytest.mark.parametrize("variant", ["mma", "umma"])
+def test_gated_output_fusion(pkg, oracle, cuda_device, variant):
+    """attn_output * sigmoid(gate) with two separate bf16 roundings, fused into the output store."""
+    lens = [513, 64]
+    case = build_case(oracle, 3, 2, 40, 8, 128, lens, 1024, seed=91)
+    g = torch.Generator().manual_seed(5)
+    gate = (torch.randn(3, 2, 40, 128, generator=g) * 2).to(torch.bfloat16)
+    dev = {k: (v.to(cuda_device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    shape = pkg.make_shape(40, dev["k_cache"], dev["v_cache"], dev["k_scale"])
+    ws = pkg.Workspace(shape, cuda_device, variant=variant)
+    seq = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+    plain = pkg.decode_attention(dev["q"], dev["k_cache"], dev["v_cache"], dev["k_scale"], dev["v_scale"], seq, workspace=ws).cpu()
+    gated = pkg.decode_attention(dev["q"], dev["k_cache"], dev["v_cache"], dev["k_scale"], dev["v_scale"], seq, workspace=ws,
+                                 gate=gate.to(cuda_device)).cpu()
+    want = plain * torch.sigmoid(gate)          # torch: sigmoid rounds to bf16, the product rounds to bf16
+    diff = (gated.float() - want.float()).abs()
+    ulp = want.float().abs().clamp_min(2.0 ** -20) * 2.0 ** -7
+    assert float((diff > ulp).float().mean()) == 0.0            # never more than one bf16 step apart
+    assert float((gated != want).float().mean()) < 1e-3         # and bit-identical but for rare rounding ties
+    ref = oracle.decode_step_reference(case["q"], case["k_cache"], case["v_cache"], case["k_scale"], case["v_scale"], lens, 1024)
+    assert_parity(oracle, gated, ref * torch.sigmoid(gate), variant)
 
 
 def test_per_token_scale_mode_decode(pkg, oracle, cuda_device):
