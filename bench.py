@@ -456,9 +456,21 @@ def run_ours(args) -> int:
         line["cpu_baseline"] = cpu_baseline(depth, cap)
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish(torch, dist, world)
     return 0
+
+
+def finish(torch, dist, world) -> None:
+    """Leave a multi-rank run: all ranks idle and in step, then exit without tearing the NCCL
+    communicator down (graphs that captured its collectives are still alive; destroying the
+    process group under them has been seen to block forever)."""
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_cfg4(args) -> int:
@@ -546,8 +558,7 @@ def run_cfg4(args) -> int:
             "tokens_per_s": 16 / sec, "gpu_launches": 3 * steps, "clocks": sampler.summary()}
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish(torch, dist, world)
     return 0
 
 
