@@ -174,7 +174,7 @@ class StepRunner:
     """One workload resident on one GPU: cache, static step buffers, captured graph."""
 
     def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto",
-                 num_splits=0):
+                 num_splits=0, gather="peer"):
         self.pkg, self.torch, self.device, self.depth, self.advance = pkg, torch, device, depth, advance
         self.h_q, self.h_kv, self.dist, self.world = h_q, h_kv, dist, world
         g = torch.Generator(device=device).manual_seed(seed)
@@ -194,17 +194,34 @@ class StepRunner:
         self.k_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
         self.v_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
         self.out = torch.empty_like(self.q)
-        self.gatherer = importlib.import_module("qwen38-5080_b200.dist").HeadGather(self.out, world) if world > 1 else None
-        self.full_out = self.gatherer.full if world > 1 else None
+        distmod = importlib.import_module("qwen38-5080_b200.dist")
+        self.peer = None
+        self.gatherer = None
+        if world > 1 and gather == "peer":
+            self.peer = distmod.PeerOutput(self.out, world, dist.get_rank())
+            self.full_out = self.peer.full
+        elif world > 1:
+            self.gatherer = distmod.HeadGather(self.out, world)
+            self.full_out = self.gatherer.full
+        else:
+            self.full_out = None
         self.graph = None
 
     def launch_step(self):
         c = self.cache
+        if self.peer is not None:
+            # append, then attention storing into every rank's gathered buffer, then the cross-GPU barrier
+            self.pkg.kv_quant_append(self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
+                                     h_q=self.h_q, advance=self.advance, status=c.workspace.status)
+            self.pkg.decode_attention(self.q, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
+                                      workspace=c.workspace, seq_len_offset=0 if self.advance else 1, peer_out=self.peer)
+            self.pkg.peer_barrier(self.peer, c.workspace.status)
+            return
         self.pkg.append_decode(self.q, self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
                                workspace=c.workspace, advance=self.advance, out=self.out)
 
     def gather(self):
-        if self.world > 1:
+        if self.gatherer is not None:
             self.gatherer.gather(self.out)     # NCCL all-gather + one strided copy into [n, b, h_q, D]
 
     def capture(self):
@@ -218,7 +235,7 @@ class StepRunner:
         torch.cuda.synchronize()
         self.reset_pos()
         self.gather_in_graph = False
-        if self.world > 1:          # the all-gather belongs to the step: capture it with the kernels
+        if self.gatherer is not None:          # the all-gather belongs to the step: capture it with the kernels
             with torch.cuda.stream(side):
                 self.gather()
             torch.cuda.current_stream().wait_stream(side)
@@ -249,6 +266,8 @@ class StepRunner:
             self.gather()
 
     def kernels_per_step(self) -> int:
+        if self.peer is not None:
+            return (3 if self.advance else 2) + 1   # append (+ bump), attention with fused gather, barrier
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump
         return n + (1 if self.cache.workspace.variant == "simt" and self.cache.workspace.num_splits > 1 else 0)
 
@@ -401,11 +420,11 @@ def run_ours(args) -> int:
         room = cap - depth - args.warmup - 4 if advance else 1 << 30   # the cache must not overflow
         steps = max(1, min(args.steps, room))
         runner = StepRunner(pkg, torch, device, depth, cap, advance, h_q, h_kv, seed=rank, dist=dist, world=world,
-                            variant=args.variant, num_splits=args.ctas)
+                            variant=args.variant, num_splits=args.ctas, gather=args.gather)
         runner.capture()
-        if world > 1:   # communicator warm-up outside the timed region
-            runner.gather()
+        if world > 1:   # every rank in step before the first timed (or barrier-carrying) launch
             torch.cuda.synchronize()
+            dist.barrier()
         with ClockSampler(torch, local) as sampler:
             sec = timed_steps(torch, dist, world, runner, steps, args.warmup)
             ksec = timed_kernel(torch, runner, steps, args.warmup)
@@ -440,8 +459,11 @@ def run_ours(args) -> int:
                    "l2": f"inputs larger than L2 ({kv_bytes_per_step(depth, h_kv) / 1e6:.0f} MB KV per GPU per step)"
                          if bytes_per_launch > 200e6 else "KV working set smaller than L2: L2-warm figure",
                    "execution": "CUDA graph replay of append + attention"
-                                + ((" + NCCL all-gather + head reorder copy, captured in the graph" if runner.gather_in_graph
-                                    else " then NCCL all-gather + head reorder copy after the replay") if world > 1 else "")},
+                                + ((" with the output all-gather fused into the attention kernel (peer stores over NVLink into "
+                                     "every rank's gathered buffer) + a cross-GPU barrier kernel, all in the graph"
+                                     if runner.peer is not None else
+                                     " + NCCL all-gather + head reorder copy, captured in the graph" if runner.gather_in_graph
+                                     else " then NCCL all-gather + head reorder copy after the replay") if world > 1 else "")},
         "hbm_gbs": kv_bytes_per_step(depth) / sec / 1e9,
         "frac_of_8TBs": kv_bytes_per_step(depth) / world / sec / 8e12,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -571,6 +593,8 @@ def main() -> int:
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cfg4"], default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
     ap.add_argument("--variant", choices=["auto", "mma", "umma", "simt"], default="auto", help="attention kernel variant")
+    ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: fused peer-store all-gather (default) or NCCL all-gather + reorder copy")
     ap.add_argument("--ctas", type=int, default=0, help="override the split / CTA count (0 = library default)")
     ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

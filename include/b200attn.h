@@ -82,6 +82,22 @@ typedef struct B200AttnShape {
   long long v_layer_stride;
 } B200AttnShape;
 
+/*
+ * Output placement for KV-head tensor parallelism (no counterpart in the reference, which is
+ * single-GPU): rank `rank` of `n_peers` computes h_q of the h_q_total query heads; instead of a
+ * local output followed by an all-gather, the attention kernel stores every result directly into
+ * the gathered tensor bf16 [n_layers][batch][h_q_total][head_dim] of ALL ranks (plain peer stores
+ * over NVLink into symmetric / peer-mapped memory), at head offset rank*h_q.  out[r] is rank r's
+ * buffer as addressable from this GPU.  b200attn_peer_barrier then makes the stores visible.
+ */
+typedef struct B200AttnPeerOut {
+  int n_peers;       /* 1..8 */
+  int rank;          /* this rank */
+  int h_q_total;     /* = n_peers * shape->h_q */
+  int reserved;
+  void* out[8];
+} B200AttnPeerOut;
+
 /* Library version (B200ATTN_VERSION of the build). */
 int b200attn_version(void);
 
@@ -191,6 +207,31 @@ int b200attn_decode_gated(const B200AttnShape* shape,
                           void* workspace, size_t workspace_bytes,
                           void* out_bf16,
                           int* status, void* stream);
+
+/*
+ * b200attn_decode whose output all-gather is fused into the kernel (see B200AttnPeerOut).
+ * Tensor-core variants only.  Follow it, on the same stream, with b200attn_peer_barrier before
+ * anything reads the gathered tensor; a buffer must not be rewritten by a later step while a
+ * slower rank may still be reading it (alternate two buffers, or add a second barrier).
+ */
+int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* peers,
+                          const void* q_bf16,
+                          const void* k_cache_u8, const void* v_cache_u8,
+                          const float* k_scale, const float* v_scale,
+                          const int* seq_len, int seq_len_offset,
+                          float softmax_scale,
+                          int variant, int num_splits,
+                          void* workspace, size_t workspace_bytes,
+                          int* status, void* stream);
+
+/*
+ * Cross-GPU arrive-and-wait.  flags[r] = rank r's flag buffer (int32[world + 1], zero-initialised,
+ * symmetric / peer-mapped memory) as addressable from this GPU.  Every rank launches it once per
+ * step; it returns when all ranks have arrived.  The wait is bounded (1 s): on expiry
+ * B200ATTN_STATUS_WAIT_TIMEOUT is OR-ed into *status and the kernel returns.  Graph-replayable:
+ * the epoch counter lives in the flag buffer.
+ */
+int b200attn_peer_barrier(void* const* flags, int rank, int world, int* status, void* stream);
 
 /*
  * b200attn_decode without a caller workspace (no counterpart in the reference: its fused kernel

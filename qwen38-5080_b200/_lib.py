@@ -31,6 +31,11 @@ class B200AttnShape(ctypes.Structure):
     ]
 
 
+class B200AttnPeerOut(ctypes.Structure):
+    _fields_ = [("n_peers", c_int), ("rank", c_int), ("h_q_total", c_int), ("reserved", c_int),
+                ("out", c_void_p * 8)]
+
+
 # name -> (restype, argtypes); every symbol include/b200attn.h declares
 PROTOTYPES = {
     "b200attn_version": (c_int, []),
@@ -49,6 +54,10 @@ PROTOTYPES = {
     "b200attn_decode_gated": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p,
                                       c_void_p, c_void_p]),
+    "b200attn_decode_peers": (c_int, [ctypes.POINTER(B200AttnShape), ctypes.POINTER(B200AttnPeerOut), c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p,
+                                      c_size_t, c_void_p, c_void_p]),
+    "b200attn_peer_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),
     "b200attn_decode_static": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "b200attn_static_scratch_bytes": (c_size_t, []),

@@ -127,14 +127,14 @@ int b200attn_kv_quant_append(const B200AttnShape* shape, const void* k_new, cons
                                        advance_pos, status, stream);
 }
 
-static int decode_impl(const B200AttnShape* shape, const void* q, const void* gate, const void* k_cache,
+static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, const void* q, const void* gate, const void* k_cache,
                        const void* v_cache, const float* k_scale, const float* v_scale, const int* seq_len,
                        int seq_len_offset, float softmax_scale, int variant, int num_splits, void* workspace,
                        size_t workspace_bytes, void* out, int* status, void* stream) {
   Geometry g;
   int rc = resolve(shape, &g);
   if (rc) return rc;
-  if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !seq_len || !out || !status) return B200ATTN_ERR_NULL;
+  if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !seq_len || (!out && !peers) || !status) return B200ATTN_ERR_NULL;
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out)) return B200ATTN_ERR_ALIGN;
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
@@ -150,7 +150,20 @@ static int decode_impl(const B200AttnShape* shape, const void* q, const void* ga
   }
   if (gate && (v == B200ATTN_VARIANT_SIMT || !aligned16(gate))) return v == B200ATTN_VARIANT_SIMT ? B200ATTN_ERR_VARIANT : B200ATTN_ERR_ALIGN;
   DecodeArgs a{q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
-               num_splits, workspace, workspace_bytes, out, status, gate};
+               num_splits, workspace, workspace_bytes, out, status, gate, 0, 0, 0, {}};
+  if (peers) {
+    if (v == B200ATTN_VARIANT_SIMT) return B200ATTN_ERR_VARIANT;
+    if (peers->n_peers < 1 || peers->n_peers > 8 || peers->rank < 0 || peers->rank >= peers->n_peers) return B200ATTN_ERR_SHAPE;
+    if (peers->h_q_total != g.h_q * peers->n_peers) return B200ATTN_ERR_SHAPE;
+    a.n_out = peers->n_peers;
+    a.out_hq_total = peers->h_q_total;
+    a.out_head_base = peers->rank * g.h_q;
+    for (int r = 0; r < peers->n_peers; ++r) {
+      if (!peers->out[r]) return B200ATTN_ERR_NULL;
+      if (!aligned16(peers->out[r])) return B200ATTN_ERR_ALIGN;
+      a.out_peer[r] = peers->out[r];
+    }
+  }
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
                                              : v == B200ATTN_VARIANT_UMMA ? launch_decode_umma(g, a, (cudaStream_t)stream)
                                              : launch_decode_mma(g, a, (cudaStream_t)stream);
@@ -161,7 +174,7 @@ int b200attn_decode(const B200AttnShape* shape, const void* q, const void* k_cac
                     const float* k_scale, const float* v_scale, const int* seq_len, int seq_len_offset,
                     float softmax_scale, int variant, int num_splits, void* workspace,
                     size_t workspace_bytes, void* out, int* status, void* stream) {
-  return decode_impl(shape, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
+  return decode_impl(shape, nullptr, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                      variant, num_splits, workspace, workspace_bytes, out, status, stream);
 }
 
@@ -170,8 +183,25 @@ int b200attn_decode_gated(const B200AttnShape* shape, const void* q, const void*
                           int seq_len_offset, float softmax_scale, int variant, int num_splits, void* workspace,
                           size_t workspace_bytes, void* out, int* status, void* stream) {
   if (!gate) return B200ATTN_ERR_NULL;
-  return decode_impl(shape, q, gate, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
+  return decode_impl(shape, nullptr, q, gate, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                      variant, num_splits, workspace, workspace_bytes, out, status, stream);
+}
+
+int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* peers, const void* q,
+                          const void* k_cache, const void* v_cache, const float* k_scale, const float* v_scale,
+                          const int* seq_len, int seq_len_offset, float softmax_scale, int variant, int num_splits,
+                          void* workspace, size_t workspace_bytes, int* status, void* stream) {
+  if (!peers) return B200ATTN_ERR_NULL;
+  return decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
+                     variant, num_splits, workspace, workspace_bytes, nullptr, status, stream);
+}
+
+int b200attn_peer_barrier(void* const* flags, int rank, int world, int* status, void* stream) {
+  if (!flags || !status) return B200ATTN_ERR_NULL;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return B200ATTN_ERR_SHAPE;
+  for (int r = 0; r < world; ++r) if (!flags[r]) return B200ATTN_ERR_NULL;
+  cudaError_t e = launch_peer_barrier(reinterpret_cast<int* const*>(flags), rank, world, status, (cudaStream_t)stream);
+  return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
 }
 
 int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void* k_new, const void* v_new,

@@ -94,7 +94,13 @@ struct DecodeArgs {
   void* out;
   int* status;
   const void* gate;   // optional (tensor-core variants only)
+  int n_out;          // peer mode (tensor-core variants only): number of rank buffers, 0 = local output
+  int out_hq_total, out_head_base;
+  void* out_peer[8];
 };
+
+// Cross-GPU arrive-and-wait on symmetric flag buffers (peer_barrier.cu).
+cudaError_t launch_peer_barrier(int* const* flags, int rank, int world, int* status, cudaStream_t stream);
 
 // SIMT variant: split-K partial kernel + combine kernel.
 size_t simt_workspace_bytes(const Geometry& g, int num_splits);

@@ -116,7 +116,11 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
-        for (int i = tid; i < g.h_q * D; i += kThreads) p.out[r * g.h_q * D + i] = 0;
+        for (int i = tid; i < g.h_q * D; i += kThreads) {
+          if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
+          else
+            for (int pr = 0; pr < p.n_out; ++pr) p.out_peer[pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
+        }
     }
   }
 
@@ -456,6 +460,10 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.tickets = (int*)(p.ws_ml + (size_t)n * 2 * 16);
   p.out = (uint16_t*)a.out;
   p.gate = (const uint16_t*)a.gate;
+  p.n_out = a.n_out;
+  p.out_hq_total = a.n_out ? a.out_hq_total : g.h_q;
+  p.out_head_base = a.n_out ? a.out_head_base : 0;
+  for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
   p.status = a.status;
   p.stages = stages_for(g);
   const size_t smem = smem_bytes_for(g, p.stages);

@@ -29,7 +29,12 @@ struct MmaParams {
   float* ws_acc;         // [num_ctas][2][G][D]
   float* ws_ml;          // [num_ctas][2][2][8]
   int* tickets;          // [pairs]
-  uint16_t* out;
+  uint16_t* out;         // local output [n_layers][batch][h_q][D] (peer mode: unused)
+  // peer mode (tensor-parallel by KV head): every result is stored into the output buffer of all
+  // n_out ranks, laid out [n_layers][batch][out_hq_total][D], at head offset out_head_base
+  uint16_t* out_peer[8];
+  int n_out;             // 0 = local output only
+  int out_hq_total, out_head_base;
   const uint16_t* gate;  // optional bf16 [n_layers][batch][h_q][D]: out *= sigmoid(gate), see store_out
   int* status;
   int stages;
@@ -206,7 +211,9 @@ __device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((
 // block, attn_output * sigmoid(gate), with its two separate bf16 roundings
 // (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150): s = bf16(sigmoid(gate)), then
 // bf16(bf16(attn) * s).
-__device__ __forceinline__ void store_out(uint16_t* out, const uint16_t* gate, long long idx, float x, float y) {
+__device__ __forceinline__ void store_out(const MmaParams& p, long long idx, long long peer_idx, float x, float y) {
+  uint16_t* out = p.out;
+  const uint16_t* gate = p.gate;
   __nv_bfloat162 ob = __floats2bfloat162_rn(x, y);
   if (gate) {
     const uint32_t gw = *reinterpret_cast<const uint32_t*>(gate + idx);
@@ -214,7 +221,15 @@ __device__ __forceinline__ void store_out(uint16_t* out, const uint16_t* gate, l
     const __nv_bfloat162 s = __floats2bfloat162_rn(__fdiv_rn(1.f, 1.f + expf(-g0)), __fdiv_rn(1.f, 1.f + expf(-g1)));
     ob = __floats2bfloat162_rn(__low2float(ob) * __low2float(s), __high2float(ob) * __high2float(s));
   }
-  *reinterpret_cast<uint32_t*>(out + idx) = *reinterpret_cast<uint32_t*>(&ob);
+  const uint32_t bits = *reinterpret_cast<uint32_t*>(&ob);
+  if (p.n_out == 0) {
+    *reinterpret_cast<uint32_t*>(out + idx) = bits;
+  } else {
+    // the output all-gather, fused: plain stores into every rank's buffer (own one included) over NVLink
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.n_out) *reinterpret_cast<uint32_t*>(p.out_peer[r] + peer_idx) = bits;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -253,6 +268,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
     float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
     const long long orow = (lb * g.h_q + c.h * G) * D;
+    const long long prow = (lb * p.out_hq_total + p.out_head_base + c.h * G) * D;   // row in the gathered layout
     if (ok) {
       for (int h = 0; h < G; ++h) {
         float mw[kConsumerWarps], M = -INFINITY;
@@ -276,7 +292,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           const float inv = ll > 0.f ? vs / ll : 0.f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            store_out(p.out, p.gate, orow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
+            store_out(p, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
           }
         } else {
 #pragma unroll
@@ -347,7 +363,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
             const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
 #pragma unroll
             for (int r = 0; r < UR; ++r) {
-              store_out(p.out, p.gate, orow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
+              store_out(p, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
             }
           }
         }

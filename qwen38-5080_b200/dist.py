@@ -58,6 +58,35 @@ class HeadGather:
         return self.full
 
 
+class PeerOutput:
+    """Gathered output [n_layers, batch, h_q_total, D] in symmetric memory, one per rank, plus the
+    flag buffers of the cross-GPU barrier.  The attention kernel of every rank stores its heads
+    straight into all of these buffers (peer stores over NVLink): the all-gather is fused into the
+    kernel, and `ops.peer_barrier` afterwards is all that is left of the collective.
+    Allocate once, before any graph capture."""
+
+    def __init__(self, local_like: torch.Tensor, world: int, rank: int, group=None):
+        import ctypes
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        from ._lib import B200AttnPeerOut
+        group = group if group is not None else dist.group.WORLD
+        n, b, hq, d = local_like.shape
+        dev = local_like.device
+        self.world, self.rank = world, rank
+        self.full = symm_mem.empty((n, b, world * hq, d), dtype=local_like.dtype, device=dev)
+        self.full.zero_()
+        self._out_hdl = symm_mem.rendezvous(self.full, group)
+        self.flags = symm_mem.empty((64,), dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        self._flag_hdl = symm_mem.rendezvous(self.flags, group)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        ptrs = (ctypes.c_void_p * 8)(*[int(p) for p in self._out_hdl.buffer_ptrs])
+        self.c_peers = B200AttnPeerOut(world, rank, world * hq, 0, ptrs)
+        self.c_flags = (ctypes.c_void_p * 8)(*[int(p) for p in self._flag_hdl.buffer_ptrs])
+
+
 def gather_sequences(local: torch.Tensor, plan: list[list[int]], batch: int, group=None) -> torch.Tensor:
     """Off-clock gather for parity checks of the sequence-sharded path: every rank contributes
     [n_layers, len(plan[rank]), h_q, D]; returns [n_layers, batch, h_q, D] in original order."""
@@ -76,4 +105,4 @@ def gather_sequences(local: torch.Tensor, plan: list[list[int]], batch: int, gro
     return out
 
 
-__all__ = ["head_shard", "assign_sequences", "HeadGather", "gather_sequences"]
+__all__ = ["head_shard", "assign_sequences", "HeadGather", "PeerOutput", "gather_sequences"]

@@ -134,7 +134,7 @@ def kv_quant_append(k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, *
 
 def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspace: Workspace,
                      softmax_scale: float | None = None, seq_len_offset: int = 0, out: torch.Tensor | None = None,
-                     variant: str | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
+                     variant: str | None = None, gate: torch.Tensor | None = None, peer_out=None) -> torch.Tensor:
     """Split-K GQA decode attention over the FP8 cache; returns bf16 with q's shape.
     With `gate` (bf16, q's shape) the result is bf16(bf16(attention) * bf16(sigmoid(gate)))."""
     _need_cuda(q, k_scale, v_scale, seq_len)
@@ -146,9 +146,16 @@ def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspac
         raise ValueError("q must be [n_layers, batch, h_q, head_dim]")
     if seq_len.dtype != torch.int32 or seq_len.numel() != shape.batch:
         raise ValueError("seq_len must be int32 [batch]")
+    scale = d ** -0.5 if softmax_scale is None else softmax_scale
+    if peer_out is not None:   # tensor parallel: results go straight into every rank's gathered buffer
+        rc = _lib.lib().b200attn_decode_peers(
+            ctypes.byref(shape), ctypes.byref(peer_out.c_peers), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale),
+            _ptr(v_scale), _ptr(seq_len), seq_len_offset, scale, VARIANTS[variant or workspace.variant],
+            workspace.num_splits, _ptr(workspace.buf), workspace.nbytes, _ptr(workspace.status), _stream())
+        check(rc, "b200attn_decode_peers")
+        return peer_out.full
     if out is None:
         out = torch.empty_like(q)
-    scale = d ** -0.5 if softmax_scale is None else softmax_scale
     if gate is not None:
         _need_cuda(gate)
         if gate.dtype != torch.bfloat16 or gate.numel() != q.numel():
@@ -164,6 +171,12 @@ def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspac
             workspace.nbytes, _ptr(out), _ptr(workspace.status), _stream())
     check(rc, "b200attn_decode")
     return out
+
+
+def peer_barrier(peer_out, status: torch.Tensor) -> None:
+    """Cross-GPU arrive-and-wait after `decode_attention(..., peer_out=...)` (same stream)."""
+    check(_lib.lib().b200attn_peer_barrier(peer_out.c_flags, peer_out.rank, peer_out.world, _ptr(status), _stream()),
+          "b200attn_peer_barrier")
 
 
 def append_decode(q, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, *, workspace: Workspace,
@@ -208,4 +221,4 @@ def calibrate_scales(x: torch.Tensor, capacity: int) -> torch.Tensor:
 
 
 __all__ = ["B200AttnError", "B200AttnShape", "Workspace", "make_shape", "pick_splits", "workspace_bytes",
-           "kv_quant_append", "decode_attention", "append_decode", "dequant_prefix", "calibrate_scales"]
+           "kv_quant_append", "decode_attention", "peer_barrier", "append_decode", "dequant_prefix", "calibrate_scales"]
