@@ -91,7 +91,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     sFlags[0] = 0; sFlags[1] = 0; sFlags[3] = 0;
-    int acc = 0, any_empty = 0, st = 0;
+    int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
       int len = p.seq_len[b] + p.seq_len_offset;
       if (len < 0) { len = 0; st |= B200ATTN_STATUS_LEN_NEGATIVE; }
@@ -100,9 +100,10 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       sCum[b] = acc;
       acc += (len + kTileT - 1) / kTileT;
       any_empty |= len == 0;
+      uniform &= b == 0 || acc - sCum[b] == sCum[1] - sCum[0];
     }
     sCum[g.batch] = acc;
-    sFlags[2] = any_empty;
+    sFlags[2] = any_empty | (uniform ? 2 : 0);
     if (st && blockIdx.x == 0) atomicOr(p.status, st);
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -112,7 +113,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   __syncthreads();
 
   // sequences of length 0 have no tiles: their outputs are zero, written by whoever gets there
-  if (sFlags[2]) {
+  if (sFlags[2] & 1) {
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
@@ -126,14 +127,11 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 
   const long long per_layer = (long long)sCum[g.batch] * g.h_kv;
   const long long total = per_layer * g.n_layers;
-  const int n_eff = (int)(total < (long long)gridDim.x ? total : (long long)gridDim.x);
-  const bool has_work = (long long)blockIdx.x < (long long)n_eff;
+  int n_eff;
+  long long r0, r1;
+  cta_range(total, (int)gridDim.x, (int)blockIdx.x, (sFlags[2] & 2) ? sCum[1] - sCum[0] : 0, n_eff, r0, r1);
+  const bool has_work = r0 < r1;
   TRACE(1);
-  long long r0 = 0, r1 = 0;
-  if (has_work) {
-    r0 = (long long)blockIdx.x * total / n_eff;
-    r1 = ((long long)blockIdx.x + 1) * total / n_eff;
-  }
 
   if (warp == kProducerWarp) {
     // ===================== producer warp: one elected lane issues the copies =====================

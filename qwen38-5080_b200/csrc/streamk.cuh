@@ -203,6 +203,32 @@ __device__ __forceinline__ int owner_of(long long x, long long total, int n) {
 }
 
 
+// Tile range [r0, r1) of CTA `cta`.  Default: the even stream-K split of `total` tiles over n_eff
+// CTAs.  Short sequences are the exception: when every pair has the same small number of tiles
+// (`pair_tiles` <= kAlignMaxTiles, i.e. depth <= 1024 with 64-token tiles) and there are enough pairs
+// to occupy at least half the grid, boundaries are rounded to whole pairs.  A split pair costs its
+// two owners a partial write, an arrival ticket and a combine (~4 us on the epilogue warp), more than
+// the few tiles of imbalance it saves; with whole pairs no partial ever exists.
+constexpr int kAlignMaxTiles = 16;
+__device__ __forceinline__ void cta_range(long long total, int grid, int cta, int pair_tiles,
+                                          int& n_eff, long long& r0, long long& r1) {
+  n_eff = (int)(total < (long long)grid ? total : (long long)grid);
+  r0 = r1 = 0;
+  if (pair_tiles > 0 && pair_tiles <= kAlignMaxTiles && total / pair_tiles >= (long long)(grid / 2)) {
+    const long long pairs = total / pair_tiles;
+    n_eff = (int)(pairs < (long long)grid ? pairs : (long long)grid);
+    if (cta < n_eff) {
+      r0 = ((long long)cta * pairs / n_eff) * pair_tiles;
+      r1 = (((long long)cta + 1) * pairs / n_eff) * pair_tiles;
+    }
+    return;
+  }
+  if (cta < n_eff) {
+    r0 = (long long)cta * total / n_eff;
+    r1 = ((long long)cta + 1) * total / n_eff;
+  }
+}
+
 // Position (in float2 units) of dim pair u inside a dumped head row.  The xor spreads the
 // consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
 __device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
