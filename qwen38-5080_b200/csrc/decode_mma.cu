@@ -41,6 +41,10 @@ constexpr int kCtasPerSm = 3;                      // D = 128: the kernel is lat
                                                    // spills 191 us).  Co-resident CTAs do not progress equally (the first resident
                                                    // one ends ~10 % early); skewing the tile split per residency slot, or fusing the
                                                    // three CTAs into one 576-thread CTA, was measured and did not help (182 us).
+                                                   // The 96-register cap of 18 warps per SM costs ~100 B of spills in the consumer
+                                                   // loop; dropping the producer warp (lane 0 of consumer warp 0 issuing the copies,
+                                                   // 15 warps, 127 registers, no spills) was slower still (198 us): the coupling of
+                                                   // copy issue to one consumer's progress costs more than the spills.
 constexpr int kDumpBufs = 2;                       // dump buffers per CTA
 
 template <int D>
