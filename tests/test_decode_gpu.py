@@ -356,3 +356,30 @@ def test_full_size_properties(pkg, oracle, cuda_device):
         ws = pkg.Workspace(shape, cuda_device, variant=variant)
         out = pkg.decode_attention(q, kc, vconst, ks, vs, seq, workspace=ws).cpu().float()
         assert (out - want.view(1, 1, h_q, 1)).abs().max().item() <= 2.0 ** -8 * want.max().item(), variant
+
+
+def test_peer_barrier_wait_is_bounded(pkg, cuda_device):
+    """The cross-GPU barrier gives up after its 1 s budget when a peer never arrives (here: a second
+    flag buffer that nobody writes), reports it in the status word, and leaves the context usable."""
+    import ctypes
+    import time
+    lib = pkg._lib.lib()
+    mine = torch.zeros(64, dtype=torch.int32, device=cuda_device)
+    silent_peer = torch.zeros(64, dtype=torch.int32, device=cuda_device)   # stands in for a rank that never arrives
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    flags = (ctypes.c_void_p * 8)(mine.data_ptr(), silent_peer.data_ptr())
+    t0 = time.perf_counter()
+    rc = lib.b200attn_peer_barrier(flags, 0, 2, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert rc == 0
+    assert status.item() & pkg._lib.STATUS_WAIT_TIMEOUT
+    assert 0.5 < dt < 5.0, dt
+    assert silent_peer[0].item() == 1          # our arrival was posted to the peer's buffer
+    # a world of one completes at once, and the device still works
+    status.zero_()
+    solo = (ctypes.c_void_p * 8)(mine.data_ptr())
+    assert lib.b200attn_peer_barrier(solo, 0, 1, status.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert float((torch.ones(8, device=cuda_device) * 2).sum()) == 16.0
