@@ -592,7 +592,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cfg4"], default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
-    ap.add_argument("--variant", choices=["auto", "mma", "umma", "simt"], default="auto", help="attention kernel variant")
+    ap.add_argument("--variant", choices=["auto", "mma", "umma", "umma2", "simt"], default="auto", help="attention kernel variant")
     ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
                     help="N > 1: fused peer-store all-gather (default) or NCCL all-gather + reorder copy")
     ap.add_argument("--ctas", type=int, default=0, help="override the split / CTA count (0 = library default)")

@@ -52,6 +52,9 @@ extern "C" {
 #define B200ATTN_VARIANT_MMA      2   /* TMA/mbarrier staged, tensor-core (mma.sync f16) stream-K kernel with fused combine */
 #define B200ATTN_VARIANT_UMMA     3   /* the same stream-K kernel with S = K q^T on tcgen05.mma kind::f8f6f4: K tiles feed the
                                          tensor cores from shared memory unconverted, scores in tensor memory */
+#define B200ATTN_VARIANT_UMMA2    4   /* both products on tcgen05.mma: S = K q^T and O += V^T P^T read the staged FP8 tiles
+                                         directly (V as an MN-major operand), scores and the output accumulator live in
+                                         tensor memory; query groups of at most 5 heads */
 
 /* scale granularity of the FP8 cache */
 #define B200ATTN_SCALE_PER_HEAD   0   /* fp32 scale per (layer, kv_head): [n_layers][h_kv] */

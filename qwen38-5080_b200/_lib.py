@@ -18,8 +18,8 @@ c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes
 OK = 0
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_SPLITS, ERR_CUDA, ERR_CAPACITY, ERR_VARIANT, ERR_TOO_LARGE = range(-1, -10, -1)
 STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEGATIVE = 1, 2, 4, 8
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA = 0, 1, 2, 3
-VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma": VARIANT_UMMA}
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA, VARIANT_UMMA2 = 0, 1, 2, 3, 4
+VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma": VARIANT_UMMA, "umma2": VARIANT_UMMA2}
 SCALE_PER_HEAD, SCALE_PER_TOKEN = 0, 1
 
 

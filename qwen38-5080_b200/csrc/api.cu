@@ -43,12 +43,14 @@ int resolve_variant(int variant, const Geometry& g) {
   if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
   if (variant == B200ATTN_VARIANT_SIMT) return variant;
   if (variant == B200ATTN_VARIANT_MMA || variant == B200ATTN_VARIANT_UMMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
+  if (variant == B200ATTN_VARIANT_UMMA2) return mma_ok && umma2_supported(g) ? variant : B200ATTN_ERR_SHAPE;
   return B200ATTN_ERR_VARIANT;
 }
 
 int pick(const Geometry& g, int v, int max_seq_len, int num_sms) {
   if (v == B200ATTN_VARIANT_SIMT) return simt_pick_splits(g, max_seq_len, num_sms);
   if (v == B200ATTN_VARIANT_UMMA) return umma_pick_ctas(g, max_seq_len, num_sms);
+  if (v == B200ATTN_VARIANT_UMMA2) return umma2_pick_ctas(g, max_seq_len, num_sms);
   return mma_pick_ctas(g, max_seq_len, num_sms);
 }
 
@@ -166,6 +168,7 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
   }
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
                                              : v == B200ATTN_VARIANT_UMMA ? launch_decode_umma(g, a, (cudaStream_t)stream)
+                                             : v == B200ATTN_VARIANT_UMMA2 ? launch_decode_umma2(g, a, (cudaStream_t)stream)
                                              : launch_decode_mma(g, a, (cudaStream_t)stream);
   return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
 }

@@ -115,5 +115,8 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
 // UMMA variant: the same stream-K kernel with the score GEMM on tcgen05.mma (FP8 bytes from shared memory).
 int umma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
 cudaError_t launch_decode_umma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
+bool umma2_supported(const Geometry& g);
+int umma2_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
+cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
 
 }  // namespace b200attn

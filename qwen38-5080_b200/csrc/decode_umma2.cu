@@ -1,0 +1,566 @@
+// Full tcgen05 variant of the stream-K decode attention: BOTH products run on the 5th-generation
+// tensor cores straight from the TMA-staged FP8 tiles; no K or V byte passes through a register.
+//
+// Same persistent stream-K skeleton, producer warp, epilogue warp and fused combine as the other
+// tensor-core kernels, 128-token tiles.  Per tile:
+//   1. issuer warp: S[128 tokens x 16] = K q^T with tcgen05.mma kind::f8f6f4 — the K tile's TMA
+//      128-byte-swizzle layout is the K-major canonical operand layout; the query is the B operand
+//      as two e4m3 rows per head (leading part + remainder = the bf16 value exactly); scores land
+//      in tensor memory (two buffers);
+//   2. four softmax warps, one thread per token: tcgen05.ld of the token's scores, one CTA-wide
+//      running reference maximum per head (redux.sync per warp + a shared-memory exchange), p =
+//      2^(s - m_ref).  The reference only moves when a tile's maximum exceeds it by more than
+//      kTau (lazy rescale: p stays <= 2^kTau), so the accumulator in tensor memory is rescaled
+//      (tcgen05.ld -> multiply -> tcgen05.st) only in the first tiles of a pair;
+//   3. the probabilities become the B operand of the second product: p * 2^13 is written as three
+//      e5m2 terms (leading 3 significant bits, then the remainder twice: 9 significant bits, the
+//      precision class of the reference's bf16 P, with e5m2's range down to 2^-29 of the
+//      reference) into a 16-row x 128-token shared-memory operand (rows 3h..3h+2 for head h);
+//   4. issuer warp: O[128 dims x 16] += V^T P^T with tcgen05.mma, A = the V tile read MN-major
+//      (its swizzled [token][dim] layout is the MN-major canonical layout), accumulating in tensor
+//      memory over the whole pair; rows beyond the valid length are zeroed in shared memory first
+//      (their bytes may be NaN patterns);
+//   5. at the end of a pair the softmax warps read O once (one thread per dim), add the three
+//      terms per head, and hand ONE state (m, l, acc) to the epilogue warp.
+// G <= 5 query heads per KV head (3 G <= 16 operand rows).
+//
+// All waits are bounded as in the other kernels; tensor memory is allocated by the issuer warp at
+// kernel start and always freed by it after the final barrier.
+#include "tcgen05.cuh"
+
+namespace b200attn {
+
+namespace {
+
+constexpr int kTile2 = 128;
+constexpr int kIssuer2 = kConsumerWarps + 2;       // warp 6
+constexpr int kThreads2 = kConsumerThreads + 96;
+constexpr int kKStages2 = 2;
+constexpr int kTmemCols2 = 64;                     // S: 2 x 16, O: 16 per 128 dims (<= 32)
+constexpr float kTau = 2.0f;                       // lazy-rescale threshold, log2 units
+constexpr float kPScale = 8192.f;                  // 2^13: p * 2^13 <= 2^15 < 57344 (e5m2 max)
+
+// D f32, A e4m3 MN-major (V^T), B e5m2 K-major (P^T), N = 16, M = 128
+constexpr uint32_t kIdescPV = (1u << 4) | (1u << 10) | (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// Leading part of x that an e5m2 value holds exactly (sign, exponent, top two mantissa bits).
+__device__ __forceinline__ float e5m2_head(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFE00000u); }
+// Two floats -> two e5m2 bytes: `lo` in the low byte, `hi` in the high byte.
+__device__ __forceinline__ uint32_t pack_e5m2x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return (uint32_t)r;
+}
+__device__ __forceinline__ void sts8(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts128z(uint32_t addr) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void bar_softmax() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(kThreads2)
+attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                          const MmaParams p) {
+  constexpr int DH = D / 128;
+  constexpr int TILE_BYTES = kTile2 * D;
+  constexpr int DP = D + 4;
+  constexpr int QOP_BYTES = DH * 16 * 128;   // query operand
+  constexpr int POP_BYTES = 16 * 128;        // probability operand: 16 rows x 128 tokens
+  const Geometry& g = p.g;
+  const int G = g.group;
+  const int vstages = p.stages;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t q_bytes = (uint32_t)G * D * 2;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sK = smem;                                                   // [2][TILE_BYTES]
+  uint8_t* sV = sK + (size_t)kKStages2 * TILE_BYTES;                    // [vstages][TILE_BYTES]
+  uint8_t* sQop = sV + (size_t)vstages * TILE_BYTES;                    // [2][QOP_BYTES]
+  uint8_t* sPop = sQop + 2 * QOP_BYTES;                                 // [2][POP_BYTES], 1024-aligned
+  uint8_t* sQraw = sPop + 2 * POP_BYTES;                                // [2][G*D] bf16
+  float* sScale = reinterpret_cast<float*>(sQraw + 2 * q_bytes);        // [2][8]
+  float* sWmax = sScale + 16;                                           // [2][4][8] per-warp tile maxima
+  float* sWl = sWmax + 64;                                              // [4][8] per-warp sums
+  float* sDump = sWl + 32;                                              // [G][DP], one CTA-wide state
+  float* sML = sDump + G * DP;                                          // [16]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + 16);
+  const uint32_t kfull0 = smem_u32(bars), kempty0 = kfull0 + 8u * kKStages2;
+  const uint32_t vfull0 = kempty0 + 8u * kKStages2, vempty0 = vfull0 + 8u * vstages;
+  const uint32_t qrfull0 = vempty0 + 8u * vstages, qrempty0 = qrfull0 + 16u;
+  const uint32_t qinfo0 = qrempty0 + 16u, sfull0 = qinfo0 + 16u, sempty0 = sfull0 + 16u;
+  const uint32_t pfull0 = sempty0 + 16u, pvdone0 = pfull0 + 16u;
+  const uint32_t dfull0 = pvdone0 + 16u, dempty0 = dfull0 + 8u;
+  constexpr int kFixedBars = 2 * kKStages2 + 16;
+  int* sFlags = reinterpret_cast<int*>(bars + kFixedBars + 2 * vstages);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
+  int* sLen = sFlags + 8;
+  int* sCum = sLen + g.batch;
+  volatile int* timed_out = sFlags;
+
+  if (tid == 0) {
+    for (int s = 0; s < kKStages2; ++s) { mbar_init(kfull0 + 8u * s, 1); mbar_init(kempty0 + 8u * s, 1); }
+    for (int s = 0; s < vstages; ++s) { mbar_init(vfull0 + 8u * s, 1); mbar_init(vempty0 + 8u * s, 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(qrfull0 + 8u * i, 1);
+      mbar_init(qrempty0 + 8u * i, 1);
+      mbar_init(qinfo0 + 8u * i, 1);
+      mbar_init(sfull0 + 8u * i, 1);
+      mbar_init(sempty0 + 8u * i, kConsumerWarps);
+      mbar_init(pfull0 + 8u * i, kConsumerWarps);
+      mbar_init(pvdone0 + 8u * i, 1);
+    }
+    mbar_init(dfull0, kConsumerWarps);
+    mbar_init(dempty0, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    sFlags[0] = 0; sFlags[3] = 0; sFlags[4] = 0; sFlags[5] = 0; sFlags[6] = 0; sFlags[7] = 0;
+    int acc = 0, any_empty = 0, st = 0, uniform = 1;
+    for (int b = 0; b < g.batch; ++b) {
+      int len = p.seq_len[b] + p.seq_len_offset;
+      if (len < 0) { len = 0; st |= B200ATTN_STATUS_LEN_NEGATIVE; }
+      if (len > g.capacity) { len = g.capacity; st |= B200ATTN_STATUS_LEN_OVER_CAP; }
+      sLen[b] = len;
+      sCum[b] = acc;
+      acc += (len + kTile2 - 1) / kTile2;
+      any_empty |= len == 0;
+      uniform &= b == 0 || acc - sCum[b] == sCum[1] - sCum[0];
+    }
+    sCum[g.batch] = acc;
+    sFlags[2] = any_empty | (uniform ? 2 : 0);
+    if (st && blockIdx.x == 0) atomicOr(p.status, st);
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
+  }
+  if (warp == kIssuer2) tmem_alloc(smem_u32(sFlags + 1), kTmemCols2);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = (uint32_t)sFlags[1];
+
+  if (sFlags[2] & 1) {   // sequences of length 0 have no tiles: their outputs are zero
+    const long long rows = (long long)g.n_layers * g.batch;
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+      if (sLen[r % g.batch] == 0)
+        for (int i = tid; i < g.h_q * D; i += kThreads2) {
+          if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
+          else
+            for (int pr = 0; pr < p.n_out; ++pr) p.out_peer[pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
+        }
+    }
+  }
+
+  const long long per_layer = (long long)sCum[g.batch] * g.h_kv;
+  const long long total = per_layer * g.n_layers;
+  int n_eff;
+  long long r0, r1;
+  cta_range(total, (int)gridDim.x, (int)blockIdx.x, (sFlags[2] & 2) ? sCum[1] - sCum[0] : 0, n_eff, r0, r1);
+  const bool has_work = r0 < r1;
+
+  if (warp == kProducerWarp) {
+    // ===================== producer warp: one elected lane issues the copies =====================
+    if (lane == 0 && has_work) {
+      Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+      int it = 0, seg = 0;
+      bool seg_start = true;
+      for (long long idx = r0; idx < r1; ++idx, ++it) {
+        if (seg_start) {
+          const int qb = seg & 1;
+          if (seg >= 2 && !mbar_wait(qrempty0 + 8u * qb, ((seg >> 1) - 1) & 1, timed_out, p.status)) break;
+          mbar_arrive_expect_tx(qrfull0 + 8u * qb, q_bytes);
+          const long long lb = (long long)c.layer * g.batch + c.b;
+          bulk_load(smem_u32(sQraw + qb * q_bytes), p.q + (lb * g.h_q + c.h * G) * D, q_bytes, qrfull0 + 8u * qb);
+          ++seg;
+          seg_start = false;
+        }
+        const int row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTile2;
+        const int ks = it % kKStages2, vs = it % vstages;
+        if (it >= kKStages2 && !mbar_wait(kempty0 + 8u * ks, ((it / kKStages2) - 1) & 1, timed_out, p.status)) break;
+        mbar_arrive_expect_tx(kfull0 + 8u * ks, TILE_BYTES);
+#pragma unroll
+        for (int hf = 0; hf < DH; ++hf)
+          tma_load_3d(smem_u32(sK + (size_t)ks * TILE_BYTES + hf * kTile2 * 128), &kmap, hf * 128, row, c.layer, kfull0 + 8u * ks);
+        sFlags[3] = it + 1;
+        if (it >= vstages && !mbar_wait(vempty0 + 8u * vs, ((it / vstages) - 1) & 1, timed_out, p.status)) break;
+        mbar_arrive_expect_tx(vfull0 + 8u * vs, TILE_BYTES);
+#pragma unroll
+        for (int hf = 0; hf < DH; ++hf)
+          tma_load_3d(smem_u32(sV + (size_t)vs * TILE_BYTES + hf * kTile2 * 128), &vmap, hf * 128, row, c.layer, vfull0 + 8u * vs);
+        sFlags[4] = it + 1;
+        if (++c.tile == c.tiles_b) {
+          seg_start = true;
+          if (idx + 1 < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+        }
+      }
+      sFlags[5] = seg;
+    }
+  } else if (warp == kEpilogueWarp) {
+    if (has_work)
+      epilogue_warp<D, 1, 1>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+  } else if (warp == kIssuer2) {
+    // ===================== issuer warp: query operand, both tcgen05.mma products =====================
+    if (has_work) {
+      Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+      const int total_it = (int)(r1 - r0);
+      int seg = 0, qb = 0;
+      bool seg_start = true, alive = true;
+      uint32_t first_mask = 0;   // bit (it & 1): tile `it` is the first of its pair segment
+      // P V for tile j: waits for the probability operand and the V tile
+      auto issue_pv = [&](int j) {
+        const int pb = j & 1, vs = j % vstages;
+        if (!mbar_wait(pfull0 + 8u * pb, (j >> 1) & 1, timed_out, p.status)) { alive = false; return; }
+        if (!mbar_wait(vfull0 + 8u * vs, (j / vstages) & 1, timed_out, p.status)) { alive = false; return; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a0 = smem_u32(sV + (size_t)vs * TILE_BYTES), b0 = smem_u32(sPop + pb * POP_BYTES);
+#pragma unroll
+          for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb)   // 32 tokens per instruction: 32 rows of 128 bytes further in V, 32 bytes further in P
+              umma_f8(tmem_base + 32u + 16u * hf, smem_desc_k128(a0 + hf * kTile2 * 128 + kb * 4096),
+                      smem_desc_k128(b0 + kb * 32), kIdescPV, (kb || !((first_mask >> pb) & 1u)) ? 1u : 0u);
+          umma_commit(pvdone0 + 8u * pb);    // O holds tile j; probability operand pb is free
+          umma_commit(vempty0 + 8u * vs);    // V tile has been read
+        }
+        __syncwarp();
+      };
+      int it = 0;
+      for (; it < total_it && alive; ++it) {
+        const int sb = it & 1;
+        if (it >= 2) alive = mbar_wait(sempty0 + 8u * sb, ((it >> 1) - 1) & 1, timed_out, p.status);
+        if (alive && seg_start) {
+          qb = seg & 1;
+          alive = mbar_wait(qrfull0 + 8u * qb, (seg >> 1) & 1, timed_out, p.status);
+          if (alive) {
+            const uint32_t qraw = smem_u32(sQraw + qb * q_bytes), qop = smem_u32(sQop + qb * QOP_BYTES);
+            for (int h = 0; h < G; ++h) {
+              float x[DH][4];
+              float amax = 0.f;
+#pragma unroll
+              for (int hf = 0; hf < DH; ++hf) {
+                uint32_t w0 = lds32(qraw + (h * D + hf * 128 + 4 * lane) * 2);
+                uint32_t w1 = lds32(qraw + (h * D + hf * 128 + 4 * lane) * 2 + 4);
+                x[hf][0] = bf16_bits_to_float(w0 & 0xFFFFu); x[hf][1] = bf16_bits_to_float(w0 >> 16);
+                x[hf][2] = bf16_bits_to_float(w1 & 0xFFFFu); x[hf][3] = bf16_bits_to_float(w1 >> 16);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(x[hf][i]));
+              }
+#pragma unroll
+              for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+              int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF);
+              ex = ex < 1 ? 127 : (ex < 8 ? 8 : (ex > 253 ? 253 : ex));
+              const float down = __uint_as_float((uint32_t)(261 - ex) << 23);   // 2^(134-ex): largest |q| into [128, 256)
+              const float up = __uint_as_float((uint32_t)(ex - 7) << 23);
+#pragma unroll
+              for (int hf = 0; hf < DH; ++hf) {
+                const float x0 = x[hf][0] * down, x1 = x[hf][1] * down, x2 = x[hf][2] * down, x3 = x[hf][3] * down;
+                const float h0 = e4m3_head(x0), h1 = e4m3_head(x1), h2 = e4m3_head(x2), h3 = e4m3_head(x3);
+                const uint32_t whi = pack_e4m3x2(h0, h1) | (pack_e4m3x2(h2, h3) << 16);
+                const uint32_t wlo = pack_e4m3x2(x0 - h0, x1 - h1) | (pack_e4m3x2(x2 - h2, x3 - h3) << 16);
+                const uint32_t off = (uint32_t)hf * 2048u + ((((uint32_t)lane >> 2) ^ (uint32_t)(h & 7)) << 4) + ((4u * lane) & 15u);
+                sts32(qop + off + (uint32_t)h * 128u, whi);
+                sts32(qop + off + (uint32_t)(8 + h) * 128u, wlo);
+              }
+              if (lane == 0) sScale[qb * 8 + h] = up * p.k_scale[c.layer * g.h_kv + c.h] * p.score_scale;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(qrempty0 + 8u * qb);
+              mbar_arrive(qinfo0 + 8u * qb);
+            }
+          }
+          ++seg;
+        }
+        first_mask = (first_mask & ~(1u << sb)) | ((seg_start ? 1u : 0u) << sb);
+        seg_start = false;
+        const int ks = it % kKStages2;
+        if (alive) alive = mbar_wait(kfull0 + 8u * ks, (it / kKStages2) & 1, timed_out, p.status);
+        if (alive) {
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a0 = smem_u32(sK + (size_t)ks * TILE_BYTES), b0 = smem_u32(sQop + qb * QOP_BYTES);
+            const uint32_t d = tmem_base + (uint32_t)sb * 16u;
+#pragma unroll
+            for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+              for (int kb = 0; kb < 4; ++kb)
+                umma_f8(d, smem_desc_k128(a0 + hf * kTile2 * 128 + kb * 32), smem_desc_k128(b0 + hf * 2048 + kb * 32),
+                        kIdescQK, (hf | kb) ? 1u : 0u);
+            umma_commit(sfull0 + 8u * sb);
+            umma_commit(kempty0 + 8u * ks);
+          }
+          __syncwarp();
+          if (lane == 0) sFlags[6] = it + 1;   // score MMAs issued
+          if (it >= 1) { issue_pv(it - 1); if (lane == 0 && alive) sFlags[7] = it; }
+        }
+        if (++c.tile == c.tiles_b) {
+          seg_start = true;
+          if (it + 1 < total_it) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+        }
+      }
+      if (alive && total_it > 0) { issue_pv(total_it - 1); if (lane == 0 && alive) sFlags[7] = total_it; }
+    }
+  } else if (has_work) {
+    // ================================ softmax warps: one thread = one token / one output dim ================================
+    Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+    long long cur = r0;
+    int it = 0, seg = 0;
+    const int tok_in_tile = warp * 32 + lane;
+    const uint32_t tmem_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t sV_addr = smem_u32(sV);
+
+    while (cur < r1) {
+      const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
+      const long long seg_end = pair_end < r1 ? pair_end : r1;
+      const int ntiles = (int)(seg_end - cur);
+      const int qb = seg & 1;
+      float sc[kMaxGroup];
+      {
+        const bool ok = mbar_wait(qinfo0 + 8u * qb, (seg >> 1) & 1, timed_out, p.status);
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h) sc[h] = (ok && h < G) ? sScale[qb * 8 + h] : 0.f;
+      }
+      float mref[kMaxGroup], l[kMaxGroup];
+#pragma unroll
+      for (int h = 0; h < kMaxGroup; ++h) { mref[h] = -INFINITY; l[h] = 0.f; }
+
+      for (int ti = 0; ti < ntiles; ++ti, ++it) {
+        const int sb = it & 1, pb = it & 1, vs = it % vstages;
+        const int tile_tok0 = (c.tile + ti) * kTile2;
+        const bool sok = mbar_wait(sfull0 + 8u * sb, (it >> 1) & 1, timed_out, p.status);
+        uint32_t r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = 0;
+        if (sok) {
+          tc_fence_after();
+          tmem_ld16(tmem_lane + (uint32_t)sb * 16u, r);
+          tc_fence_before();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sempty0 + 8u * sb);
+        const bool valid = sok && tile_tok0 + tok_in_tile < c.len_b;
+        // scores and the tile maximum per head (CTA-wide)
+        float s[kMaxGroup];
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h) {
+          s[h] = -INFINITY;
+          if (h < G) {
+            if (valid) s[h] = (__uint_as_float(r[h]) + __uint_as_float(r[8 + h])) * sc[h];
+            const float wm = warp_max(s[h]);
+            if (lane == 0) sWmax[((it & 1) * 4 + warp) * 8 + h] = wm;
+          }
+        }
+        bar_softmax();
+        bool rescale = false;
+        float alpha[kMaxGroup];
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h) {
+          alpha[h] = 1.f;
+          if (h < G) {
+            const float* wm = sWmax + (it & 1) * 32 + h;
+            const float tmax = fmaxf(fmaxf(wm[0], wm[8]), fmaxf(wm[16], wm[24]));
+            if (tmax > mref[h] + kTau || mref[h] == -INFINITY) {   // the reference moves (always on the first tile)
+              alpha[h] = mref[h] == -INFINITY ? 0.f : ex2(mref[h] - tmax);
+              rescale |= mref[h] != -INFINITY;
+              mref[h] = tmax;
+              l[h] *= alpha[h];
+            }
+          }
+        }
+        if (rescale) {
+          // O *= alpha per head, in tensor memory: thread = dim row; needs the previous tile's P V finished
+          if (mbar_wait(pvdone0 + 8u * ((it - 1) & 1), ((it - 1) >> 1) & 1, timed_out, p.status)) {
+            tc_fence_after();
+#pragma unroll
+            for (int hf = 0; hf < DH; ++hf) {
+              uint32_t o[16];
+              tmem_ld16(tmem_lane + 32u + 16u * hf, o);
+#pragma unroll
+              for (int h = 0; h < 5; ++h)
+#pragma unroll
+                for (int t = 0; t < 3; ++t) o[3 * h + t] = __float_as_uint(__uint_as_float(o[3 * h + t]) * alpha[h]);
+              tmem_st16(tmem_lane + 32u + 16u * hf, o);
+            }
+            tc_fence_before();
+          }
+        }
+        // probabilities: p <= 2^kTau; p * 2^13 as three e5m2 terms
+        uint32_t bytes[15];
+#pragma unroll
+        for (int h = 0; h < 5; ++h) {
+          float pr = 0.f;
+          if (h < G && valid) pr = ex2(s[h] - mref[h]);
+          l[h] += pr;
+          const float q = pr * kPScale;
+          const float t1 = e5m2_head(q), r1f = q - t1, t2 = e5m2_head(r1f), t3 = r1f - t2;
+          const uint32_t b12 = pack_e5m2x2(t1, t2), b3 = pack_e5m2x2(t3, 0.f);
+          bytes[3 * h] = b12 & 0xFFu; bytes[3 * h + 1] = b12 >> 8; bytes[3 * h + 2] = b3 & 0xFFu;
+        }
+        // the probability operand buffer is free once the P V of two tiles ago has completed
+        bool pok = true;
+        if (it >= 2) pok = mbar_wait(pvdone0 + 8u * pb, ((it >> 1) - 1) & 1, timed_out, p.status);
+        const bool partial = tile_tok0 + kTile2 > c.len_b;
+        const bool vok = partial && mbar_wait(vfull0 + 8u * vs, (it / vstages) & 1, timed_out, p.status);
+        if (pok) {
+          const uint32_t pop = smem_u32(sPop + pb * POP_BYTES);
+          const uint32_t col = ((uint32_t)(tok_in_tile >> 4) << 4), within = (uint32_t)tok_in_tile & 15u;
+#pragma unroll
+          for (int n = 0; n < 15; ++n)
+            sts8(pop + n * 128 + (col ^ ((uint32_t)(n & 7) << 4)) + within, bytes[n]);
+          sts8(pop + 15 * 128 + (col ^ (7u << 4)) + within, 0u);   // unused 16th row: keep it finite
+        }
+        if (vok && !valid) {
+          // this token slot is at or beyond the valid length: its V row may hold anything (NaN patterns
+          // included) and 0 * NaN would poison O: zero the row in shared memory before the product
+#pragma unroll
+          for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              sts128z(sV_addr + vs * TILE_BYTES + hf * kTile2 * 128 + tok_in_tile * 128 + ch * 16);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand bytes -> visible to the tensor core
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pfull0 + 8u * pb);
+      }
+
+      // ---------------- end of segment: read O once, hand one state to the epilogue warp ----------------
+      const int last = it - 1;
+      const bool ook = mbar_wait(pvdone0 + 8u * (last & 1), (last >> 1) & 1, timed_out, p.status);
+#pragma unroll
+      for (int h = 0; h < 5; ++h) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], off);
+        if (lane == 0) sWl[warp * 8 + h] = l[h];
+      }
+      const bool dok = seg < 1 || mbar_wait(dempty0, (seg - 1) & 1, timed_out, p.status);
+      bar_softmax();
+      if (ook && dok) {
+        tc_fence_after();
+#pragma unroll
+        for (int hf = 0; hf < DH; ++hf) {
+          uint32_t o[16];
+          tmem_ld16(tmem_lane + 32u + 16u * hf, o);
+#pragma unroll
+          for (int h = 0; h < 5; ++h)
+            if (h < G)
+              sDump[h * DP + hf * 128 + tok_in_tile] =
+                  (__uint_as_float(o[3 * h]) + __uint_as_float(o[3 * h + 1]) + __uint_as_float(o[3 * h + 2])) * (1.f / kPScale);
+        }
+        tc_fence_before();
+        if (tid < 5) {
+          sML[tid] = mref[tid];
+          sML[8 + tid] = sWl[tid] + sWl[8 + tid] + sWl[16 + tid] + sWl[24 + tid];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dfull0);
+      bar_softmax();   // sWl / sWmax reuse by the next segment
+      ++seg;
+      cur = seg_end;
+      if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kIssuer2) {
+    if (sFlags[0] && lane == 0) {
+      // A wait gave up: wait (bounded) for everything already issued into this CTA's shared / tensor memory.
+      auto drain = [&](uint32_t bar0, int ring, int issued) {
+        for (int s = 0; s < ring && s < issued; ++s) {
+          const int lastu = ((issued - 1 - s) / ring) * ring + s;
+          const unsigned long long t0 = global_timer_ns();
+          while (!mbar_try_wait(bar0 + 8u * s, (lastu / ring) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
+        }
+      };
+      drain(kfull0, kKStages2, sFlags[3]);
+      drain(vfull0, vstages, sFlags[4]);
+      drain(qrfull0, 2, sFlags[5]);
+      drain(sfull0, 2, sFlags[6]);
+      drain(pvdone0, 2, sFlags[7]);
+    }
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols2);
+  }
+}
+
+int vstages2_for(const Geometry& g) { return g.head_dim == 128 ? 3 : 2; }
+
+size_t umma2_smem_bytes(const Geometry& g, int vstages) {
+  const int dh = g.head_dim / 128;
+  size_t b = 1024;
+  b += (size_t)(kKStages2 + vstages) * kTile2 * g.head_dim;         // K and V rings
+  b += (size_t)2 * dh * 16 * 128;                                   // query operand
+  b += (size_t)2 * 16 * 128;                                        // probability operand
+  b += (size_t)2 * g.group * g.head_dim * 2;                        // raw query rows
+  b += (16 + 64 + 32) * 4;                                          // scales, per-warp maxima and sums
+  b += (size_t)g.group * (g.head_dim + 4) * 4 + 64;                 // the dumped state and its m, l
+  b += (size_t)(2 * kKStages2 + 16 + 2 * vstages) * 8;              // barriers
+  b += 32;                                                          // flags
+  b += (size_t)(2 * g.batch + 1) * 4;
+  return (b + 15) & ~(size_t)15;
+}
+
+}  // namespace
+
+bool umma2_supported(const Geometry& g) { return g.group <= 5; }
+
+int umma2_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
+  (void)max_seq_len;
+  const size_t smem = umma2_smem_bytes(g, vstages2_for(g));
+  int per_sm = (int)((227 * 1024) / (smem + 1024));
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 2) per_sm = 2;
+  return num_sms * per_sm;
+}
+
+cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStream_t stream) {
+  if (g.scale_mode != B200ATTN_SCALE_PER_HEAD || g.batch > kMaxBatchMma || !umma2_supported(g)) return cudaErrorNotSupported;
+  CUtensorMap kmap, vmap;
+  if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride, kTile2) ||
+      !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride, kTile2))
+    return cudaErrorInvalidValue;
+  MmaParams p;
+  p.g = g;
+  p.q = (const uint16_t*)a.q;
+  p.k_scale = a.k_scale;
+  p.v_scale = a.v_scale;
+  p.seq_len = a.seq_len;
+  p.seq_len_offset = a.seq_len_offset;
+  p.score_scale = a.softmax_scale * kLog2e;
+  const int n = a.num_splits;
+  p.ws_acc = (float*)a.workspace;
+  p.ws_ml = p.ws_acc + (size_t)n * 2 * g.group * g.head_dim;
+  p.tickets = (int*)(p.ws_ml + (size_t)n * 2 * 16);
+  p.out = (uint16_t*)a.out;
+  p.gate = (const uint16_t*)a.gate;
+  p.n_out = a.n_out;
+  p.out_hq_total = a.n_out ? a.out_hq_total : g.h_q;
+  p.out_head_base = a.n_out ? a.out_head_base : 0;
+  for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
+  p.status = a.status;
+  p.stages = vstages2_for(g);
+  const size_t smem = umma2_smem_bytes(g, p.stages);
+  auto launch = [&](auto kernel) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<n, kThreads2, smem, stream>>>(kmap, vmap, p);
+    return cudaGetLastError();
+  };
+  return g.head_dim == 128 ? launch(attn_streamk_umma2_kernel<128>) : launch(attn_streamk_umma2_kernel<256>);
+}
+
+}  // namespace b200attn

@@ -260,12 +260,13 @@ __device__ __forceinline__ void store_out(const MmaParams& p, long long idx, lon
 
 // ---------------------------------------------------------------------------------------------
 // epilogue warp: walks the CTA's segments in the consumers' order.  For each it waits for the
-// four dumped warp states (m[8], l[8], acc[G][D] in the xor layout of dump_pos), merges them,
+// NW dumped states (m[8], l[8], acc[G][D]; four warp states in the xor layout of dump_pos, or one
+// CTA-wide state in plain order), merges them,
 // and either writes the normalised bf16 output (pair fully owned by this CTA) or writes an
 // (m, l, acc) partial, takes an arrival ticket and, if it is the last owner to arrive, merges all
 // partials of the pair in CTA order and resets the ticket.
 // ---------------------------------------------------------------------------------------------
-template <int D, int NDUMP>
+template <int D, int NDUMP, int NW = kConsumerWarps>
 __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long long r0, long long r1,
                                               long long total, int n_eff, const int* sCum, const int* sLen,
                                               const float* sDump, const float* sML, uint32_t dfull0,
@@ -288,8 +289,8 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     const float vs = p.v_scale[c.layer * g.h_kv + c.h];
     const int db = seg % NDUMP;
     const bool ok = mbar_wait(dfull0 + 8u * db, (seg / NDUMP) & 1, timed_out, p.status);
-    const float* dump = sDump + db * kConsumerWarps * dump_warp_floats;
-    const float* ml = sML + db * kConsumerWarps * 16;
+    const float* dump = sDump + db * NW * dump_warp_floats;
+    const float* ml = sML + db * NW * 16;
     const int slot = cur == r0 ? 0 : 1;
     float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
     float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
@@ -297,19 +298,19 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     const long long prow = (lb * p.out_hq_total + p.out_head_base + c.h * G) * D;   // row in the gathered layout
     if (ok) {
       for (int h = 0; h < G; ++h) {
-        float mw[kConsumerWarps], M = -INFINITY;
+        float mw[NW], M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) { mw[w] = ml[w * 16 + h]; M = fmaxf(M, mw[w]); }
+        for (int w = 0; w < NW; ++w) { mw[w] = ml[w * 16 + h]; M = fmaxf(M, mw[w]); }
         float ll = 0.f, ax[UR], ay[UR];
 #pragma unroll
         for (int r = 0; r < UR; ++r) { ax[r] = 0.f; ay[r] = 0.f; }
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) {
+        for (int w = 0; w < NW; ++w) {
           const float f = mw[w] == -INFINITY ? 0.f : ex2(mw[w] - M);
           ll += ml[w * 16 + 8 + h] * f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            const float2 v = *reinterpret_cast<const float2*>(dump + w * dump_warp_floats + h * DP + 2 * dump_pos(lane + 32 * r));
+            const float2 v = *reinterpret_cast<const float2*>(dump + w * dump_warp_floats + h * DP + 2 * (NW == 1 ? lane + 32 * r : dump_pos(lane + 32 * r)));
             ax[r] += v.x * f;
             ay[r] += v.y * f;
           }
