@@ -7,8 +7,10 @@
 //      128-byte-swizzle layout is the K-major canonical operand layout; the query is the B operand
 //      as two e4m3 rows per head (leading part + remainder = the bf16 value exactly); scores land
 //      in tensor memory (two buffers);
-//   2. four softmax warps, one thread per token: tcgen05.ld of the token's scores, one CTA-wide
-//      running reference maximum per head (redux.sync per warp + a shared-memory exchange), p =
+//   2. eight softmax warps in two groups of four; a group owns the tiles of one parity with its own
+//      score buffer, probability operand, running state and output accumulator, so two tiles are
+//      in flight per CTA.  One thread per token: tcgen05.ld of the token's scores, one group-wide
+//      reference maximum per head (redux.sync per warp + a shared-memory exchange), p =
 //      2^(s - m_ref).  The reference only moves when a tile's maximum exceeds it by more than
 //      kTau (lazy rescale: p stays <= 2^kTau), so the accumulator in tensor memory is rescaled
 //      (tcgen05.ld -> multiply -> tcgen05.st) only in the first tiles of a pair;
@@ -17,11 +19,11 @@
 //      precision class of the reference's bf16 P, with e5m2's range down to 2^-29 of the
 //      reference) into a 16-row x 128-token shared-memory operand (rows 3h..3h+2 for head h);
 //   4. issuer warp: O[128 dims x 16] += V^T P^T with tcgen05.mma, A = the V tile read MN-major
-//      (its swizzled [token][dim] layout is the MN-major canonical layout), accumulating in tensor
-//      memory over the whole pair; rows beyond the valid length are zeroed in shared memory first
-//      (their bytes may be NaN patterns);
-//   5. at the end of a pair the softmax warps read O once (one thread per dim), add the three
-//      terms per head, and hand ONE state (m, l, acc) to the epilogue warp.
+//      (its swizzled [token][dim] layout is the MN-major canonical layout), accumulating in the
+//      group's tensor-memory accumulator over the whole pair; rows beyond the valid length are
+//      zeroed in shared memory first (their bytes may be NaN patterns);
+//   5. at the end of a pair each group reads its O once (one thread per dim), adds the three
+//      terms per head, and hands its state (m, l, acc) to the epilogue warp, which merges the two.
 // G <= 5 query heads per KV head (3 G <= 16 operand rows).
 //
 // All waits are bounded as in the other kernels; tensor memory is allocated by the issuer warp at
@@ -33,10 +35,12 @@ namespace b200attn {
 namespace {
 
 constexpr int kTile2 = 128;
-constexpr int kIssuer2 = kConsumerWarps + 2;       // warp 6
-constexpr int kThreads2 = kConsumerThreads + 96;
+constexpr int kSoftmaxWarps2 = 8;                  // two groups of four; a group owns the tiles of one parity
+constexpr int kProducer2 = kSoftmaxWarps2;         // warp 8: TMA issue
+constexpr int kEpilogue2 = kSoftmaxWarps2 + 1;     // warp 9: merge, output, fused combine
+constexpr int kIssuer2 = kSoftmaxWarps2 + 2;       // warp 10: query operand, tcgen05.mma issue, tensor memory owner
+constexpr int kThreads2 = (kSoftmaxWarps2 + 3) * 32;
 constexpr int kKStages2 = 2;
-constexpr int kTmemCols2 = 64;                     // S: 2 x 16, O: 16 per 128 dims (<= 32)
 constexpr float kTau = 2.0f;                       // lazy-rescale threshold, log2 units
 constexpr float kPScale = 8192.f;                  // 2^13: p * 2^13 <= 2^15 < 57344 (e5m2 max)
 
@@ -64,10 +68,14 @@ __device__ __forceinline__ void sts8(uint32_t addr, uint32_t v) {
 __device__ __forceinline__ void sts128z(uint32_t addr) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
 }
-__device__ __forceinline__ void bar_softmax() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+// Named barrier of one softmax group (128 threads): ids 1 and 2.
+__device__ __forceinline__ void bar_group(int grp) {
+  if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
 
 template <int D>
-__global__ void __launch_bounds__(kThreads2)
+__global__ void __launch_bounds__(kThreads2, D == 128 ? 2 : 1)
 attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                           const MmaParams p) {
   constexpr int DH = D / 128;
@@ -75,6 +83,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   constexpr int DP = D + 4;
   constexpr int QOP_BYTES = DH * 16 * 128;   // query operand
   constexpr int POP_BYTES = 16 * 128;        // probability operand: 16 rows x 128 tokens
+  constexpr uint32_t O_COL0 = 32;            // tensor memory: S of group 0 | S of group 1 | O of group 0 | O of group 1
+  constexpr uint32_t TMEM_COLS = D == 128 ? 64 : 128;
   const Geometry& g = p.g;
   const int G = g.group;
   const int vstages = p.stages;
@@ -87,14 +97,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   uint8_t* sK = smem;                                                   // [2][TILE_BYTES]
   uint8_t* sV = sK + (size_t)kKStages2 * TILE_BYTES;                    // [vstages][TILE_BYTES]
   uint8_t* sQop = sV + (size_t)vstages * TILE_BYTES;                    // [2][QOP_BYTES]
-  uint8_t* sPop = sQop + 2 * QOP_BYTES;                                 // [2][POP_BYTES], 1024-aligned
+  uint8_t* sPop = sQop + 2 * QOP_BYTES;                                 // [2 groups][POP_BYTES], 1024-aligned
   uint8_t* sQraw = sPop + 2 * POP_BYTES;                                // [2][G*D] bf16
   float* sScale = reinterpret_cast<float*>(sQraw + 2 * q_bytes);        // [2][8]
-  float* sWmax = sScale + 16;                                           // [2][4][8] per-warp tile maxima
-  float* sWl = sWmax + 64;                                              // [4][8] per-warp sums
-  float* sDump = sWl + 32;                                              // [G][DP], one CTA-wide state
-  float* sML = sDump + G * DP;                                          // [16]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + 16);
+  float* sWmax = sScale + 16;                                           // [2 groups][2][4 warps][8] tile maxima
+  float* sWl = sWmax + 128;                                             // [2 groups][4 warps][8] sums
+  float* sDump = sWl + 64;                                              // [2 groups][G][DP]
+  float* sML = sDump + 2 * G * DP;                                      // [2 groups][16]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + 32);
   const uint32_t kfull0 = smem_u32(bars), kempty0 = kfull0 + 8u * kKStages2;
   const uint32_t vfull0 = kempty0 + 8u * kKStages2, vempty0 = vfull0 + 8u * vstages;
   const uint32_t qrfull0 = vempty0 + 8u * vstages, qrempty0 = qrfull0 + 16u;
@@ -115,11 +125,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       mbar_init(qrempty0 + 8u * i, 1);
       mbar_init(qinfo0 + 8u * i, 1);
       mbar_init(sfull0 + 8u * i, 1);
-      mbar_init(sempty0 + 8u * i, kConsumerWarps);
-      mbar_init(pfull0 + 8u * i, kConsumerWarps);
+      mbar_init(sempty0 + 8u * i, 4);     // the four warps of softmax group i
+      mbar_init(pfull0 + 8u * i, 4);
       mbar_init(pvdone0 + 8u * i, 1);
     }
-    mbar_init(dfull0, kConsumerWarps);
+    mbar_init(dfull0, kSoftmaxWarps2);
     mbar_init(dempty0, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -139,11 +149,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     sFlags[2] = any_empty | (uniform ? 2 : 0);
     if (st && blockIdx.x == 0) atomicOr(p.status, st);
   }
-  if (warp == kProducerWarp && lane == 0) {
+  if (warp == kProducer2 && lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
   }
-  if (warp == kIssuer2) tmem_alloc(smem_u32(sFlags + 1), kTmemCols2);
+  if (warp == kIssuer2) tmem_alloc(smem_u32(sFlags + 1), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -168,7 +178,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   cta_range(total, (int)gridDim.x, (int)blockIdx.x, (sFlags[2] & 2) ? sCum[1] - sCum[0] : 0, n_eff, r0, r1);
   const bool has_work = r0 < r1;
 
-  if (warp == kProducerWarp) {
+  if (warp == kProducer2) {
     // ===================== producer warp: one elected lane issues the copies =====================
     if (lane == 0 && has_work) {
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
@@ -205,18 +215,18 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       }
       sFlags[5] = seg;
     }
-  } else if (warp == kEpilogueWarp) {
+  } else if (warp == kEpilogue2) {
     if (has_work)
-      epilogue_warp<D, 1, 1>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+      epilogue_warp<D, 1, 2, true>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
   } else if (warp == kIssuer2) {
     // ===================== issuer warp: query operand, both tcgen05.mma products =====================
     if (has_work) {
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
       const int total_it = (int)(r1 - r0);
-      int seg = 0, qb = 0;
+      int seg = 0, qb = 0, seg_pos = 0;
       bool seg_start = true, alive = true;
-      uint32_t first_mask = 0;   // bit (it & 1): tile `it` is the first of its pair segment
-      // P V for tile j: waits for the probability operand and the V tile
+      uint32_t fresh_mask = 0;   // bit (it & 1): tile `it` is its group's first of the segment (accumulator starts over)
+      // P V for tile j (group j & 1): waits for the probability operand and the V tile
       auto issue_pv = [&](int j) {
         const int pb = j & 1, vs = j % vstages;
         if (!mbar_wait(pfull0 + 8u * pb, (j >> 1) & 1, timed_out, p.status)) { alive = false; return; }
@@ -224,12 +234,13 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         tc_fence_after();
         if (lane == 0) {
           const uint32_t a0 = smem_u32(sV + (size_t)vs * TILE_BYTES), b0 = smem_u32(sPop + pb * POP_BYTES);
+          const uint32_t d0 = tmem_base + O_COL0 + (uint32_t)pb * 16u * DH;
 #pragma unroll
           for (int hf = 0; hf < DH; ++hf)
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb)   // 32 tokens per instruction: 32 rows of 128 bytes further in V, 32 bytes further in P
-              umma_f8(tmem_base + 32u + 16u * hf, smem_desc_k128(a0 + hf * kTile2 * 128 + kb * 4096),
-                      smem_desc_k128(b0 + kb * 32), kIdescPV, (kb || !((first_mask >> pb) & 1u)) ? 1u : 0u);
+              umma_f8(d0 + 16u * hf, smem_desc_k128(a0 + hf * kTile2 * 128 + kb * 4096),
+                      smem_desc_k128(b0 + kb * 32), kIdescPV, (kb || !((fresh_mask >> pb) & 1u)) ? 1u : 0u);
           umma_commit(pvdone0 + 8u * pb);    // O holds tile j; probability operand pb is free
           umma_commit(vempty0 + 8u * vs);    // V tile has been read
         }
@@ -243,6 +254,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           qb = seg & 1;
           alive = mbar_wait(qrfull0 + 8u * qb, (seg >> 1) & 1, timed_out, p.status);
           if (alive) {
+            // Each head h: row h = leading e4m3 part of q * 2^e, row 8+h = remainder; lane owns 4 dims
+            // per 128-dim block.  2^e puts the head's largest |q| into [128, 256).
             const uint32_t qraw = smem_u32(sQraw + qb * q_bytes), qop = smem_u32(sQop + qb * QOP_BYTES);
             for (int h = 0; h < G; ++h) {
               float x[DH][4];
@@ -259,31 +272,34 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
 #pragma unroll
               for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
               int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF);
-              ex = ex < 1 ? 127 : (ex < 8 ? 8 : (ex > 253 ? 253 : ex));
-              const float down = __uint_as_float((uint32_t)(261 - ex) << 23);   // 2^(134-ex): largest |q| into [128, 256)
-              const float up = __uint_as_float((uint32_t)(ex - 7) << 23);
+              ex = ex < 1 ? 127 : (ex < 8 ? 8 : (ex > 253 ? 253 : ex));   // zero / denormal / inf / NaN: no rescale worth doing
+              const float down = __uint_as_float((uint32_t)(261 - ex) << 23);   // 2^(134-ex)
+              const float up = __uint_as_float((uint32_t)(ex - 7) << 23);       // 2^(ex-134)
 #pragma unroll
               for (int hf = 0; hf < DH; ++hf) {
                 const float x0 = x[hf][0] * down, x1 = x[hf][1] * down, x2 = x[hf][2] * down, x3 = x[hf][3] * down;
                 const float h0 = e4m3_head(x0), h1 = e4m3_head(x1), h2 = e4m3_head(x2), h3 = e4m3_head(x3);
                 const uint32_t whi = pack_e4m3x2(h0, h1) | (pack_e4m3x2(h2, h3) << 16);
                 const uint32_t wlo = pack_e4m3x2(x0 - h0, x1 - h1) | (pack_e4m3x2(x2 - h2, x3 - h3) << 16);
+                // 128-byte swizzle: 16-byte chunk index xor (row & 7); rows h and 8+h share (row & 7)
                 const uint32_t off = (uint32_t)hf * 2048u + ((((uint32_t)lane >> 2) ^ (uint32_t)(h & 7)) << 4) + ((4u * lane) & 15u);
                 sts32(qop + off + (uint32_t)h * 128u, whi);
                 sts32(qop + off + (uint32_t)(8 + h) * 128u, wlo);
               }
               if (lane == 0) sScale[qb * 8 + h] = up * p.k_scale[c.layer * g.h_kv + c.h] * p.score_scale;
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand bytes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) {
-              mbar_arrive(qrempty0 + 8u * qb);
-              mbar_arrive(qinfo0 + 8u * qb);
+              mbar_arrive(qrempty0 + 8u * qb);   // raw query buffer may be refilled
+              mbar_arrive(qinfo0 + 8u * qb);     // scales are in place for the softmax warps
             }
           }
           ++seg;
+          seg_pos = 0;
         }
-        first_mask = (first_mask & ~(1u << sb)) | ((seg_start ? 1u : 0u) << sb);
+        fresh_mask = (fresh_mask & ~(1u << sb)) | ((seg_pos < 2 ? 1u : 0u) << sb);
+        ++seg_pos;
         seg_start = false;
         const int ks = it % kKStages2;
         if (alive) alive = mbar_wait(kfull0 + 8u * ks, (it / kKStages2) & 1, timed_out, p.status);
@@ -298,11 +314,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
               for (int kb = 0; kb < 4; ++kb)
                 umma_f8(d, smem_desc_k128(a0 + hf * kTile2 * 128 + kb * 32), smem_desc_k128(b0 + hf * 2048 + kb * 32),
                         kIdescQK, (hf | kb) ? 1u : 0u);
-            umma_commit(sfull0 + 8u * sb);
-            umma_commit(kempty0 + 8u * ks);
+            umma_commit(sfull0 + 8u * sb);     // scores of this tile are complete
+            umma_commit(kempty0 + 8u * ks);    // and the K tile has been read
+            sFlags[6] = it + 1;                // score MMAs issued
           }
           __syncwarp();
-          if (lane == 0) sFlags[6] = it + 1;   // score MMAs issued
           if (it >= 1) { issue_pv(it - 1); if (lane == 0 && alive) sFlags[7] = it; }
         }
         if (++c.tile == c.tiles_b) {
@@ -313,13 +329,22 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       if (alive && total_it > 0) { issue_pv(total_it - 1); if (lane == 0 && alive) sFlags[7] = total_it; }
     }
   } else if (has_work) {
-    // ================================ softmax warps: one thread = one token / one output dim ================================
+    // ============ softmax warps: two groups of four; group = tile parity; one thread = one token / one output dim ============
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
     long long cur = r0;
-    int it = 0, seg = 0;
-    const int tok_in_tile = warp * 32 + lane;
-    const uint32_t tmem_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+    int it0 = 0, seg = 0;
+    const int grp = warp >> 2, wq = warp & 3;
+    const int tok_in_tile = wq * 32 + lane;
+    const uint32_t tmem_lane = tmem_base + ((uint32_t)(wq * 32) << 16);
+    const uint32_t tmem_s = tmem_lane + (uint32_t)grp * 16u;
+    const uint32_t tmem_o = tmem_lane + O_COL0 + (uint32_t)grp * 16u * DH;
+    const uint32_t sfull = sfull0 + 8u * grp, sempty = sempty0 + 8u * grp, pfull = pfull0 + 8u * grp, pvdone = pvdone0 + 8u * grp;
+    const uint32_t pop = smem_u32(sPop + grp * POP_BYTES);
+    const uint32_t pcol = ((uint32_t)(tok_in_tile >> 4) << 4), pwithin = (uint32_t)tok_in_tile & 15u;
     const uint32_t sV_addr = smem_u32(sV);
+    float* wmax = sWmax + grp * 64;
+    float* wl = sWl + grp * 32;
+    float* dump = sDump + grp * G * DP;
 
     while (cur < r1) {
       const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
@@ -332,46 +357,49 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
 #pragma unroll
         for (int h = 0; h < kMaxGroup; ++h) sc[h] = (ok && h < G) ? sScale[qb * 8 + h] : 0.f;
       }
-      float mref[kMaxGroup], l[kMaxGroup];
+      float mref[5], l[5];
 #pragma unroll
-      for (int h = 0; h < kMaxGroup; ++h) { mref[h] = -INFINITY; l[h] = 0.f; }
+      for (int h = 0; h < 5; ++h) { mref[h] = -INFINITY; l[h] = 0.f; }
 
-      for (int ti = 0; ti < ntiles; ++ti, ++it) {
-        const int sb = it & 1, pb = it & 1, vs = it % vstages;
-        const int tile_tok0 = (c.tile + ti) * kTile2;
-        const bool sok = mbar_wait(sfull0 + 8u * sb, (it >> 1) & 1, timed_out, p.status);
+      const int jfirst = it0 + ((it0 ^ grp) & 1);   // this group's tiles: CTA-wide tile index j with (j & 1) == grp
+      int jlast = -1;
+      for (int j = jfirst; j < it0 + ntiles; j += 2) {
+        jlast = j;
+        const int vs = j % vstages;
+        const int tile_tok0 = (c.tile + (j - it0)) * kTile2;
+        const bool sok = mbar_wait(sfull, (j >> 1) & 1, timed_out, p.status);
         uint32_t r[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) r[i] = 0;
         if (sok) {
           tc_fence_after();
-          tmem_ld16(tmem_lane + (uint32_t)sb * 16u, r);
+          tmem_ld16(tmem_s, r);
           tc_fence_before();
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(sempty0 + 8u * sb);
+        if (lane == 0) mbar_arrive(sempty);
         const bool valid = sok && tile_tok0 + tok_in_tile < c.len_b;
-        // scores and the tile maximum per head (CTA-wide)
-        float s[kMaxGroup];
+        // scores and the tile maximum per head (over the group's 128 tokens)
+        float s[5];
+        float* wm_w = wmax + ((j >> 1) & 1) * 32;
 #pragma unroll
-        for (int h = 0; h < kMaxGroup; ++h) {
+        for (int h = 0; h < 5; ++h) {
           s[h] = -INFINITY;
           if (h < G) {
             if (valid) s[h] = (__uint_as_float(r[h]) + __uint_as_float(r[8 + h])) * sc[h];
             const float wm = warp_max(s[h]);
-            if (lane == 0) sWmax[((it & 1) * 4 + warp) * 8 + h] = wm;
+            if (lane == 0) wm_w[wq * 8 + h] = wm;
           }
         }
-        bar_softmax();
+        bar_group(grp);
         bool rescale = false;
-        float alpha[kMaxGroup];
+        float alpha[5];
 #pragma unroll
-        for (int h = 0; h < kMaxGroup; ++h) {
+        for (int h = 0; h < 5; ++h) {
           alpha[h] = 1.f;
           if (h < G) {
-            const float* wm = sWmax + (it & 1) * 32 + h;
-            const float tmax = fmaxf(fmaxf(wm[0], wm[8]), fmaxf(wm[16], wm[24]));
-            if (tmax > mref[h] + kTau || mref[h] == -INFINITY) {   // the reference moves (always on the first tile)
+            const float tmax = fmaxf(fmaxf(wm_w[h], wm_w[8 + h]), fmaxf(wm_w[16 + h], wm_w[24 + h]));
+            if (tmax > mref[h] + kTau || mref[h] == -INFINITY) {   // the reference moves (always on the group's first tile)
               alpha[h] = mref[h] == -INFINITY ? 0.f : ex2(mref[h] - tmax);
               rescale |= mref[h] != -INFINITY;
               mref[h] = tmax;
@@ -379,96 +407,100 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             }
           }
         }
-        if (rescale) {
-          // O *= alpha per head, in tensor memory: thread = dim row; needs the previous tile's P V finished
-          if (mbar_wait(pvdone0 + 8u * ((it - 1) & 1), ((it - 1) >> 1) & 1, timed_out, p.status)) {
-            tc_fence_after();
-#pragma unroll
-            for (int hf = 0; hf < DH; ++hf) {
-              uint32_t o[16];
-              tmem_ld16(tmem_lane + 32u + 16u * hf, o);
-#pragma unroll
-              for (int h = 0; h < 5; ++h)
-#pragma unroll
-                for (int t = 0; t < 3; ++t) o[3 * h + t] = __float_as_uint(__uint_as_float(o[3 * h + t]) * alpha[h]);
-              tmem_st16(tmem_lane + 32u + 16u * hf, o);
-            }
-            tc_fence_before();
-          }
-        }
-        // probabilities: p <= 2^kTau; p * 2^13 as three e5m2 terms
-        uint32_t bytes[15];
-#pragma unroll
-        for (int h = 0; h < 5; ++h) {
-          float pr = 0.f;
-          if (h < G && valid) pr = ex2(s[h] - mref[h]);
-          l[h] += pr;
-          const float q = pr * kPScale;
-          const float t1 = e5m2_head(q), r1f = q - t1, t2 = e5m2_head(r1f), t3 = r1f - t2;
-          const uint32_t b12 = pack_e5m2x2(t1, t2), b3 = pack_e5m2x2(t3, 0.f);
-          bytes[3 * h] = b12 & 0xFFu; bytes[3 * h + 1] = b12 >> 8; bytes[3 * h + 2] = b3 & 0xFFu;
-        }
-        // the probability operand buffer is free once the P V of two tiles ago has completed
+        // The P V of this group's previous tile (two tiles back) has completed: the probability operand
+        // is free and the accumulator holds everything up to that tile.
         bool pok = true;
-        if (it >= 2) pok = mbar_wait(pvdone0 + 8u * pb, ((it >> 1) - 1) & 1, timed_out, p.status);
-        const bool partial = tile_tok0 + kTile2 > c.len_b;
-        const bool vok = partial && mbar_wait(vfull0 + 8u * vs, (it / vstages) & 1, timed_out, p.status);
-        if (pok) {
-          const uint32_t pop = smem_u32(sPop + pb * POP_BYTES);
-          const uint32_t col = ((uint32_t)(tok_in_tile >> 4) << 4), within = (uint32_t)tok_in_tile & 15u;
+        if (j >= 2) pok = mbar_wait(pvdone, ((j >> 1) - 1) & 1, timed_out, p.status);
+        if (rescale && pok) {   // O *= alpha per head, in tensor memory: thread = dim row
+          tc_fence_after();
 #pragma unroll
-          for (int n = 0; n < 15; ++n)
-            sts8(pop + n * 128 + (col ^ ((uint32_t)(n & 7) << 4)) + within, bytes[n]);
-          sts8(pop + 15 * 128 + (col ^ (7u << 4)) + within, 0u);   // unused 16th row: keep it finite
+          for (int hf = 0; hf < DH; ++hf) {
+            uint32_t o[16];
+            tmem_ld16(tmem_o + 16u * hf, o);
+#pragma unroll
+            for (int h = 0; h < 5; ++h)
+#pragma unroll
+              for (int t = 0; t < 3; ++t) o[3 * h + t] = __float_as_uint(__uint_as_float(o[3 * h + t]) * alpha[h]);
+            tmem_st16(tmem_o + 16u * hf, o);
+          }
+          tc_fence_before();
         }
-        if (vok && !valid) {
-          // this token slot is at or beyond the valid length: its V row may hold anything (NaN patterns
-          // included) and 0 * NaN would poison O: zero the row in shared memory before the product
+        // probabilities: p <= 2^kTau; p * 2^13 as three e5m2 terms, rows 3h..3h+2 of the operand
+        if (pok) {
 #pragma unroll
-          for (int hf = 0; hf < DH; ++hf)
+          for (int h = 0; h < 5; ++h) {
+            float pr = 0.f;
+            if (h < G && valid) pr = ex2(s[h] - mref[h]);
+            l[h] += pr;
+            const float q = pr * kPScale;
+            const float t1 = e5m2_head(q), r1f = q - t1, t2 = e5m2_head(r1f), t3 = r1f - t2;
+            const uint32_t b12 = pack_e5m2x2(t1, t2), b3 = pack_e5m2x2(t3, 0.f);
+            sts8(pop + (3 * h) * 128 + (pcol ^ ((uint32_t)((3 * h) & 7) << 4)) + pwithin, b12);
+            sts8(pop + (3 * h + 1) * 128 + (pcol ^ ((uint32_t)((3 * h + 1) & 7) << 4)) + pwithin, b12 >> 8);
+            sts8(pop + (3 * h + 2) * 128 + (pcol ^ ((uint32_t)((3 * h + 2) & 7) << 4)) + pwithin, b3);
+          }
+          sts8(pop + 15 * 128 + (pcol ^ (7u << 4)) + pwithin, 0u);   // unused 16th row: keep it finite
+        }
+        if (tile_tok0 + kTile2 > c.len_b) {
+          // A token slot at or beyond the valid length: its V row may hold anything (NaN patterns
+          // included) and 0 * NaN would poison O: zero the row in shared memory before the product.
+          const bool vok = mbar_wait(vfull0 + 8u * vs, (j / vstages) & 1, timed_out, p.status);
+          if (vok && !valid) {
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-              sts128z(sV_addr + vs * TILE_BYTES + hf * kTile2 * 128 + tok_in_tile * 128 + ch * 16);
+            for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+              for (int ch = 0; ch < 8; ++ch)
+                sts128z(sV_addr + vs * TILE_BYTES + hf * kTile2 * 128 + tok_in_tile * 128 + ch * 16);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand bytes -> visible to the tensor core
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(pfull0 + 8u * pb);
+        if (lane == 0) mbar_arrive(pfull);
       }
 
-      // ---------------- end of segment: read O once, hand one state to the epilogue warp ----------------
-      const int last = it - 1;
-      const bool ook = mbar_wait(pvdone0 + 8u * (last & 1), (last >> 1) & 1, timed_out, p.status);
+      // ---------------- end of segment: read O once, hand the group's state to the epilogue warp ----------------
+      const bool ook = jlast < 0 || mbar_wait(pvdone, (jlast >> 1) & 1, timed_out, p.status);
 #pragma unroll
       for (int h = 0; h < 5; ++h) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], off);
-        if (lane == 0) sWl[warp * 8 + h] = l[h];
+        if (lane == 0) wl[wq * 8 + h] = l[h];
       }
       const bool dok = seg < 1 || mbar_wait(dempty0, (seg - 1) & 1, timed_out, p.status);
-      bar_softmax();
+      bar_group(grp);
       if (ook && dok) {
-        tc_fence_after();
+        if (jlast >= 0) {
+          tc_fence_after();
 #pragma unroll
-        for (int hf = 0; hf < DH; ++hf) {
-          uint32_t o[16];
-          tmem_ld16(tmem_lane + 32u + 16u * hf, o);
+          for (int hf = 0; hf < DH; ++hf) {
+            uint32_t o[16];
+            tmem_ld16(tmem_o + 16u * hf, o);
 #pragma unroll
-          for (int h = 0; h < 5; ++h)
-            if (h < G)
-              sDump[h * DP + hf * 128 + tok_in_tile] =
-                  (__uint_as_float(o[3 * h]) + __uint_as_float(o[3 * h + 1]) + __uint_as_float(o[3 * h + 2])) * (1.f / kPScale);
+            for (int h = 0; h < 5; ++h)
+              if (h < G)
+                dump[h * DP + hf * 128 + tok_in_tile] =
+                    (__uint_as_float(o[3 * h]) + __uint_as_float(o[3 * h + 1]) + __uint_as_float(o[3 * h + 2])) * (1.f / kPScale);
+          }
+          tc_fence_before();
+        } else {   // the segment had no tile of this parity: an empty state (m = -inf) with finite contents
+          for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int hf = 0; hf < DH; ++hf) dump[h * DP + hf * 128 + tok_in_tile] = 0.f;
         }
-        tc_fence_before();
-        if (tid < 5) {
-          sML[tid] = mref[tid];
-          sML[8 + tid] = sWl[tid] + sWl[8 + tid] + sWl[16 + tid] + sWl[24 + tid];
+        if (wq == 0 && lane < 5) {
+          float m = mref[0];
+#pragma unroll
+          for (int h = 1; h < 5; ++h) m = lane == h ? mref[h] : m;
+          sML[grp * 16 + lane] = m;
+          sML[grp * 16 + 8 + lane] = wl[lane] + wl[8 + lane] + wl[16 + lane] + wl[24 + lane];
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(dfull0);
-      bar_softmax();   // sWl / sWmax reuse by the next segment
+      bar_group(grp);   // the sums are reused by the next segment
       ++seg;
+      it0 += ntiles;
       cur = seg_end;
       if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
     }
@@ -493,7 +525,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     }
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols2);
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -506,8 +538,8 @@ size_t umma2_smem_bytes(const Geometry& g, int vstages) {
   b += (size_t)2 * dh * 16 * 128;                                   // query operand
   b += (size_t)2 * 16 * 128;                                        // probability operand
   b += (size_t)2 * g.group * g.head_dim * 2;                        // raw query rows
-  b += (16 + 64 + 32) * 4;                                          // scales, per-warp maxima and sums
-  b += (size_t)g.group * (g.head_dim + 4) * 4 + 64;                 // the dumped state and its m, l
+  b += (16 + 128 + 64) * 4;                                         // scales, per-warp maxima and sums
+  b += (size_t)2 * g.group * (g.head_dim + 4) * 4 + 128;            // the two dumped states and their m, l
   b += (size_t)(2 * kKStages2 + 16 + 2 * vstages) * 8;              // barriers
   b += 32;                                                          // flags
   b += (size_t)(2 * g.batch + 1) * 4;

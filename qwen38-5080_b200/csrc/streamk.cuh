@@ -69,6 +69,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // Bounded wait.  Returns false (and raises the CTA's timeout flag) when the budget runs out or
 // when another thread of the CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* timed_out, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
   if (*timed_out) return false;
 #pragma unroll 1
   for (int i = 0; i < 64; ++i)
@@ -260,13 +261,13 @@ __device__ __forceinline__ void store_out(const MmaParams& p, long long idx, lon
 
 // ---------------------------------------------------------------------------------------------
 // epilogue warp: walks the CTA's segments in the consumers' order.  For each it waits for the
-// NW dumped states (m[8], l[8], acc[G][D]; four warp states in the xor layout of dump_pos, or one
-// CTA-wide state in plain order), merges them,
+// NW dumped states (m[8], l[8], acc[G][D]; head rows in the xor layout of dump_pos, or in plain
+// dim order when PLAIN), merges them,
 // and either writes the normalised bf16 output (pair fully owned by this CTA) or writes an
 // (m, l, acc) partial, takes an arrival ticket and, if it is the last owner to arrive, merges all
 // partials of the pair in CTA order and resets the ticket.
 // ---------------------------------------------------------------------------------------------
-template <int D, int NDUMP, int NW = kConsumerWarps>
+template <int D, int NDUMP, int NW = kConsumerWarps, bool PLAIN = false>
 __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long long r0, long long r1,
                                               long long total, int n_eff, const int* sCum, const int* sLen,
                                               const float* sDump, const float* sML, uint32_t dfull0,
@@ -310,7 +311,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           ll += ml[w * 16 + 8 + h] * f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            const float2 v = *reinterpret_cast<const float2*>(dump + w * dump_warp_floats + h * DP + 2 * (NW == 1 ? lane + 32 * r : dump_pos(lane + 32 * r)));
+            const float2 v = *reinterpret_cast<const float2*>(dump + w * dump_warp_floats + h * DP + 2 * (PLAIN ? lane + 32 * r : dump_pos(lane + 32 * r)));
             ax[r] += v.x * f;
             ay[r] += v.y * f;
           }
