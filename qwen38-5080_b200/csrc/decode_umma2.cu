@@ -35,14 +35,23 @@ namespace b200attn {
 namespace {
 
 constexpr int kTile2 = 128;
-constexpr int kSoftmaxWarps2 = 8;                  // two groups of four; a group owns the tiles of one parity
-constexpr int kProducer2 = kSoftmaxWarps2;         // warp 8: TMA issue
-constexpr int kEpilogue2 = kSoftmaxWarps2 + 1;     // warp 9: merge, output, fused combine
-constexpr int kIssuer2 = kSoftmaxWarps2 + 2;       // warp 10: query operand, tcgen05.mma issue, tensor memory owner
-constexpr int kThreads2 = (kSoftmaxWarps2 + 3) * 32;
-constexpr int kKStages2 = 2;
-constexpr float kTau = 2.0f;                       // lazy-rescale threshold, log2 units
-constexpr float kPScale = 8192.f;                  // 2^13: p * 2^13 <= 2^15 < 57344 (e5m2 max)
+#ifndef B200ATTN_U2_GROUPS
+#define B200ATTN_U2_GROUPS 4
+#endif
+#ifndef B200ATTN_U2_MAXTILES
+#define B200ATTN_U2_MAXTILES 12
+#endif
+constexpr int kGroups2 = B200ATTN_U2_GROUPS;         // softmax groups of four warps; group = tile index mod kGroups2
+constexpr int kMaxRingTiles2 = B200ATTN_U2_MAXTILES; // K + V tiles staged per CTA, at most
+constexpr int kSoftmaxWarps2 = 4 * kGroups2;
+constexpr int kProducer2 = kSoftmaxWarps2;           // TMA issue
+constexpr int kEpilogue2 = kSoftmaxWarps2 + 1;       // merge, output, fused combine
+constexpr int kIssuerS2 = kSoftmaxWarps2 + 2;        // query operand, S = K q^T issue, tensor memory owner
+constexpr int kIssuerPV2 = kSoftmaxWarps2 + 3;       // O += V^T P^T issue
+constexpr int kThreads2 = (kSoftmaxWarps2 + 4) * 32;
+constexpr int kQRing2 = 4;                           // query operands / score scales in flight (segments)
+constexpr float kTau = 2.0f;                         // lazy-rescale threshold, log2 units
+constexpr float kPScale = 8192.f;                    // 2^13: p * 2^13 <= 2^15 < 57344 (e5m2 max)
 
 // D f32, A e4m3 MN-major (V^T), B e5m2 K-major (P^T), N = 16, M = 128
 constexpr uint32_t kIdescPV = (1u << 4) | (1u << 10) | (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
@@ -68,62 +77,107 @@ __device__ __forceinline__ void sts8(uint32_t addr, uint32_t v) {
 __device__ __forceinline__ void sts128z(uint32_t addr) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
 }
-// Named barrier of one softmax group (128 threads): ids 1 and 2.
+// Named barrier of one softmax group (128 threads): ids 1..kGroups2.
 __device__ __forceinline__ void bar_group(int grp) {
-  if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
-  else asm volatile("bar.sync 2, 128;" ::: "memory");
+  switch (grp) {
+    case 0: asm volatile("bar.sync 1, 128;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 2, 128;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 3, 128;" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 128;" ::: "memory"); break;
+  }
+}
+
+#ifdef B200ATTN_TRACE
+// Development-only stall accounting: cycles spent inside each class of wait, 16 slots per CTA.
+static __device__ unsigned long long g_trace2[4096 * 32];
+#define TWAIT(acc, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); (acc) += clock64() - t_; return r_; }()
+#define TDECL(...) long long __VA_ARGS__
+#define TSTORE(slot, v) g_trace2[blockIdx.x * 32 + (slot)] = (unsigned long long)(v)
+#define TSTAMP(slot) g_trace2[blockIdx.x * 32 + (slot)] = global_timer_ns()
+#else
+#define TWAIT(acc, expr) (expr)
+#define TDECL(...) do { } while (0)
+#define TSTORE(slot, v) do { } while (0)
+#define TSTAMP(slot) do { } while (0)
+#endif
+
+// Shared-memory plan, computed the same way on the host and in the kernel.
+struct Plan2 {
+  int kstages, vstages;
+  size_t bytes;
+};
+__host__ __device__ inline size_t umma2_fixed_bytes(int group, int head_dim, int batch) {
+  const int dh = head_dim / 128;
+  size_t b = 1024;                                                   // alignment slack
+  b += (size_t)kQRing2 * dh * 16 * 128;                              // query operands
+  b += (size_t)kGroups2 * 16 * 128;                                  // probability operands
+  b += (size_t)2 * group * head_dim * 2;                             // raw query rows
+  b += (size_t)(kQRing2 * 8 + kGroups2 * 64 + kGroups2 * 32) * 4;    // scales, per-warp maxima and sums
+  b += (size_t)kGroups2 * group * (head_dim + 4) * 4;                // dumped states
+  b += (size_t)kGroups2 * 16 * 4;                                    // their m, l
+  b += (size_t)(4 + 2 * kQRing2 + 4 * kGroups2 + 2) * 8;             // fixed barriers
+  b += 32;                                                           // flags
+  b += (size_t)(2 * batch + 1) * 4;
+  return b;
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads2, D == 128 ? 2 : 1)
+__global__ void __launch_bounds__(kThreads2, (kGroups2 <= 2 && D == 128 && kMaxRingTiles2 <= 5) ? 2 : 1)
 attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                           const MmaParams p) {
+  constexpr int NG = kGroups2;
   constexpr int DH = D / 128;
   constexpr int TILE_BYTES = kTile2 * D;
   constexpr int DP = D + 4;
   constexpr int QOP_BYTES = DH * 16 * 128;   // query operand
   constexpr int POP_BYTES = 16 * 128;        // probability operand: 16 rows x 128 tokens
-  constexpr uint32_t O_COL0 = 32;            // tensor memory: S of group 0 | S of group 1 | O of group 0 | O of group 1
-  constexpr uint32_t TMEM_COLS = D == 128 ? 64 : 128;
+  // The four 32-token products of a tile go to separate accumulators (summed once per segment): products
+  // into one accumulator execute back to back at full latency, independent ones overlap.
+  constexpr int OSPLIT = DH == 1 ? 4 : 1;
+  constexpr uint32_t O_COL0 = NG * 16;       // tensor memory: S of each group, then O of each group
+  constexpr uint32_t O_COLS = 16 * DH * OSPLIT;   // per group
+  constexpr uint32_t TMEM_NEED = NG * (16 + O_COLS);
+  constexpr uint32_t TMEM_COLS = TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   const Geometry& g = p.g;
   const int G = g.group;
-  const int vstages = p.stages;
+  const int kstages = p.kstages, vstages = p.stages;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t q_bytes = (uint32_t)G * D * 2;
 
+  if (tid == 0) TSTAMP(16);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  uint8_t* sK = smem;                                                   // [2][TILE_BYTES]
-  uint8_t* sV = sK + (size_t)kKStages2 * TILE_BYTES;                    // [vstages][TILE_BYTES]
-  uint8_t* sQop = sV + (size_t)vstages * TILE_BYTES;                    // [2][QOP_BYTES]
-  uint8_t* sPop = sQop + 2 * QOP_BYTES;                                 // [2 groups][POP_BYTES], 1024-aligned
-  uint8_t* sQraw = sPop + 2 * POP_BYTES;                                // [2][G*D] bf16
-  float* sScale = reinterpret_cast<float*>(sQraw + 2 * q_bytes);        // [2][8]
-  float* sWmax = sScale + 16;                                           // [2 groups][2][4 warps][8] tile maxima
-  float* sWl = sWmax + 128;                                             // [2 groups][4 warps][8] sums
-  float* sDump = sWl + 64;                                              // [2 groups][G][DP]
-  float* sML = sDump + 2 * G * DP;                                      // [2 groups][16]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + 32);
-  const uint32_t kfull0 = smem_u32(bars), kempty0 = kfull0 + 8u * kKStages2;
-  const uint32_t vfull0 = kempty0 + 8u * kKStages2, vempty0 = vfull0 + 8u * vstages;
+  uint8_t* sK = smem;                                                   // [kstages][TILE_BYTES]
+  uint8_t* sV = sK + (size_t)kstages * TILE_BYTES;                      // [vstages][TILE_BYTES]
+  uint8_t* sQop = sV + (size_t)vstages * TILE_BYTES;                    // [kQRing2][QOP_BYTES]
+  uint8_t* sPop = sQop + kQRing2 * QOP_BYTES;                           // [NG][POP_BYTES], 1024-aligned
+  uint8_t* sQraw = sPop + NG * POP_BYTES;                               // [2][G*D] bf16
+  float* sScale = reinterpret_cast<float*>(sQraw + 2 * q_bytes);        // [kQRing2][8]
+  float* sWmax = sScale + kQRing2 * 8;                                  // [NG][2][4 warps][8] tile maxima
+  float* sWl = sWmax + NG * 64;                                         // [NG][4 warps][8] sums
+  float* sDump = sWl + NG * 32;                                         // [NG][G][DP]
+  float* sML = sDump + NG * G * DP;                                     // [NG][16]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sML + NG * 16);
+  const uint32_t kfull0 = smem_u32(bars), kempty0 = kfull0 + 8u * kstages;
+  const uint32_t vfull0 = kempty0 + 8u * kstages, vempty0 = vfull0 + 8u * vstages;
   const uint32_t qrfull0 = vempty0 + 8u * vstages, qrempty0 = qrfull0 + 16u;
-  const uint32_t qinfo0 = qrempty0 + 16u, sfull0 = qinfo0 + 16u, sempty0 = sfull0 + 16u;
-  const uint32_t pfull0 = sempty0 + 16u, pvdone0 = pfull0 + 16u;
-  const uint32_t dfull0 = pvdone0 + 16u, dempty0 = dfull0 + 8u;
-  constexpr int kFixedBars = 2 * kKStages2 + 16;
-  int* sFlags = reinterpret_cast<int*>(bars + kFixedBars + 2 * vstages);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
+  const uint32_t qinfo0 = qrempty0 + 16u, qfree0 = qinfo0 + 8u * kQRing2;
+  const uint32_t sfull0 = qfree0 + 8u * kQRing2, sempty0 = sfull0 + 8u * NG;
+  const uint32_t pfull0 = sempty0 + 8u * NG, pvdone0 = pfull0 + 8u * NG;
+  const uint32_t dfull0 = pvdone0 + 8u * NG, dempty0 = dfull0 + 8u;
+  constexpr int kFixedBars = 4 + 2 * kQRing2 + 4 * NG + 2;
+  int* sFlags = reinterpret_cast<int*>(bars + kFixedBars + 2 * kstages + 2 * vstages);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
   int* sLen = sFlags + 8;
   int* sCum = sLen + g.batch;
   volatile int* timed_out = sFlags;
 
   if (tid == 0) {
-    for (int s = 0; s < kKStages2; ++s) { mbar_init(kfull0 + 8u * s, 1); mbar_init(kempty0 + 8u * s, 1); }
+    for (int s = 0; s < kstages; ++s) { mbar_init(kfull0 + 8u * s, 1); mbar_init(kempty0 + 8u * s, 1); }
     for (int s = 0; s < vstages; ++s) { mbar_init(vfull0 + 8u * s, 1); mbar_init(vempty0 + 8u * s, 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(qrfull0 + 8u * i, 1);
-      mbar_init(qrempty0 + 8u * i, 1);
-      mbar_init(qinfo0 + 8u * i, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(qrfull0 + 8u * i, 1); mbar_init(qrempty0 + 8u * i, 1); }
+    for (int i = 0; i < kQRing2; ++i) { mbar_init(qinfo0 + 8u * i, 1); mbar_init(qfree0 + 8u * i, kSoftmaxWarps2); }
+    for (int i = 0; i < NG; ++i) {
       mbar_init(sfull0 + 8u * i, 1);
       mbar_init(sempty0 + 8u * i, 4);     // the four warps of softmax group i
       mbar_init(pfull0 + 8u * i, 4);
@@ -153,11 +207,12 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     asm volatile("prefetch.tensormap [%0];" ::"l"(&kmap) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
   }
-  if (warp == kIssuer2) tmem_alloc(smem_u32(sFlags + 1), TMEM_COLS);
+  if (warp == kIssuerS2) tmem_alloc(smem_u32(sFlags + 1), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)sFlags[1];
+  if (tid == 0) TSTAMP(17);
 
   if (sFlags[2] & 1) {   // sequences of length 0 have no tiles: their outputs are zero
     const long long rows = (long long)g.n_layers * g.batch;
@@ -180,11 +235,15 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
 
   if (warp == kProducer2) {
     // ===================== producer warp: one elected lane issues the copies =====================
+    // (this lane, like the two issuer lanes, is a serial instruction stream that must keep up with one
+    // tile per ~1300 cycles: stage indices, ring rounds and rows are carried, not recomputed)
     if (lane == 0 && has_work) {
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
-      int it = 0, seg = 0;
-      bool seg_start = true;
-      for (long long idx = r0; idx < r1; ++idx, ++it) {
+      const int total_it = (int)(r1 - r0);
+      int seg = 0, ks = 0, kround = 0, vs = 0, vround = 0, kissued = 0, vissued = 0, row = 0;
+      bool seg_start = true, ok = true;
+      TDECL(w_kempty = 0, w_vempty = 0, t_begin = clock64());
+      for (int it = 0; it < total_it && ok; ++it) {
         if (seg_start) {
           const int qb = seg & 1;
           if (seg >= 2 && !mbar_wait(qrempty0 + 8u * qb, ((seg >> 1) - 1) & 1, timed_out, p.status)) break;
@@ -193,70 +252,60 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           bulk_load(smem_u32(sQraw + qb * q_bytes), p.q + (lb * g.h_q + c.h * G) * D, q_bytes, qrfull0 + 8u * qb);
           ++seg;
           seg_start = false;
+          row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTile2;
         }
-        const int row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTile2;
-        const int ks = it % kKStages2, vs = it % vstages;
-        if (it >= kKStages2 && !mbar_wait(kempty0 + 8u * ks, ((it / kKStages2) - 1) & 1, timed_out, p.status)) break;
+        if (kround && !TWAIT(w_kempty, mbar_wait(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status))) break;
         mbar_arrive_expect_tx(kfull0 + 8u * ks, TILE_BYTES);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf)
-          tma_load_3d(smem_u32(sK + (size_t)ks * TILE_BYTES + hf * kTile2 * 128), &kmap, hf * 128, row, c.layer, kfull0 + 8u * ks);
-        sFlags[3] = it + 1;
-        if (it >= vstages && !mbar_wait(vempty0 + 8u * vs, ((it / vstages) - 1) & 1, timed_out, p.status)) break;
+          tma_load_3d(smem_u32(sK) + ks * TILE_BYTES + hf * kTile2 * 128, &kmap, hf * 128, row, c.layer, kfull0 + 8u * ks);
+        ++kissued;
+#ifdef B200ATTN_TRACE
+        if (it == 0) TSTAMP(18);
+        if (it == total_it - 1) TSTAMP(21);
+#endif
+        if (++ks == kstages) { ks = 0; ++kround; }
+        if (vround && !TWAIT(w_vempty, mbar_wait(vempty0 + 8u * vs, (vround - 1) & 1, timed_out, p.status))) break;
         mbar_arrive_expect_tx(vfull0 + 8u * vs, TILE_BYTES);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf)
-          tma_load_3d(smem_u32(sV + (size_t)vs * TILE_BYTES + hf * kTile2 * 128), &vmap, hf * 128, row, c.layer, vfull0 + 8u * vs);
-        sFlags[4] = it + 1;
+          tma_load_3d(smem_u32(sV) + vs * TILE_BYTES + hf * kTile2 * 128, &vmap, hf * 128, row, c.layer, vfull0 + 8u * vs);
+        ++vissued;
+        if (++vs == vstages) { vs = 0; ++vround; }
+        row += kTile2;
         if (++c.tile == c.tiles_b) {
           seg_start = true;
-          if (idx + 1 < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+          if (it + 1 < total_it) next_pair(c, sCum, sLen, g.batch, g.h_kv);
         }
       }
-      sFlags[5] = seg;
+      sFlags[3] = kissued; sFlags[4] = vissued; sFlags[5] = seg;   // read by the drain after a timed-out wait
+      TSTORE(0, clock64() - t_begin); TSTORE(1, w_kempty); TSTORE(2, w_vempty);
     }
   } else if (warp == kEpilogue2) {
     if (has_work)
-      epilogue_warp<D, 1, 2, true>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
-  } else if (warp == kIssuer2) {
-    // ===================== issuer warp: query operand, both tcgen05.mma products =====================
+      epilogue_warp<D, 1, NG, true>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+  } else if (warp == kIssuerS2) {
+    // ===================== S issuer warp: query operand, S = K q^T =====================
     if (has_work) {
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
       const int total_it = (int)(r1 - r0);
-      int seg = 0, qb = 0, seg_pos = 0;
+      int seg = 0, qb = 0, ks = 0, kround = 0, issued = 0;
       bool seg_start = true, alive = true;
-      uint32_t fresh_mask = 0;   // bit (it & 1): tile `it` is its group's first of the segment (accumulator starts over)
-      // P V for tile j (group j & 1): waits for the probability operand and the V tile
-      auto issue_pv = [&](int j) {
-        const int pb = j & 1, vs = j % vstages;
-        if (!mbar_wait(pfull0 + 8u * pb, (j >> 1) & 1, timed_out, p.status)) { alive = false; return; }
-        if (!mbar_wait(vfull0 + 8u * vs, (j / vstages) & 1, timed_out, p.status)) { alive = false; return; }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a0 = smem_u32(sV + (size_t)vs * TILE_BYTES), b0 = smem_u32(sPop + pb * POP_BYTES);
-          const uint32_t d0 = tmem_base + O_COL0 + (uint32_t)pb * 16u * DH;
-#pragma unroll
-          for (int hf = 0; hf < DH; ++hf)
-#pragma unroll
-            for (int kb = 0; kb < 4; ++kb)   // 32 tokens per instruction: 32 rows of 128 bytes further in V, 32 bytes further in P
-              umma_f8(d0 + 16u * hf, smem_desc_k128(a0 + hf * kTile2 * 128 + kb * 4096),
-                      smem_desc_k128(b0 + kb * 32), kIdescPV, (kb || !((fresh_mask >> pb) & 1u)) ? 1u : 0u);
-          umma_commit(pvdone0 + 8u * pb);    // O holds tile j; probability operand pb is free
-          umma_commit(vempty0 + 8u * vs);    // V tile has been read
-        }
-        __syncwarp();
-      };
-      int it = 0;
-      for (; it < total_it && alive; ++it) {
-        const int sb = it & 1;
-        if (it >= 2) alive = mbar_wait(sempty0 + 8u * sb, ((it >> 1) - 1) & 1, timed_out, p.status);
+      const uint64_t descK0 = smem_desc_k128(smem_u32(sK)), descQ0 = smem_desc_k128(smem_u32(sQop));
+      TDECL(w_sempty = 0, w_kfull = 0, w_q = 0, t_begin = clock64());
+      for (int it = 0; it < total_it && alive; ++it) {
+        const int sb = it % NG;
+        if (it >= NG) alive = TWAIT(w_sempty, mbar_wait(sempty0 + 8u * sb, ((it / NG) - 1) & 1, timed_out, p.status));
         if (alive && seg_start) {
-          qb = seg & 1;
-          alive = mbar_wait(qrfull0 + 8u * qb, (seg >> 1) & 1, timed_out, p.status);
+          qb = seg % kQRing2;
+          alive = TWAIT(w_q, mbar_wait(qrfull0 + 8u * (seg & 1), (seg >> 1) & 1, timed_out, p.status));
+          // every softmax warp has taken the scales of the segment that used this slot before; its
+          // score products completed before the score buffer waits above could pass
+          if (alive && seg >= kQRing2) alive = TWAIT(w_q, mbar_wait(qfree0 + 8u * qb, ((seg / kQRing2) - 1) & 1, timed_out, p.status));
           if (alive) {
             // Each head h: row h = leading e4m3 part of q * 2^e, row 8+h = remainder; lane owns 4 dims
             // per 128-dim block.  2^e puts the head's largest |q| into [128, 256).
-            const uint32_t qraw = smem_u32(sQraw + qb * q_bytes), qop = smem_u32(sQop + qb * QOP_BYTES);
+            const uint32_t qraw = smem_u32(sQraw + (seg & 1) * q_bytes), qop = smem_u32(sQop + qb * QOP_BYTES);
             for (int h = 0; h < G; ++h) {
               float x[DH][4];
               float amax = 0.f;
@@ -291,45 +340,85 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand bytes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) {
-              mbar_arrive(qrempty0 + 8u * qb);   // raw query buffer may be refilled
-              mbar_arrive(qinfo0 + 8u * qb);     // scales are in place for the softmax warps
+              mbar_arrive(qrempty0 + 8u * (seg & 1));   // raw query buffer may be refilled
+              mbar_arrive(qinfo0 + 8u * qb);            // scales are in place for the softmax warps
             }
           }
           ++seg;
-          seg_pos = 0;
         }
-        fresh_mask = (fresh_mask & ~(1u << sb)) | ((seg_pos < 2 ? 1u : 0u) << sb);
-        ++seg_pos;
         seg_start = false;
-        const int ks = it % kKStages2;
-        if (alive) alive = mbar_wait(kfull0 + 8u * ks, (it / kKStages2) & 1, timed_out, p.status);
+        if (alive) alive = TWAIT(w_kfull, mbar_wait(kfull0 + 8u * ks, kround & 1, timed_out, p.status));
+#ifdef B200ATTN_TRACE
+        if (it == 0 && lane == 0) TSTAMP(19);
+#endif
         if (alive) {
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t a0 = smem_u32(sK + (size_t)ks * TILE_BYTES), b0 = smem_u32(sQop + qb * QOP_BYTES);
+            // descriptors address shared memory in 16-byte units: stepping the start address is an add
+            const uint64_t a0 = descK0 + (uint64_t)(ks * (TILE_BYTES >> 4)), b0 = descQ0 + (uint64_t)(qb * (QOP_BYTES >> 4));
             const uint32_t d = tmem_base + (uint32_t)sb * 16u;
 #pragma unroll
             for (int hf = 0; hf < DH; ++hf)
 #pragma unroll
               for (int kb = 0; kb < 4; ++kb)
-                umma_f8(d, smem_desc_k128(a0 + hf * kTile2 * 128 + kb * 32), smem_desc_k128(b0 + hf * 2048 + kb * 32),
+                umma_f8(d, a0 + (uint64_t)(hf * (kTile2 * 128 >> 4) + kb * 2), b0 + (uint64_t)(hf * 128 + kb * 2),
                         kIdescQK, (hf | kb) ? 1u : 0u);
             umma_commit(sfull0 + 8u * sb);     // scores of this tile are complete
             umma_commit(kempty0 + 8u * ks);    // and the K tile has been read
-            sFlags[6] = it + 1;                // score MMAs issued
           }
           __syncwarp();
-          if (it >= 1) { issue_pv(it - 1); if (lane == 0 && alive) sFlags[7] = it; }
+          ++issued;
+          if (++ks == kstages) { ks = 0; ++kround; }
         }
         if (++c.tile == c.tiles_b) {
           seg_start = true;
           if (it + 1 < total_it) next_pair(c, sCum, sLen, g.batch, g.h_kv);
         }
       }
-      if (alive && total_it > 0) { issue_pv(total_it - 1); if (lane == 0 && alive) sFlags[7] = total_it; }
+      if (lane == 0) { sFlags[6] = issued; TSTORE(3, clock64() - t_begin); TSTORE(4, w_sempty); TSTORE(5, w_kfull); TSTORE(6, w_q); }
+    }
+  } else if (warp == kIssuerPV2) {
+    // ===================== P V issuer warp: O[group] += V^T P^T =====================
+    if (has_work) {
+      Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+      const int total_it = (int)(r1 - r0);
+      int seg_pos = 0, vs = 0, vround = 0, issued = 0;
+      bool alive = true;
+      const uint64_t descV0 = smem_desc_k128(smem_u32(sV)), descP0 = smem_desc_k128(smem_u32(sPop));
+      TDECL(w_pfull = 0, w_vfull = 0, t_begin = clock64());
+      for (int j = 0; j < total_it && alive; ++j) {
+        const int pb = j % NG;
+        const bool fresh = seg_pos < NG;   // the group's first tile of this segment: its accumulator starts over
+        alive = TWAIT(w_pfull, mbar_wait(pfull0 + 8u * pb, (j / NG) & 1, timed_out, p.status));
+        if (alive) alive = TWAIT(w_vfull, mbar_wait(vfull0 + 8u * vs, vround & 1, timed_out, p.status));
+        if (alive) {
+          tc_fence_after();
+          if (lane == 0) {
+            const uint64_t a0 = descV0 + (uint64_t)(vs * (TILE_BYTES >> 4)), b0 = descP0 + (uint64_t)(pb * (POP_BYTES >> 4));
+            const uint32_t d0 = tmem_base + O_COL0 + (uint32_t)pb * O_COLS;
+#pragma unroll
+            for (int hf = 0; hf < DH; ++hf)
+#pragma unroll
+              for (int kb = 0; kb < 4; ++kb)   // 32 tokens per instruction: 32 rows of 128 bytes further in V, 32 bytes further in P
+                umma_f8(d0 + 16u * hf + (OSPLIT > 1 ? 16u * kb : 0u), a0 + (uint64_t)(hf * (kTile2 * 128 >> 4) + kb * (4096 >> 4)),
+                        b0 + (uint64_t)(kb * 2), kIdescPV, ((OSPLIT == 1 && kb) || !fresh) ? 1u : 0u);
+            umma_commit(pvdone0 + 8u * pb);    // O holds tile j; the group's probability operand is free
+            umma_commit(vempty0 + 8u * vs);    // V tile has been read
+          }
+          __syncwarp();
+          ++issued;
+          if (++vs == vstages) { vs = 0; ++vround; }
+        }
+        ++seg_pos;
+        if (++c.tile == c.tiles_b) {
+          seg_pos = 0;
+          if (j + 1 < total_it) next_pair(c, sCum, sLen, g.batch, g.h_kv);
+        }
+      }
+      if (lane == 0) { sFlags[7] = issued; TSTORE(7, clock64() - t_begin); TSTORE(8, w_pfull); TSTORE(9, w_vfull); }
     }
   } else if (has_work) {
-    // ============ softmax warps: two groups of four; group = tile parity; one thread = one token / one output dim ============
+    // ===== softmax warps: groups of four; group = tile index mod NG; one thread = one token / one output dim =====
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
     long long cur = r0;
     int it0 = 0, seg = 0;
@@ -337,7 +426,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     const int tok_in_tile = wq * 32 + lane;
     const uint32_t tmem_lane = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t tmem_s = tmem_lane + (uint32_t)grp * 16u;
-    const uint32_t tmem_o = tmem_lane + O_COL0 + (uint32_t)grp * 16u * DH;
+    const uint32_t tmem_o = tmem_lane + O_COL0 + (uint32_t)grp * O_COLS;
     const uint32_t sfull = sfull0 + 8u * grp, sempty = sempty0 + 8u * grp, pfull = pfull0 + 8u * grp, pvdone = pvdone0 + 8u * grp;
     const uint32_t pop = smem_u32(sPop + grp * POP_BYTES);
     const uint32_t pcol = ((uint32_t)(tok_in_tile >> 4) << 4), pwithin = (uint32_t)tok_in_tile & 15u;
@@ -345,29 +434,33 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     float* wmax = sWmax + grp * 64;
     float* wl = sWl + grp * 32;
     float* dump = sDump + grp * G * DP;
+    TDECL(w_sfull = 0, w_pvdone = 0, w_bar = 0, w_seg = 0, t_begin = clock64());
 
     while (cur < r1) {
       const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
       const long long seg_end = pair_end < r1 ? pair_end : r1;
       const int ntiles = (int)(seg_end - cur);
-      const int qb = seg & 1;
-      float sc[kMaxGroup];
+      const int qb = seg % kQRing2;
+      float sc[5];
       {
-        const bool ok = mbar_wait(qinfo0 + 8u * qb, (seg >> 1) & 1, timed_out, p.status);
+        const bool ok = mbar_wait(qinfo0 + 8u * qb, (seg / kQRing2) & 1, timed_out, p.status);
 #pragma unroll
-        for (int h = 0; h < kMaxGroup; ++h) sc[h] = (ok && h < G) ? sScale[qb * 8 + h] : 0.f;
+        for (int h = 0; h < 5; ++h) sc[h] = (ok && h < G) ? sScale[qb * 8 + h] : 0.f;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(qfree0 + 8u * qb);
       }
       float mref[5], l[5];
 #pragma unroll
       for (int h = 0; h < 5; ++h) { mref[h] = -INFINITY; l[h] = 0.f; }
 
-      const int jfirst = it0 + ((it0 ^ grp) & 1);   // this group's tiles: CTA-wide tile index j with (j & 1) == grp
+      // this group's tiles: CTA-wide tile index j with j mod NG == grp
+      const int jfirst = it0 + (((grp - it0) % NG) + NG) % NG;
       int jlast = -1;
-      for (int j = jfirst; j < it0 + ntiles; j += 2) {
+      for (int j = jfirst; j < it0 + ntiles; j += NG) {
         jlast = j;
-        const int vs = j % vstages;
+        const int ph = (j / NG) & 1;
         const int tile_tok0 = (c.tile + (j - it0)) * kTile2;
-        const bool sok = mbar_wait(sfull, (j >> 1) & 1, timed_out, p.status);
+        const bool sok = TWAIT(w_sfull, mbar_wait(sfull, ph, timed_out, p.status));
         uint32_t r[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) r[i] = 0;
@@ -381,7 +474,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         const bool valid = sok && tile_tok0 + tok_in_tile < c.len_b;
         // scores and the tile maximum per head (over the group's 128 tokens)
         float s[5];
-        float* wm_w = wmax + ((j >> 1) & 1) * 32;
+        float* wm_w = wmax + ph * 32;
 #pragma unroll
         for (int h = 0; h < 5; ++h) {
           s[h] = -INFINITY;
@@ -391,7 +484,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             if (lane == 0) wm_w[wq * 8 + h] = wm;
           }
         }
-        bar_group(grp);
+        TWAIT(w_bar, (bar_group(grp), true));
         bool rescale = false;
         float alpha[5];
 #pragma unroll
@@ -407,14 +500,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             }
           }
         }
-        // The P V of this group's previous tile (two tiles back) has completed: the probability operand
-        // is free and the accumulator holds everything up to that tile.
+        // The P V of this group's previous tile has completed: the probability operand is free and the
+        // accumulator holds everything up to that tile.
         bool pok = true;
-        if (j >= 2) pok = mbar_wait(pvdone, ((j >> 1) - 1) & 1, timed_out, p.status);
+        if (j >= NG) pok = TWAIT(w_pvdone, mbar_wait(pvdone, ph ^ 1, timed_out, p.status));
         if (rescale && pok) {   // O *= alpha per head, in tensor memory: thread = dim row
           tc_fence_after();
 #pragma unroll
-          for (int hf = 0; hf < DH; ++hf) {
+          for (int hf = 0; hf < DH * OSPLIT; ++hf) {
             uint32_t o[16];
             tmem_ld16(tmem_o + 16u * hf, o);
 #pragma unroll
@@ -444,6 +537,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         if (tile_tok0 + kTile2 > c.len_b) {
           // A token slot at or beyond the valid length: its V row may hold anything (NaN patterns
           // included) and 0 * NaN would poison O: zero the row in shared memory before the product.
+          const int vs = j % vstages;
           const bool vok = mbar_wait(vfull0 + 8u * vs, (j / vstages) & 1, timed_out, p.status);
           if (vok && !valid) {
 #pragma unroll
@@ -457,10 +551,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(pfull);
+#ifdef B200ATTN_TRACE
+        if (tid == 0 && j == 0) TSTAMP(20);
+#endif
       }
 
       // ---------------- end of segment: read O once, hand the group's state to the epilogue warp ----------------
-      const bool ook = jlast < 0 || mbar_wait(pvdone, (jlast >> 1) & 1, timed_out, p.status);
+      TDECL(t_seg = clock64());
+      const bool ook = jlast < 0 || mbar_wait(pvdone, (jlast / NG) & 1, timed_out, p.status);
 #pragma unroll
       for (int h = 0; h < 5; ++h) {
 #pragma unroll
@@ -474,16 +572,21 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           tc_fence_after();
 #pragma unroll
           for (int hf = 0; hf < DH; ++hf) {
-            uint32_t o[16];
-            tmem_ld16(tmem_o + 16u * hf, o);
+            float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int sp = 0; sp < OSPLIT; ++sp) {
+              uint32_t o[16];
+              tmem_ld16(tmem_o + 16u * (hf + sp), o);   // OSPLIT > 1 only with DH == 1
+#pragma unroll
+              for (int h = 0; h < 5; ++h)
+                acc[h] += __uint_as_float(o[3 * h]) + __uint_as_float(o[3 * h + 1]) + __uint_as_float(o[3 * h + 2]);
+            }
 #pragma unroll
             for (int h = 0; h < 5; ++h)
-              if (h < G)
-                dump[h * DP + hf * 128 + tok_in_tile] =
-                    (__uint_as_float(o[3 * h]) + __uint_as_float(o[3 * h + 1]) + __uint_as_float(o[3 * h + 2])) * (1.f / kPScale);
+              if (h < G) dump[h * DP + hf * 128 + tok_in_tile] = acc[h] * (1.f / kPScale);
           }
           tc_fence_before();
-        } else {   // the segment had no tile of this parity: an empty state (m = -inf) with finite contents
+        } else {   // the segment had no tile for this group: an empty state (m = -inf) with finite contents
           for (int h = 0; h < G; ++h)
 #pragma unroll
             for (int hf = 0; hf < DH; ++hf) dump[h * DP + hf * 128 + tok_in_tile] = 0.f;
@@ -499,15 +602,20 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(dfull0);
       bar_group(grp);   // the sums are reused by the next segment
+#ifdef B200ATTN_TRACE
+      w_seg += clock64() - t_seg;
+#endif
       ++seg;
       it0 += ntiles;
       cur = seg_end;
       if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
     }
+    if (tid == 0) { TSTAMP(22); TSTORE(10, clock64() - t_begin); TSTORE(11, w_sfull); TSTORE(12, w_pvdone); TSTORE(13, w_bar); TSTORE(14, w_seg); }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kIssuer2) {
+  if (tid == 0) TSTAMP(23);
+  if (warp == kIssuerS2) {
     if (sFlags[0] && lane == 0) {
       // A wait gave up: wait (bounded) for everything already issued into this CTA's shared / tensor memory.
       auto drain = [&](uint32_t bar0, int ring, int issued) {
@@ -517,11 +625,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           while (!mbar_try_wait(bar0 + 8u * s, (lastu / ring) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
         }
       };
-      drain(kfull0, kKStages2, sFlags[3]);
+      drain(kfull0, kstages, sFlags[3]);
       drain(vfull0, vstages, sFlags[4]);
       drain(qrfull0, 2, sFlags[5]);
-      drain(sfull0, 2, sFlags[6]);
-      drain(pvdone0, 2, sFlags[7]);
+      drain(sfull0, NG, sFlags[6]);
+      drain(pvdone0, NG, sFlags[7]);
     }
     __syncwarp();
     tc_fence_after();
@@ -529,21 +637,23 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   }
 }
 
-int vstages2_for(const Geometry& g) { return g.head_dim == 128 ? 3 : 2; }
-
-size_t umma2_smem_bytes(const Geometry& g, int vstages) {
-  const int dh = g.head_dim / 128;
-  size_t b = 1024;
-  b += (size_t)(kKStages2 + vstages) * kTile2 * g.head_dim;         // K and V rings
-  b += (size_t)2 * dh * 16 * 128;                                   // query operand
-  b += (size_t)2 * 16 * 128;                                        // probability operand
-  b += (size_t)2 * g.group * g.head_dim * 2;                        // raw query rows
-  b += (16 + 128 + 64) * 4;                                         // scales, per-warp maxima and sums
-  b += (size_t)2 * g.group * (g.head_dim + 4) * 4 + 128;            // the two dumped states and their m, l
-  b += (size_t)(2 * kKStages2 + 16 + 2 * vstages) * 8;              // barriers
-  b += 32;                                                          // flags
-  b += (size_t)(2 * g.batch + 1) * 4;
-  return (b + 15) & ~(size_t)15;
+// Ring depths: all of the shared memory that the fixed part leaves, at most 4 K and 8 V tiles.
+Plan2 plan2_for(const Geometry& g) {
+  const size_t tile = (size_t)kTile2 * g.head_dim;
+  const size_t fixed = umma2_fixed_bytes(g.group, g.head_dim, g.batch);
+  const size_t budget = 227 * 1024 - 1024;
+  Plan2 pl{2, 2, 0};
+  for (int total = kMaxRingTiles2; total >= 4; --total) {
+#ifdef B200ATTN_U2_KSTAGES
+    const int ks = total >= 9 ? B200ATTN_U2_KSTAGES : total >= 6 ? 3 : 2, vs = total - ks;
+#else
+    const int ks = total >= 9 ? 4 : total >= 6 ? 3 : 2, vs = total - ks;
+#endif
+    const size_t b = fixed + (size_t)total * tile + (size_t)2 * total * 8;
+    if (b <= budget && vs <= 8) { pl.kstages = ks; pl.vstages = vs; pl.bytes = (b + 15) & ~(size_t)15; return pl; }
+  }
+  pl.bytes = (fixed + 4 * tile + 64 + 15) & ~(size_t)15;
+  return pl;
 }
 
 }  // namespace
@@ -552,10 +662,13 @@ bool umma2_supported(const Geometry& g) { return g.group <= 5; }
 
 int umma2_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
   (void)max_seq_len;
-  const size_t smem = umma2_smem_bytes(g, vstages2_for(g));
-  int per_sm = (int)((227 * 1024) / (smem + 1024));
+  const Plan2 pl = plan2_for(g);
+  int per_sm = (int)((227 * 1024) / (pl.bytes + 1024));
+  const int dh = g.head_dim / 128, need = kGroups2 * (16 + 16 * dh * (dh == 1 ? 4 : 1));
+  const int tmem_cols = need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
+  if (per_sm > 512 / tmem_cols) per_sm = 512 / tmem_cols;
+  if (per_sm > 2048 / kThreads2) per_sm = 2048 / kThreads2;
   if (per_sm < 1) per_sm = 1;
-  if (per_sm > 2) per_sm = 2;
   return num_sms * per_sm;
 }
 
@@ -584,15 +697,26 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   p.out_head_base = a.n_out ? a.out_head_base : 0;
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
   p.status = a.status;
-  p.stages = vstages2_for(g);
-  const size_t smem = umma2_smem_bytes(g, p.stages);
+  const Plan2 pl = plan2_for(g);
+  p.stages = pl.vstages;
+  p.kstages = pl.kstages;
   auto launch = [&](auto kernel) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.bytes);
     if (e != cudaSuccess) return e;
-    kernel<<<n, kThreads2, smem, stream>>>(kmap, vmap, p);
+    kernel<<<n, kThreads2, pl.bytes, stream>>>(kmap, vmap, p);
     return cudaGetLastError();
   };
   return g.head_dim == 128 ? launch(attn_streamk_umma2_kernel<128>) : launch(attn_streamk_umma2_kernel<256>);
 }
 
 }  // namespace b200attn
+
+#ifdef B200ATTN_TRACE
+extern "C" int b200attn_debug_trace2(unsigned long long* host_out, int n_ctas, int clear) {
+  if (clear) {
+    static unsigned long long zeros[4096 * 32];
+    return (int)cudaMemcpyToSymbol(b200attn::g_trace2, zeros, sizeof(zeros));
+  }
+  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_trace2, (size_t)n_ctas * 32 * sizeof(unsigned long long));
+}
+#endif

@@ -37,7 +37,8 @@ struct MmaParams {
   int out_hq_total, out_head_base;
   const uint16_t* gate;  // optional bf16 [n_layers][batch][h_q][D]: out *= sigmoid(gate), see store_out
   int* status;
-  int stages;
+  int stages;            // ring depth (the V ring where K and V have their own)
+  int kstages;           // K ring depth, kernels with separate rings only
 };
 
 // ---------------------------------------------------------------------------------------------
