@@ -129,10 +129,18 @@ int b200attn_kv_quant_append(const B200AttnShape* shape, const void* k_new, cons
                                        advance_pos, status, stream);
 }
 
+// The fused step of the all-tcgen05 variant: new-token rows quantised into the cache and positions
+// advanced by the attention launch itself.
+struct FusedStep {
+  const void* k_new;
+  const void* v_new;
+  int* seq_pos;   // null = do not advance
+};
+
 static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, const void* q, const void* gate, const void* k_cache,
                        const void* v_cache, const float* k_scale, const float* v_scale, const int* seq_len,
                        int seq_len_offset, float softmax_scale, int variant, int num_splits, void* workspace,
-                       size_t workspace_bytes, void* out, int* status, void* stream) {
+                       size_t workspace_bytes, void* out, int* status, void* stream, const FusedStep* fused = nullptr) {
   Geometry g;
   int rc = resolve(shape, &g);
   if (rc) return rc;
@@ -153,6 +161,12 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
   if (gate && (v == B200ATTN_VARIANT_SIMT || !aligned16(gate))) return v == B200ATTN_VARIANT_SIMT ? B200ATTN_ERR_VARIANT : B200ATTN_ERR_ALIGN;
   DecodeArgs a{q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                num_splits, workspace, workspace_bytes, out, status, gate, 0, 0, 0, {}};
+  if (fused) {
+    if (v != B200ATTN_VARIANT_UMMA2) return B200ATTN_ERR_VARIANT;
+    a.k_new = fused->k_new;
+    a.v_new = fused->v_new;
+    a.seq_pos = fused->seq_pos;
+  }
   if (peers) {
     if (v == B200ATTN_VARIANT_SIMT) return B200ATTN_ERR_VARIANT;
     if (peers->n_peers < 1 || peers->n_peers > 8 || peers->rank < 0 || peers->rank >= peers->n_peers) return B200ATTN_ERR_SHAPE;
@@ -227,6 +241,14 @@ int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void
     if (workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
   }
   if (!aligned16(q) || !aligned16(out) || !aligned16(workspace)) return B200ATTN_ERR_ALIGN;
+  if (v == B200ATTN_VARIANT_UMMA2) {
+    // one launch: the attention kernel appends the new rows and advances the positions itself
+    if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale) return B200ATTN_ERR_NULL;
+    if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return B200ATTN_ERR_ALIGN;
+    const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr};
+    return decode_impl(shape, nullptr, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
+                       workspace, workspace_bytes, out, status, stream, &fused);
+  }
   rc = b200attn_kv_quant_append_bulk(shape, 1, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 0,
                                      status, stream);
   if (rc) return rc;

@@ -97,6 +97,11 @@ struct DecodeArgs {
   int n_out;          // peer mode (tensor-core variants only): number of rank buffers, 0 = local output
   int out_hq_total, out_head_base;
   void* out_peer[8];
+  // fused step (all-tcgen05 variant only): the new token of every pair is quantised into the cache by
+  // the CTA that owns the pair's last tile, and the last CTA to finish advances the positions
+  const void* k_new = nullptr;   // bf16 [n_layers][batch][h_kv][1][head_dim]; null = attention only
+  const void* v_new = nullptr;
+  int* seq_pos = nullptr;        // positions to advance (the same buffer as seq_len), or null
 };
 
 // Cross-GPU arrive-and-wait on symmetric flag buffers (peer_barrier.cu).

@@ -430,7 +430,7 @@ size_t mma_workspace_bytes(const Geometry& g, int num_ctas) {
   const size_t pairs = (size_t)g.n_layers * g.batch * g.h_kv;
   size_t b = (size_t)num_ctas * 2 * g.group * g.head_dim * sizeof(float);   // ws_acc
   b += (size_t)num_ctas * 2 * 16 * sizeof(float);                            // ws_ml
-  b += pairs * sizeof(int);                                                  // tickets
+  b += (pairs + 1) * sizeof(int);                                            // tickets, exit counter of the fused step
   return (b + 255) & ~(size_t)255;
 }
 
@@ -448,7 +448,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   CUtensorMap kmap, vmap;
   if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride, kTileT) || !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride, kTileT))
     return cudaErrorInvalidValue;
-  MmaParams p;
+  MmaParams p{};
   p.g = g;
   p.q = (const uint16_t*)a.q;
   p.k_scale = a.k_scale;

@@ -479,7 +479,7 @@ cudaError_t launch_decode_umma(const Geometry& g, const DecodeArgs& a, cudaStrea
   if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride, kTileU) ||
       !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride, kTileU))
     return cudaErrorInvalidValue;
-  MmaParams p;
+  MmaParams p{};
   p.g = g;
   p.q = (const uint16_t*)a.q;
   p.k_scale = a.k_scale;

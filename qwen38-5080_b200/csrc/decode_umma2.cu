@@ -115,10 +115,48 @@ __host__ __device__ inline size_t umma2_fixed_bytes(int group, int head_dim, int
   b += (size_t)(kQRing2 * 8 + kGroups2 * 64 + kGroups2 * 32) * 4;    // scales, per-warp maxima and sums
   b += (size_t)kGroups2 * group * (head_dim + 4) * 4;                // dumped states
   b += (size_t)kGroups2 * 16 * 4;                                    // their m, l
-  b += (size_t)(4 + 2 * kQRing2 + 4 * kGroups2 + 2) * 8;             // fixed barriers
+  b += (size_t)(4 + 2 * kQRing2 + 4 * kGroups2 + 3) * 8;             // fixed barriers
   b += 32;                                                           // flags
   b += (size_t)(2 * batch + 1) * 4;
   return b;
+}
+
+// Fused step: quantise the new token of every pair whose last tile the CTA owns (the tile that holds it),
+// exactly as the append kernel does.  Called by the softmax warps; threads work in teams of D/2, 4 values
+// of the K or V row each.  Kept out of line: it runs once per launch and must not disturb the tile loop.
+template <int D>
+__device__ __noinline__ void append_new_rows(int n_layers, int batch, int h_kv, int capacity, long long k_layer_stride,
+                                             long long v_layer_stride, const uint16_t* k_new, const uint16_t* v_new,
+                                             uint8_t* k_cache, uint8_t* v_cache, const float* k_scale, const float* v_scale,
+                                             const int* seq_pos, int tid, long long r0, long long r1,
+                                             const int* sCum, const int* sLen) {
+  (void)n_layers;
+  constexpr int TEAM = D / 2, TEAMS = kSoftmaxWarps2 * 32 / TEAM;
+  const int team = tid / TEAM, e = tid % TEAM, which = e >= D / 4 ? 1 : 0, el = (e % (D / 4)) * 4;
+  Cursor a = locate(r0, sCum, sLen, batch, h_kv);
+  long long cur = r0;
+  int n = 0;
+  while (cur < r1) {
+    const long long pair_end = cur - a.tile + a.tiles_b;
+    if (pair_end <= r1) {
+      const int pos = seq_pos[a.b];
+      if (n % TEAMS == team && pos >= 0 && pos < capacity) {
+        const long long rowi = ((long long)a.layer * batch + a.b) * h_kv + a.h;
+        const uint2 raw = *reinterpret_cast<const uint2*>((which ? v_new : k_new) + rowi * D + el);
+        const float sc = (which ? v_scale : k_scale)[a.layer * h_kv + a.h];
+        const uint32_t bytes = (uint32_t)quantize_e4m3(bf16_bits_to_float(raw.x & 0xFFFFu), sc) |
+                               ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.x >> 16), sc) << 8) |
+                               ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.y & 0xFFFFu), sc) << 16) |
+                               ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.y >> 16), sc) << 24);
+        uint8_t* dst = (which ? v_cache : k_cache) + (long long)a.layer * (which ? v_layer_stride : k_layer_stride) +
+                       (((long long)a.b * h_kv + a.h) * capacity + pos) * D + el;
+        *reinterpret_cast<uint32_t*>(dst) = bytes;
+      }
+      ++n;
+    }
+    cur = pair_end < r1 ? pair_end : r1;
+    if (cur < r1) next_pair(a, sCum, sLen, batch, h_kv);
+  }
 }
 
 template <int D>
@@ -165,8 +203,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   const uint32_t qinfo0 = qrempty0 + 16u, qfree0 = qinfo0 + 8u * kQRing2;
   const uint32_t sfull0 = qfree0 + 8u * kQRing2, sempty0 = sfull0 + 8u * NG;
   const uint32_t pfull0 = sempty0 + 8u * NG, pvdone0 = pfull0 + 8u * NG;
-  const uint32_t dfull0 = pvdone0 + 8u * NG, dempty0 = dfull0 + 8u;
-  constexpr int kFixedBars = 4 + 2 * kQRing2 + 4 * NG + 2;
+  const uint32_t dfull0 = pvdone0 + 8u * NG, dempty0 = dfull0 + 8u, appended0 = dempty0 + 8u;
+  constexpr int kFixedBars = 4 + 2 * kQRing2 + 4 * NG + 3;
   int* sFlags = reinterpret_cast<int*>(bars + kFixedBars + 2 * kstages + 2 * vstages);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
   int* sLen = sFlags + 8;
   int* sCum = sLen + g.batch;
@@ -185,12 +223,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     }
     mbar_init(dfull0, kSoftmaxWarps2);
     mbar_init(dempty0, 1);
+    mbar_init(appended0, kSoftmaxWarps2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     sFlags[0] = 0; sFlags[3] = 0; sFlags[4] = 0; sFlags[5] = 0; sFlags[6] = 0; sFlags[7] = 0;
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
       int len = p.seq_len[b] + p.seq_len_offset;
+      if (p.k_new && (len < 1 || len > g.capacity)) st |= B200ATTN_STATUS_POS_AT_CAPACITY;   // the new token has no slot
       if (len < 0) { len = 0; st |= B200ATTN_STATUS_LEN_NEGATIVE; }
       if (len > g.capacity) { len = g.capacity; st |= B200ATTN_STATUS_LEN_OVER_CAP; }
       sLen[b] = len;
@@ -241,7 +281,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
       const int total_it = (int)(r1 - r0);
       int seg = 0, ks = 0, kround = 0, vs = 0, vround = 0, kissued = 0, vissued = 0, row = 0;
-      bool seg_start = true, ok = true;
+      bool seg_start = true, ok = true, need_append = p.k_new != nullptr;
       TDECL(w_kempty = 0, w_vempty = 0, t_begin = clock64());
       for (int it = 0; it < total_it && ok; ++it) {
         if (seg_start) {
@@ -253,6 +293,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           ++seg;
           seg_start = false;
           row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTile2;
+        }
+        if (need_append && c.tile == c.tiles_b - 1) {   // the tile that holds the new token: its row must be in the cache
+          if (!mbar_wait(appended0, 0, timed_out, p.status)) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          need_append = false;
         }
         if (kround && !TWAIT(w_kempty, mbar_wait(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status))) break;
         mbar_arrive_expect_tx(kfull0 + 8u * ks, TILE_BYTES);
@@ -419,6 +464,13 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     }
   } else if (has_work) {
     // ===== softmax warps: groups of four; group = tile index mod NG; one thread = one token / one output dim =====
+    if (p.k_new) {
+      append_new_rows<D>(g.n_layers, g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new,
+                         p.k_cache_w, p.v_cache_w, p.k_scale, p.v_scale, p.seq_len, tid, r0, r1, sCum, sLen);
+      asm volatile("fence.proxy.async.global;" ::: "memory");   // the rows -> visible to the TMA loads of this CTA
+      __syncwarp();
+      if (lane == 0) mbar_arrive(appended0);
+    }
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
     long long cur = r0;
     int it0 = 0, seg = 0;
@@ -635,6 +687,18 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (p.seq_pos && tid == 0) {
+    // Every CTA read the positions before it got here; the last one to arrive advances them.
+    int arrived;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.exit_count) : "memory");
+    if (arrived == (int)gridDim.x - 1) {
+      for (int b = 0; b < g.batch; ++b) {
+        const int pos = p.seq_pos[b];
+        if (pos >= 0 && pos + 1 <= g.capacity) p.seq_pos[b] = pos + 1;
+      }
+      *p.exit_count = 0;   // ready for the next launch
+    }
+  }
 }
 
 // Ring depths: all of the shared memory that the fixed part leaves, at most 4 K and 8 V tiles.
@@ -678,7 +742,7 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride, kTile2) ||
       !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride, kTile2))
     return cudaErrorInvalidValue;
-  MmaParams p;
+  MmaParams p{};
   p.g = g;
   p.q = (const uint16_t*)a.q;
   p.k_scale = a.k_scale;
@@ -697,6 +761,12 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   p.out_head_base = a.n_out ? a.out_head_base : 0;
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
   p.status = a.status;
+  p.k_new = (const uint16_t*)a.k_new;
+  p.v_new = (const uint16_t*)a.v_new;
+  p.k_cache_w = (uint8_t*)a.k_cache;
+  p.v_cache_w = (uint8_t*)a.v_cache;
+  p.seq_pos = a.seq_pos;
+  p.exit_count = p.tickets + (size_t)g.n_layers * g.batch * g.h_kv;
   const Plan2 pl = plan2_for(g);
   p.stages = pl.vstages;
   p.kstages = pl.kstages;

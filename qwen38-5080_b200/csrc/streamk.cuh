@@ -39,6 +39,14 @@ struct MmaParams {
   int* status;
   int stages;            // ring depth (the V ring where K and V have their own)
   int kstages;           // K ring depth, kernels with separate rings only
+  // fused step (kernels that implement it): new-token rows to quantise into the cache first, positions
+  // to advance at the end, and the exit counter that elects the last CTA
+  const uint16_t* k_new;
+  const uint16_t* v_new;
+  uint8_t* k_cache_w;
+  uint8_t* v_cache_w;
+  int* seq_pos;
+  int* exit_count;
 };
 
 // ---------------------------------------------------------------------------------------------

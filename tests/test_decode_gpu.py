@@ -374,6 +374,55 @@ def test_full_size_properties(pkg, oracle, cuda_device):
         assert (out - want.view(1, 1, h_q, 1)).abs().max().item() <= 2.0 ** -8 * want.max().item(), variant
 
 
+def test_fused_step_equals_separate_launches(pkg, oracle, cuda_device):
+    """The all-tcgen05 variant does a decode step in ONE launch (new rows quantised by the CTA that
+    owns the pair's last tile, positions advanced by the last CTA to finish).  Against the
+    three-launch path of the mma variant: cache bytes and positions identical, outputs in tolerance;
+    ragged lengths that cross a tile boundary, and a sequence already at capacity (flagged, neither
+    written nor advanced)."""
+    n_layers, batch, h_q, h_kv, d, cap, steps = 3, 4, 40, 8, 128, 256, 4
+    lens = [126, 1, 200, cap - 2]          # 126 -> crosses the 128-token tile; cap-2 -> fills up, then refuses
+    g = torch.Generator().manual_seed(23)
+    k0 = torch.randn(n_layers, batch, h_kv, cap, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    v0 = torch.randn(n_layers, batch, h_kv, cap, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    qs = torch.randn(steps, n_layers, batch, h_q, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    kn = torch.randn(steps, n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    vn = torch.randn(steps, n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    caches = {}
+    for variant in ("mma", "umma2"):
+        c = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant=variant)
+        c.set_scales(pkg.calibrate_scales(k0, cap), pkg.calibrate_scales(v0, cap))
+        # ragged prefill: every sequence gets its own prefix; garbage (0xFF = NaN) beyond it
+        c.k_cache.fill_(0xFF)
+        c.v_cache.fill_(0xFF)
+        full = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant="mma")
+        full.set_scales(c.k_scale, c.v_scale)
+        full.prefill(k0, v0)
+        for b, L in enumerate(lens):
+            c.k_cache[:, b, :, :L] = full.k_cache[:, b, :, :L]
+            c.v_cache[:, b, :, :L] = full.v_cache[:, b, :, :L]
+        c.seq_pos.copy_(torch.tensor(lens, dtype=torch.int32))
+        caches[variant] = c
+    for i in range(steps):
+        outs = {v: caches[v].step(qs[i], kn[i], vn[i], count=False).clone() for v in caches}
+        torch.cuda.synchronize()
+        a, u = caches["mma"], caches["umma2"]
+        assert torch.equal(a.k_cache, u.k_cache) and torch.equal(a.v_cache, u.v_cache), f"step {i}: cache bytes differ"
+        assert a.seq_pos.cpu().tolist() == u.seq_pos.cpu().tolist(), f"step {i}"
+        want_pos = [min(L + i + 1, cap) for L in lens]
+        assert u.seq_pos.cpu().tolist() == want_pos
+        full_already = lens[3] + i >= cap
+        st_a, st_u = int(a.status.cpu().view(-1)[0]), int(u.status.cpu().view(-1)[0])
+        assert bool(st_u & pkg._lib.STATUS_POS_AT_CAPACITY) == full_already and bool(st_a & pkg._lib.STATUS_POS_AT_CAPACITY) == full_already
+        m = oracle.error_metrics(outs["umma2"].cpu(), outs["mma"].cpu())
+        assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, (i, m)
+        ref = oracle.decode_step_reference(qs[i].cpu(), u.k_cache.cpu(), u.v_cache.cpu(), u.k_scale.cpu(), u.v_scale.cpu(),
+                                           want_pos, cap)
+        assert_parity(oracle, outs["umma2"].cpu(), ref, f"fused step {i}")
+        for c in caches.values():
+            c.workspace.status.zero_()
+
+
 def test_peer_barrier_wait_is_bounded(pkg, cuda_device):
     """The cross-GPU barrier gives up after its 1 s budget when a peer never arrives (here: a second
     flag buffer that nobody writes), reports it in the status word, and leaves the context usable."""
