@@ -60,12 +60,18 @@ def load_peak() -> tuple[float, str]:
     return PEAK_FALLBACK_GBS, "fallback"
 
 
-def load_traffic(workload: str):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
+KERNEL_NAMES = {"simt": "attn_splitk_simt_kernel<128,5>", "mma": "attn_streamk_mma_kernel<128>",
+                "umma": "attn_streamk_umma_kernel<128>", "umma2": "attn_streamk_umma2_kernel<128>"}
+
+
+def load_traffic(workload: str, variant: str):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any
+    (keyed by workload, then by kernel variant)."""
     p = ROOT / "profiles" / "dram_traffic.json"
     if p.exists():
         try:
-            return json.loads(p.read_text()).get(workload)
+            entry = json.loads(p.read_text()).get(workload)
+            return entry.get(variant) if isinstance(entry, dict) else entry
         except Exception:  # noqa: BLE001
             return None
     return None
@@ -268,6 +274,8 @@ class StepRunner:
     def kernels_per_step(self) -> int:
         if self.peer is not None:
             return (3 if self.advance else 2) + 1   # append (+ bump), attention with fused gather, barrier
+        if self.cache.workspace.resolved == "umma2":
+            return 1                         # the fused step: append, attention, combine and position bump in one launch
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump
         return n + (1 if self.cache.workspace.variant == "simt" and self.cache.workspace.num_splits > 1 else 0)
 
@@ -458,7 +466,7 @@ def run_ours(args) -> int:
         "config": {"workload": workload_name(key, depth, cap), "sharding": f"kv-head tensor parallel x{world}",
                    "l2": f"inputs larger than L2 ({kv_bytes_per_step(depth, h_kv) / 1e6:.0f} MB KV per GPU per step)"
                          if bytes_per_launch > 200e6 else "KV working set smaller than L2: L2-warm figure",
-                   "execution": "CUDA graph replay of append + attention"
+                   "execution": "CUDA graph replay of " + ("the fused append + attention launch" if runner.kernels_per_step() == 1 else "append + attention")
                                 + ((" with the output all-gather fused into the attention kernel (peer stores over NVLink into "
                                      "every rank's gathered buffer) + a cross-GPU barrier kernel, all in the graph"
                                      if runner.peer is not None else
@@ -467,7 +475,7 @@ def run_ours(args) -> int:
         "hbm_gbs": kv_bytes_per_step(depth) / sec / 1e9,
         "frac_of_8TBs": kv_bytes_per_step(depth) / world / sec / 8e12,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": load_traffic(key), "kernel": "attn_splitk_simt_kernel<128,5>" if args.variant == "simt" else "attn_streamk_mma_kernel<128>", "peak_kind": peak_kind,
+                     "traffic": load_traffic(key, runner.cache.workspace.resolved), "kernel": KERNEL_NAMES[runner.cache.workspace.resolved], "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": bytes_per_launch, "launch_us": ksec * 1e6},
         "e2e": {"value": e2e_sec * 1e6, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": runner.kernels_per_step() * steps,
@@ -575,9 +583,9 @@ def run_cfg4(args) -> int:
             "config": {"workload": f"cfg4: {N_LAYERS}-layer batched decode, bs=16, ragged depths U[1024,16384] seed 0 "
                                    f"(sum {sum(depths_all)}), capacity {cap}, fused one-token append per sequence per step",
                        "sharding": f"by sequence x{world} (greedy longest-first on depth), no collective",
-                       "execution": "CUDA graph replay of append + attention + position bump"},
+                       "execution": "CUDA graph replay of " + ("one fused launch: append + attention + position bump" if cache.workspace.resolved == "umma2" else "append + attention + position bump")},
             "hbm_gbs": total_bytes / sec / 1e9, "frac_of_8TBs": total_bytes / world / sec / 8e12,
-            "tokens_per_s": 16 / sec, "gpu_launches": 3 * steps, "clocks": sampler.summary()}
+            "tokens_per_s": 16 / sec, "gpu_launches": (1 if cache.workspace.resolved == "umma2" else 3) * steps, "clocks": sampler.summary()}
     if rank == 0:
         print(json.dumps(line), flush=True)
     finish(torch, dist, world)

@@ -119,6 +119,14 @@ int b200attn_last_cuda_error(void);
 int b200attn_pick_splits(const B200AttnShape* shape, int max_seq_len, int num_sms, int variant);
 
 /*
+ * The kernel variant a request resolves to for this shape: B200ATTN_VARIANT_AUTO becomes the
+ * variant the library would run, an explicit variant comes back unchanged, and a variant the
+ * shape cannot use is the same negative error b200attn_decode would return.  Pure host function;
+ * no counterpart in the reference, whose kernel choice is made by its Python caller.
+ */
+int b200attn_resolve_variant(const B200AttnShape* shape, int variant);
+
+/*
  * Bytes of workspace b200attn_decode needs for `num_splits` (as returned by
  * b200attn_pick_splits, or larger).  The workspace holds split-K partials
  * (m, l, acc[G][D] in fp32) and the arrival tickets of the fused combine.

@@ -42,6 +42,7 @@ PROTOTYPES = {
     "b200attn_error_string": (ctypes.c_char_p, [c_int]),
     "b200attn_last_cuda_error": (c_int, []),
     "b200attn_pick_splits": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_int, c_int]),
+    "b200attn_resolve_variant": (c_int, [ctypes.POINTER(B200AttnShape), c_int]),
     "b200attn_workspace_bytes": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_int, ctypes.POINTER(c_size_t)]),
     "b200attn_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "b200attn_kv_quant_append": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p,

@@ -36,10 +36,19 @@ int resolve(const B200AttnShape* s, Geometry* g) {
   return B200ATTN_OK;
 }
 
-// AUTO = the tensor-core stream-K kernel wherever it applies (per-head scales); the per-token
-// scale layout is served by the SIMT kernel.  An explicit request that cannot be met is an error.
+// AUTO = a tensor-core stream-K kernel wherever one applies (per-head scales); the per-token
+// scale layout is served by the SIMT kernel.  Between the tensor-core kernels: the all-tcgen05
+// kernel (one CTA per SM, 128-token tiles, ~19 us of fixed cost per launch) for long caches with
+// head_dim 128 and query groups of at most 5; the mma.sync kernel (three CTAs per SM, 64-token
+// tiles, finer split) for short ones, where it measured faster (depth 512: 22 vs 25 us).  The
+// lengths live on the device, so the cache capacity stands in for them: at least 2048 token slots
+// and at least 24 tiles per CTA at capacity.  An explicit request that cannot be met is an error.
 int resolve_variant(int variant, const Geometry& g) {
   const bool mma_ok = g.scale_mode == B200ATTN_SCALE_PER_HEAD && g.batch <= 2048;
+  if (variant == B200ATTN_VARIANT_AUTO && mma_ok && umma2_supported(g) && g.head_dim == 128 && g.capacity >= 2048) {
+    const long long tiles = (long long)g.n_layers * g.batch * g.h_kv * ((g.capacity + 127) / 128);
+    if (tiles >= 24LL * 148) return B200ATTN_VARIANT_UMMA2;
+  }
   if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
   if (variant == B200ATTN_VARIANT_SIMT) return variant;
   if (variant == B200ATTN_VARIANT_MMA || variant == B200ATTN_VARIANT_UMMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
@@ -87,6 +96,13 @@ int b200attn_pick_splits(const B200AttnShape* shape, int max_seq_len, int num_sm
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
   return pick(g, v, max_seq_len, num_sms);
+}
+
+int b200attn_resolve_variant(const B200AttnShape* shape, int variant) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  return resolve_variant(variant, g);
 }
 
 int b200attn_workspace_bytes(const B200AttnShape* shape, int num_splits, int variant, size_t* bytes) {

@@ -95,6 +95,8 @@ class Workspace:
     def __init__(self, shape: B200AttnShape, device, variant: str = "auto", num_splits: int = 0,
                  max_seq_len: int | None = None):
         self.variant = variant
+        code = check(_lib.lib().b200attn_resolve_variant(ctypes.byref(shape), VARIANTS[variant]), "b200attn_resolve_variant")
+        self.resolved = next(name for name, c in VARIANTS.items() if c == code)   # the kernel "auto" stands for
         self.num_splits = num_splits or pick_splits(shape, max_seq_len, variant=variant)
         self.nbytes = max(256, workspace_bytes(shape, self.num_splits, variant))
         self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
