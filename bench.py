@@ -216,12 +216,9 @@ class StepRunner:
     def launch_step(self):
         c = self.cache
         if self.peer is not None:
-            # append, then attention storing into every rank's gathered buffer, then the cross-GPU barrier
-            self.pkg.kv_quant_append(self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
-                                     h_q=self.h_q, advance=self.advance, status=c.workspace.status)
-            self.pkg.decode_attention(self.q, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
-                                      workspace=c.workspace, seq_len_offset=0 if self.advance else 1, peer_out=self.peer)
-            self.pkg.peer_barrier(self.peer, c.workspace.status)
+            # append + attention storing into every rank's gathered buffer (+ position bump), then the cross-GPU barrier
+            self.pkg.append_decode(self.q, self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
+                                   workspace=c.workspace, advance=self.advance, peer_out=self.peer, barrier=True)
             return
         self.pkg.append_decode(self.q, self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
                                workspace=c.workspace, advance=self.advance, out=self.out)
@@ -272,8 +269,8 @@ class StepRunner:
             self.gather()
 
     def kernels_per_step(self) -> int:
-        if self.peer is not None:
-            return (3 if self.advance else 2) + 1   # append (+ bump), attention with fused gather, barrier
+        if self.peer is not None:                # (append, bump,) attention with fused gather, barrier
+            return 1 if self.cache.workspace.resolved == "umma2" else (3 if self.advance else 2) + 1
         if self.cache.workspace.resolved == "umma2":
             return 1                         # the fused step: append, attention, combine and position bump in one launch
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump

@@ -236,6 +236,28 @@ int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* pee
                           int* status, void* stream);
 
 /*
+ * The decode step of b200attn_append_decode with the gathered output of b200attn_decode_peers:
+ * append this rank's new K/V rows, attend seq_pos[b]+1 tokens, store the results into every
+ * rank's gathered buffer, advance seq_pos if advance_pos.  One launch with
+ * B200ATTN_VARIANT_UMMA2, three otherwise.  With barrier_flags == NULL, follow it with
+ * b200attn_peer_barrier as for b200attn_decode_peers.  With barrier_flags (the flag buffers
+ * b200attn_peer_barrier takes) the cross-GPU arrive-and-wait is part of the call: done by the
+ * last CTA of the attention launch with B200ATTN_VARIANT_UMMA2, by the barrier kernel launched
+ * behind the attention otherwise; same bounded wait and status bit.
+ * (The reference has no multi-GPU path: no counterpart there.)
+ */
+int b200attn_append_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* peers,
+                                 const void* q_bf16, const void* k_new_bf16, const void* v_new_bf16,
+                                 void* k_cache_u8, void* v_cache_u8,
+                                 float* k_scale, float* v_scale,
+                                 int* seq_pos, int advance_pos,
+                                 float softmax_scale,
+                                 int variant, int num_splits,
+                                 void* workspace, size_t workspace_bytes,
+                                 void* const* barrier_flags,
+                                 int* status, void* stream);
+
+/*
  * Cross-GPU arrive-and-wait.  flags[r] = rank r's flag buffer (int32[world + 1], zero-initialised,
  * symmetric / peer-mapped memory) as addressable from this GPU.  Every rank launches it once per
  * step; it returns when all ranks have arrived.  The wait is bounded (1 s): on expiry
@@ -274,6 +296,11 @@ size_t b200attn_static_scratch_bytes(void);
 /*
  * Fused convenience for one decode step: A (append at seq_pos) then B+C attending
  * seq_pos[b]+1 tokens, then seq_pos[b] += 1 if advance_pos.  Same stream, no host sync.
+ * With B200ATTN_VARIANT_UMMA2 (or AUTO resolving to it) the step is ONE launch: the CTA that
+ * owns the tile holding a pair's new token quantises that row first, and the last CTA to
+ * finish advances the positions; the other variants launch append, attention and the
+ * position kernel one after the other.  Cache bytes, positions and status bits are the same
+ * either way.
  */
 int b200attn_append_decode(const B200AttnShape* shape,
                            const void* q_bf16,

@@ -150,7 +150,8 @@ int b200attn_kv_quant_append(const B200AttnShape* shape, const void* k_new, cons
 struct FusedStep {
   const void* k_new;
   const void* v_new;
-  int* seq_pos;   // null = do not advance
+  int* seq_pos;               // null = do not advance
+  void* const* barrier_flags; // null = no cross-GPU barrier at the end of the launch
 };
 
 static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, const void* q, const void* gate, const void* k_cache,
@@ -182,6 +183,15 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
     a.k_new = fused->k_new;
     a.v_new = fused->v_new;
     a.seq_pos = fused->seq_pos;
+    if (fused->barrier_flags) {
+      if (!peers) return B200ATTN_ERR_NULL;
+      for (int r = 0; r < peers->n_peers; ++r) {
+        if (!fused->barrier_flags[r]) return B200ATTN_ERR_NULL;
+        a.bar_flags[r] = (int*)fused->barrier_flags[r];
+      }
+      a.bar_rank = peers->rank;
+      a.bar_world = peers->n_peers;
+    }
   }
   if (peers) {
     if (v == B200ATTN_VARIANT_SIMT) return B200ATTN_ERR_VARIANT;
@@ -237,15 +247,24 @@ int b200attn_peer_barrier(void* const* flags, int rank, int world, int* status, 
   return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
 }
 
-int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void* k_new, const void* v_new,
-                           void* k_cache, void* v_cache, float* k_scale, float* v_scale, int* seq_pos,
-                           int advance_pos, float softmax_scale, int variant, int num_splits,
-                           void* workspace, size_t workspace_bytes, void* out, int* status, void* stream) {
+static int step_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, const void* q, const void* k_new, const void* v_new,
+                     void* k_cache, void* v_cache, float* k_scale, float* v_scale, int* seq_pos,
+                     int advance_pos, float softmax_scale, int variant, int num_splits,
+                     void* workspace, size_t workspace_bytes, void* out, int* status, void* stream,
+                     void* const* barrier_flags = nullptr) {
   // Validate everything before the first launch so that an argument error launches nothing.
   Geometry g;
   int rc = resolve(shape, &g);
   if (rc) return rc;
-  if (!q || !out || !seq_pos || !status) return B200ATTN_ERR_NULL;
+  if (!q || (!out && !peers) || !seq_pos || !status) return B200ATTN_ERR_NULL;
+  if (peers) {
+    if (peers->n_peers < 1 || peers->n_peers > 8 || peers->rank < 0 || peers->rank >= peers->n_peers) return B200ATTN_ERR_SHAPE;
+    if (peers->h_q_total != g.h_q * peers->n_peers) return B200ATTN_ERR_SHAPE;
+    for (int r = 0; r < peers->n_peers; ++r) {
+      if (!peers->out[r]) return B200ATTN_ERR_NULL;
+      if (!aligned16(peers->out[r])) return B200ATTN_ERR_ALIGN;
+    }
+  }
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
   if (num_splits == 0)
@@ -261,21 +280,45 @@ int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void
     // one launch: the attention kernel appends the new rows and advances the positions itself
     if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale) return B200ATTN_ERR_NULL;
     if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return B200ATTN_ERR_ALIGN;
-    const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr};
-    return decode_impl(shape, nullptr, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
+    const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr, barrier_flags};
+    return decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
                        workspace, workspace_bytes, out, status, stream, &fused);
   }
+  if (peers && v == B200ATTN_VARIANT_SIMT) return B200ATTN_ERR_VARIANT;
   rc = b200attn_kv_quant_append_bulk(shape, 1, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 0,
                                      status, stream);
   if (rc) return rc;
-  rc = b200attn_decode(shape, q, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
-                       workspace, workspace_bytes, out, status, stream);
+  rc = decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
+                   workspace, workspace_bytes, out, status, stream);
   if (rc) return rc;
   if (advance_pos) {
     cudaError_t e = launch_advance_pos(g, 1, seq_pos, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e);
   }
+  if (barrier_flags) return b200attn_peer_barrier(barrier_flags, peers->rank, peers->n_peers, status, stream);
   return B200ATTN_OK;
+}
+
+int b200attn_append_decode(const B200AttnShape* shape, const void* q, const void* k_new, const void* v_new,
+                           void* k_cache, void* v_cache, float* k_scale, float* v_scale, int* seq_pos,
+                           int advance_pos, float softmax_scale, int variant, int num_splits,
+                           void* workspace, size_t workspace_bytes, void* out, int* status, void* stream) {
+  if (!out) return B200ATTN_ERR_NULL;
+  return step_impl(shape, nullptr, q, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, advance_pos, softmax_scale,
+                   variant, num_splits, workspace, workspace_bytes, out, status, stream);
+}
+
+int b200attn_append_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* peers, const void* q, const void* k_new,
+                                 const void* v_new, void* k_cache, void* v_cache, float* k_scale, float* v_scale,
+                                 int* seq_pos, int advance_pos, float softmax_scale, int variant, int num_splits,
+                                 void* workspace, size_t workspace_bytes, void* const* barrier_flags, int* status,
+                                 void* stream) {
+  if (!peers) return B200ATTN_ERR_NULL;
+  if (barrier_flags)
+    for (int r = 0; r < peers->n_peers && r < 8; ++r)
+      if (!barrier_flags[r]) return B200ATTN_ERR_NULL;
+  return step_impl(shape, peers, q, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, advance_pos, softmax_scale,
+                   variant, num_splits, workspace, workspace_bytes, nullptr, status, stream, barrier_flags);
 }
 
 int b200attn_dequant_prefix(const B200AttnShape* shape, int n_tokens, const void* cache, long long layer_stride,

@@ -102,6 +102,9 @@ struct DecodeArgs {
   const void* k_new = nullptr;   // bf16 [n_layers][batch][h_kv][1][head_dim]; null = attention only
   const void* v_new = nullptr;
   int* seq_pos = nullptr;        // positions to advance (the same buffer as seq_len), or null
+  // cross-GPU barrier done by the last CTA to finish (flag buffers as for launch_peer_barrier); 0 ranks = none
+  int* bar_flags[8] = {};
+  int bar_rank = 0, bar_world = 0;
 };
 
 // Cross-GPU arrive-and-wait on symmetric flag buffers (peer_barrier.cu).

@@ -90,7 +90,14 @@ __device__ __forceinline__ void bar_group(int grp) {
 #ifdef B200ATTN_TRACE
 // Development-only stall accounting: cycles spent inside each class of wait, 16 slots per CTA.
 static __device__ unsigned long long g_trace2[4096 * 32];
+// per launch (in issue order, modulo 64): earliest CTA entry, latest CTA exit
+static __device__ unsigned long long g_launch_span[64 * 2];
+static __device__ unsigned int g_entry_ctr;
+#ifdef B200ATTN_TRACE_LIGHT   // time stamps only
+#define TWAIT(acc, expr) (expr)
+#else
 #define TWAIT(acc, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); (acc) += clock64() - t_; return r_; }()
+#endif
 #define TDECL(...) long long __VA_ARGS__
 #define TSTORE(slot, v) g_trace2[blockIdx.x * 32 + (slot)] = (unsigned long long)(v)
 #define TSTAMP(slot) g_trace2[blockIdx.x * 32 + (slot)] = global_timer_ns()
@@ -182,7 +189,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t q_bytes = (uint32_t)G * D * 2;
 
-  if (tid == 0) TSTAMP(16);
+#ifdef B200ATTN_TRACE
+  __shared__ unsigned int s_launch;
+  if (tid == 0) {
+    TSTAMP(16);
+    s_launch = (atomicAdd(&g_entry_ctr, 1u) / gridDim.x) % 64u;
+    atomicMin(&g_launch_span[2 * s_launch], global_timer_ns());
+  }
+#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -666,7 +680,9 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   }
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) TSTAMP(23);
+#ifdef B200ATTN_TRACE
+  if (tid == 0) { TSTAMP(23); atomicMax(&g_launch_span[2 * s_launch + 1], global_timer_ns()); }
+#endif
   if (warp == kIssuerS2) {
     if (sFlags[0] && lane == 0) {
       // A wait gave up: wait (bounded) for everything already issued into this CTA's shared / tensor memory.
@@ -687,16 +703,38 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if (p.seq_pos && tid == 0) {
-    // Every CTA read the positions before it got here; the last one to arrive advances them.
+  if ((p.seq_pos || p.bar_world) && tid == 0) {
+    // Every CTA read the positions and stored its outputs before it got here; the last one to arrive
+    // advances the positions and, in a tensor-parallel step, does the cross-GPU arrive-and-wait.
     int arrived;
     asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.exit_count) : "memory");
     if (arrived == (int)gridDim.x - 1) {
-      for (int b = 0; b < g.batch; ++b) {
-        const int pos = p.seq_pos[b];
-        if (pos >= 0 && pos + 1 <= g.capacity) p.seq_pos[b] = pos + 1;
-      }
+      if (p.seq_pos)
+        for (int b = 0; b < g.batch; ++b) {
+          const int pos = p.seq_pos[b];
+          if (pos >= 0 && pos + 1 <= g.capacity) p.seq_pos[b] = pos + 1;
+        }
       *p.exit_count = 0;   // ready for the next launch
+      if (p.bar_world) {
+        // Same protocol as the stand-alone barrier kernel: bump the own epoch, publish it to every rank
+        // (system-scope release: all peer stores of this launch are ordered before it through the exit
+        // counter), wait (bounded, 1 s) until every rank's epoch has reached it.
+        int* mine = p.bar_flags[p.bar_rank];
+        const int e = mine[p.bar_world] + 1;
+        __threadfence_system();
+        for (int r = 0; r < p.bar_world; ++r)
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.bar_flags[r] + p.bar_rank), "r"(e) : "memory");
+        const unsigned long long t0 = global_timer_ns();
+        for (int r = 0; r < p.bar_world; ++r) {
+          for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + r) : "memory");
+            if (v - e >= 0) break;
+            if (global_timer_ns() - t0 > 1000000000ull) { atomicOr(p.status, B200ATTN_STATUS_WAIT_TIMEOUT); r = p.bar_world; break; }
+          }
+        }
+        mine[p.bar_world] = e;
+      }
     }
   }
 }
@@ -767,6 +805,9 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   p.v_cache_w = (uint8_t*)a.v_cache;
   p.seq_pos = a.seq_pos;
   p.exit_count = p.tickets + (size_t)g.n_layers * g.batch * g.h_kv;
+  for (int r = 0; r < 8; ++r) p.bar_flags[r] = r < a.bar_world ? a.bar_flags[r] : nullptr;
+  p.bar_rank = a.bar_rank;
+  p.bar_world = a.bar_world;
   const Plan2 pl = plan2_for(g);
   p.stages = pl.vstages;
   p.kstages = pl.kstages;
@@ -788,5 +829,15 @@ extern "C" int b200attn_debug_trace2(unsigned long long* host_out, int n_ctas, i
     return (int)cudaMemcpyToSymbol(b200attn::g_trace2, zeros, sizeof(zeros));
   }
   return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_trace2, (size_t)n_ctas * 32 * sizeof(unsigned long long));
+}
+extern "C" int b200attn_debug_launch_spans(unsigned long long* host_out, int reset) {
+  if (reset) {
+    static unsigned long long init[128];
+    for (int i = 0; i < 64; ++i) { init[2 * i] = ~0ull; init[2 * i + 1] = 0; }
+    unsigned int zero = 0;
+    cudaMemcpyToSymbol(b200attn::g_entry_ctr, &zero, sizeof(zero));
+    return (int)cudaMemcpyToSymbol(b200attn::g_launch_span, init, sizeof(init));
+  }
+  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_launch_span, 128 * sizeof(unsigned long long));
 }
 #endif

@@ -47,6 +47,9 @@ struct MmaParams {
   uint8_t* v_cache_w;
   int* seq_pos;
   int* exit_count;
+  // cross-GPU arrive-and-wait by the last CTA to finish (protocol of peer_barrier.cu); bar_world 0 = none
+  int* bar_flags[8];
+  int bar_rank, bar_world;
 };
 
 // ---------------------------------------------------------------------------------------------
