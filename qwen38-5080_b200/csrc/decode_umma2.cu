@@ -300,7 +300,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       for (int it = 0; it < total_it && ok; ++it) {
         if (seg_start) {
           const int qb = seg & 1;
-          if (seg >= 2 && !mbar_wait(qrempty0 + 8u * qb, ((seg >> 1) - 1) & 1, timed_out, p.status)) break;
+          if (seg >= 2 && !mbar_wait_lean(qrempty0 + 8u * qb, ((seg >> 1) - 1) & 1, timed_out, p.status)) break;
           mbar_arrive_expect_tx(qrfull0 + 8u * qb, q_bytes);
           const long long lb = (long long)c.layer * g.batch + c.b;
           bulk_load(smem_u32(sQraw + qb * q_bytes), p.q + (lb * g.h_q + c.h * G) * D, q_bytes, qrfull0 + 8u * qb);
@@ -309,11 +309,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTile2;
         }
         if (need_append && c.tile == c.tiles_b - 1) {   // the tile that holds the new token: its row must be in the cache
-          if (!mbar_wait(appended0, 0, timed_out, p.status)) break;
+          if (!mbar_wait_lean(appended0, 0, timed_out, p.status)) break;
           asm volatile("fence.proxy.async.global;" ::: "memory");
           need_append = false;
         }
-        if (kround && !TWAIT(w_kempty, mbar_wait(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status))) break;
+        if (kround && !TWAIT(w_kempty, mbar_wait_lean(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status))) break;
         mbar_arrive_expect_tx(kfull0 + 8u * ks, TILE_BYTES);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf)
@@ -324,7 +324,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         if (it == total_it - 1) TSTAMP(21);
 #endif
         if (++ks == kstages) { ks = 0; ++kround; }
-        if (vround && !TWAIT(w_vempty, mbar_wait(vempty0 + 8u * vs, (vround - 1) & 1, timed_out, p.status))) break;
+        if (vround && !TWAIT(w_vempty, mbar_wait_lean(vempty0 + 8u * vs, (vround - 1) & 1, timed_out, p.status))) break;
         mbar_arrive_expect_tx(vfull0 + 8u * vs, TILE_BYTES);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf)
@@ -354,13 +354,13 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       TDECL(w_sempty = 0, w_kfull = 0, w_q = 0, t_begin = clock64());
       for (int it = 0; it < total_it && alive; ++it) {
         const int sb = it % NG;
-        if (it >= NG) alive = TWAIT(w_sempty, mbar_wait(sempty0 + 8u * sb, ((it / NG) - 1) & 1, timed_out, p.status));
+        if (it >= NG) alive = TWAIT(w_sempty, mbar_wait_lean(sempty0 + 8u * sb, ((it / NG) - 1) & 1, timed_out, p.status));
         if (alive && seg_start) {
           qb = seg % kQRing2;
-          alive = TWAIT(w_q, mbar_wait(qrfull0 + 8u * (seg & 1), (seg >> 1) & 1, timed_out, p.status));
+          alive = TWAIT(w_q, mbar_wait_lean(qrfull0 + 8u * (seg & 1), (seg >> 1) & 1, timed_out, p.status));
           // every softmax warp has taken the scales of the segment that used this slot before; its
           // score products completed before the score buffer waits above could pass
-          if (alive && seg >= kQRing2) alive = TWAIT(w_q, mbar_wait(qfree0 + 8u * qb, ((seg / kQRing2) - 1) & 1, timed_out, p.status));
+          if (alive && seg >= kQRing2) alive = TWAIT(w_q, mbar_wait_lean(qfree0 + 8u * qb, ((seg / kQRing2) - 1) & 1, timed_out, p.status));
           if (alive) {
             // Each head h: row h = leading e4m3 part of q * 2^e, row 8+h = remainder; lane owns 4 dims
             // per 128-dim block.  2^e puts the head's largest |q| into [128, 256).
@@ -406,7 +406,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           ++seg;
         }
         seg_start = false;
-        if (alive) alive = TWAIT(w_kfull, mbar_wait(kfull0 + 8u * ks, kround & 1, timed_out, p.status));
+        if (alive) alive = TWAIT(w_kfull, mbar_wait_lean(kfull0 + 8u * ks, kround & 1, timed_out, p.status));
 #ifdef B200ATTN_TRACE
         if (it == 0 && lane == 0) TSTAMP(19);
 #endif
@@ -448,8 +448,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       for (int j = 0; j < total_it && alive; ++j) {
         const int pb = j % NG;
         const bool fresh = seg_pos < NG;   // the group's first tile of this segment: its accumulator starts over
-        alive = TWAIT(w_pfull, mbar_wait(pfull0 + 8u * pb, (j / NG) & 1, timed_out, p.status));
-        if (alive) alive = TWAIT(w_vfull, mbar_wait(vfull0 + 8u * vs, vround & 1, timed_out, p.status));
+        alive = TWAIT(w_pfull, mbar_wait_lean(pfull0 + 8u * pb, (j / NG) & 1, timed_out, p.status));
+        if (alive) alive = TWAIT(w_vfull, mbar_wait_lean(vfull0 + 8u * vs, vround & 1, timed_out, p.status));
         if (alive) {
           tc_fence_after();
           if (lane == 0) {
@@ -509,7 +509,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       const int qb = seg % kQRing2;
       float sc[5];
       {
-        const bool ok = mbar_wait(qinfo0 + 8u * qb, (seg / kQRing2) & 1, timed_out, p.status);
+        const bool ok = mbar_wait_lean(qinfo0 + 8u * qb, (seg / kQRing2) & 1, timed_out, p.status);
 #pragma unroll
         for (int h = 0; h < 5; ++h) sc[h] = (ok && h < G) ? sScale[qb * 8 + h] : 0.f;
         __syncwarp();
@@ -526,7 +526,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         jlast = j;
         const int ph = (j / NG) & 1;
         const int tile_tok0 = (c.tile + (j - it0)) * kTile2;
-        const bool sok = TWAIT(w_sfull, mbar_wait(sfull, ph, timed_out, p.status));
+        const bool sok = TWAIT(w_sfull, mbar_wait_lean(sfull, ph, timed_out, p.status));
         uint32_t r[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) r[i] = 0;
@@ -569,7 +569,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         // The P V of this group's previous tile has completed: the probability operand is free and the
         // accumulator holds everything up to that tile.
         bool pok = true;
-        if (j >= NG) pok = TWAIT(w_pvdone, mbar_wait(pvdone, ph ^ 1, timed_out, p.status));
+        if (j >= NG) pok = TWAIT(w_pvdone, mbar_wait_lean(pvdone, ph ^ 1, timed_out, p.status));
         if (rescale && pok) {   // O *= alpha per head, in tensor memory: thread = dim row
           tc_fence_after();
 #pragma unroll
@@ -604,7 +604,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           // A token slot at or beyond the valid length: its V row may hold anything (NaN patterns
           // included) and 0 * NaN would poison O: zero the row in shared memory before the product.
           const int vs = j % vstages;
-          const bool vok = mbar_wait(vfull0 + 8u * vs, (j / vstages) & 1, timed_out, p.status);
+          const bool vok = mbar_wait_lean(vfull0 + 8u * vs, (j / vstages) & 1, timed_out, p.status);
           if (vok && !valid) {
 #pragma unroll
             for (int hf = 0; hf < DH; ++hf)
@@ -624,14 +624,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
 
       // ---------------- end of segment: read O once, hand the group's state to the epilogue warp ----------------
       TDECL(t_seg = clock64());
-      const bool ook = jlast < 0 || mbar_wait(pvdone, (jlast / NG) & 1, timed_out, p.status);
+      const bool ook = jlast < 0 || mbar_wait_lean(pvdone, (jlast / NG) & 1, timed_out, p.status);
 #pragma unroll
       for (int h = 0; h < 5; ++h) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], off);
         if (lane == 0) wl[wq * 8 + h] = l[h];
       }
-      const bool dok = seg < 1 || mbar_wait(dempty0, (seg - 1) & 1, timed_out, p.status);
+      const bool dok = seg < 1 || mbar_wait_lean(dempty0, (seg - 1) & 1, timed_out, p.status);
       bar_group(grp);
       if (ook && dok) {
         if (jlast >= 0) {

@@ -100,6 +100,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+// The same wait with only the first try inline, for kernels with many wait sites and registers to
+// spare: the spin / time-out code at every site costs instruction-cache room that the tile loops need
+// (the all-tcgen05 kernel's role loops are instruction-fetch sensitive; in the register-tight mma.sync
+// kernel the call's spills cost more than the code size saves: 175 -> 180 us).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* timed_out, int* status) {
+  return mbar_wait(bar, parity, timed_out, status);
+}
+__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar, uint32_t parity, volatile int* timed_out, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, timed_out, status);
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
