@@ -60,6 +60,13 @@ def load_peak() -> tuple[float, str]:
     return PEAK_FALLBACK_GBS, "fallback"
 
 
+DTYPES = {"umma2": "fp8-e4m3 KV fed to tcgen05 as stored; query as two e4m3 terms (exact), probabilities as three e5m2 terms; "
+                    "fp32 accumulate/softmax, bf16 in/out",
+          "mma": "fp8-e4m3 KV, f16 tensor-core products, fp32 accumulate/softmax, bf16 in/out",
+          "simt": "fp8-e4m3 KV, fp32 CUDA-core products, fp32 accumulate/softmax, bf16 in/out"}
+DTYPES["umma"] = DTYPES["mma"]
+
+
 KERNEL_NAMES = {"simt": "attn_splitk_simt_kernel<128,5>", "mma": "attn_streamk_mma_kernel<128>",
                 "umma": "attn_streamk_umma_kernel<128>", "umma2": "attn_streamk_umma2_kernel<128>"}
 
@@ -344,38 +351,64 @@ def timed_kernel(torch, runner, steps, warmup) -> float:
 
 
 def timed_e2e(torch, dist, world, runner, steps, warmup) -> tuple[float, int, int]:
-    """Through the public API with HOST buffers: per step, pinned-host q/k/v -> device, the
-    captured step, device -> pinned-host output, and a synchronize (the caller needs the result)."""
-    hq = [runner.q.cpu().pin_memory() for _ in range(2)]
-    hk = [runner.k_new.cpu().pin_memory() for _ in range(2)]
-    hv = [runner.v_new.cpu().pin_memory() for _ in range(2)]
+    """Through the public API with HOST buffers: per step, pinned-host q/k/v -> device, the decode
+    step, device -> pinned-host output, and a synchronize (the caller needs the result).  The
+    copies and the step are captured into one CUDA graph (memcpy nodes + the library's launches),
+    as a host that replays its decode step would do; if that capture is refused the same sequence
+    is issued call by call."""
+    hq, hk, hv = (t.cpu().pin_memory() for t in (runner.q, runner.k_new, runner.v_new))
     src = runner.full_out if world > 1 else runner.out
     hout = torch.empty(src.shape, dtype=src.dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in (hq[0], hk[0], hv[0]))
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
     d2h = hout.numel() * hout.element_size()
 
-    def one(i):
-        runner.q.copy_(hq[i & 1], non_blocking=True)
-        runner.k_new.copy_(hk[i & 1], non_blocking=True)
-        runner.v_new.copy_(hv[i & 1], non_blocking=True)
-        runner.step()
+    def sequence():
+        runner.q.copy_(hq, non_blocking=True)
+        runner.k_new.copy_(hk, non_blocking=True)
+        runner.v_new.copy_(hv, non_blocking=True)
+        runner.launch_step()
+        if runner.gatherer is not None:
+            runner.gather()
         hout.copy_(src, non_blocking=True)
+
+    graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            sequence()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sequence()
+    except Exception as exc:  # noqa: BLE001 - e.g. NCCL capture unsupported: issue the calls one by one
+        print(f"[bench] e2e sequence not captured ({type(exc).__name__}); issuing it call by call", file=sys.stderr)
+        graph = None
+        torch.cuda.synchronize()
+
+    def one():
+        if graph is not None:
+            graph.replay()
+        else:
+            sequence()
         torch.cuda.synchronize()
 
     runner.reset_pos()
-    for i in range(warmup):
-        one(i)
+    for _ in range(warmup):
+        one()
     barrier(dist, world)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        one(i)
+    for _ in range(steps):
+        one()
     e1.record()
     torch.cuda.synchronize()
     wall = (time.perf_counter() - t0) / steps
     barrier(dist, world)
+    runner.reset_pos()
     sec = max(e0.elapsed_time(e1) / 1e3 / steps, wall)
     if world > 1:
         t = torch.tensor([sec], device=runner.device, dtype=torch.float64)
@@ -458,7 +491,7 @@ def run_ours(args) -> int:
     line = {
         "metric": METRIC, "value": sec * 1e6, "unit": "us/step", "n_gpus": world, "steps": steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": "fp8-e4m3 KV, f16 tensor-core products, fp32 accumulate/softmax, bf16 in/out",
+        "vs_baseline": None, "dtype": DTYPES[runner.cache.workspace.resolved],
         "data": "synthetic",
         "config": {"workload": workload_name(key, depth, cap), "sharding": f"kv-head tensor parallel x{world}",
                    "l2": f"inputs larger than L2 ({kv_bytes_per_step(depth, h_kv) / 1e6:.0f} MB KV per GPU per step)"
@@ -576,7 +609,7 @@ def run_cfg4(args) -> int:
     total_bytes = N_LAYERS * H_KV * D * 2 * sum(mean_len)
     line = {"metric": METRIC, "value": sec * 1e6, "unit": "us/step", "n_gpus": world, "steps": steps, "warmup": args.warmup,
             "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": "fp8-e4m3 KV, f16 tensor-core products, fp32 accumulate/softmax, bf16 in/out", "data": "synthetic",
+            "dtype": DTYPES[cache.workspace.resolved], "data": "synthetic",
             "config": {"workload": f"cfg4: {N_LAYERS}-layer batched decode, bs=16, ragged depths U[1024,16384] seed 0 "
                                    f"(sum {sum(depths_all)}), capacity {cap}, fused one-token append per sequence per step",
                        "sharding": f"by sequence x{world} (greedy longest-first on depth), no collective",
