@@ -175,9 +175,12 @@ def run_reference(args) -> int:
     return 0
 
 
+SCALES_TEXT = "per-(layer,kv-head)"
+
+
 def workload_name(key: str, depth: int, cap: int) -> str:
     return (f"{key}: {N_LAYERS}-layer bs=1 decode attention, depth {depth}, capacity {cap}, H_q={H_Q} H_kv={H_KV} "
-            f"D={D}, FP8-e4m3 KV with per-(layer,kv-head) scales, append+attend per step")
+            f"D={D}, FP8-e4m3 KV with {SCALES_TEXT} scales, append+attend per step")
 
 
 # ------------------------------------------------------------------------------------------
@@ -187,12 +190,12 @@ class StepRunner:
     """One workload resident on one GPU: cache, static step buffers, captured graph."""
 
     def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto",
-                 num_splits=0, gather="peer"):
+                 num_splits=0, gather="peer", scale_mode="per_head"):
         self.pkg, self.torch, self.device, self.depth, self.advance = pkg, torch, device, depth, advance
         self.h_q, self.h_kv, self.dist, self.world = h_q, h_kv, dist, world
         g = torch.Generator(device=device).manual_seed(seed)
         self.cache = pkg.FP8StaticCache(N_LAYERS, 1, h_q, h_kv, D, cap, device=device, variant=variant,
-                                        num_splits=num_splits)
+                                        num_splits=num_splits, scale_mode=scale_mode)
         prefix = depth if advance else depth - 1      # cfg2: slot depth-1 is rewritten by every step
         chunk = 8192
         scales_done = False
@@ -200,7 +203,7 @@ class StepRunner:
             n = min(chunk, prefix - t0)
             k = torch.randn(N_LAYERS, 1, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
             v = torch.randn(N_LAYERS, 1, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
-            self.cache.prefill(k, v, calibrate=not scales_done)
+            self.cache.prefill(k, v, calibrate=not scales_done and scale_mode == "per_head")
             scales_done = True
         self.start_pos = prefix
         self.q = torch.randn(N_LAYERS, 1, h_q, D, generator=g, device=device, dtype=torch.bfloat16)
@@ -276,9 +279,10 @@ class StepRunner:
             self.gather()
 
     def kernels_per_step(self) -> int:
+        fused = self.cache.workspace.resolved == "umma2" and not self.cache.per_token
         if self.peer is not None:                # (append, bump,) attention with fused gather, barrier
-            return 1 if self.cache.workspace.resolved == "umma2" else (3 if self.advance else 2) + 1
-        if self.cache.workspace.resolved == "umma2":
+            return 1 if fused else (3 if self.advance else 2) + 1
+        if fused:
             return 1                         # the fused step: append, attention, combine and position bump in one launch
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump
         return n + (1 if self.cache.workspace.variant == "simt" and self.cache.workspace.num_splits > 1 else 0)
@@ -458,7 +462,7 @@ def run_ours(args) -> int:
         room = cap - depth - args.warmup - 4 if advance else 1 << 30   # the cache must not overflow
         steps = max(1, min(args.steps, room))
         runner = StepRunner(pkg, torch, device, depth, cap, advance, h_q, h_kv, seed=rank, dist=dist, world=world,
-                            variant=args.variant, num_splits=args.ctas, gather=args.gather)
+                            variant=args.variant, num_splits=args.ctas, gather=args.gather, scale_mode=args.scales)
         runner.capture()
         if world > 1:   # every rank in step before the first timed (or barrier-carrying) launch
             torch.cuda.synchronize()
@@ -633,13 +637,17 @@ def main() -> int:
     ap.add_argument("--variant", choices=["auto", "mma", "umma", "umma2", "simt"], default="auto", help="attention kernel variant")
     ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
                     help="N > 1: fused peer-store all-gather (default) or NCCL all-gather + reorder copy")
+    ap.add_argument("--scales", choices=["per_head", "per_token"], default="per_head",
+                    help="scale granularity of the FP8 cache (per_token = the reference's frozen [capacity, kv_heads] layout)")
     ap.add_argument("--ctas", type=int, default=0, help="override the split / CTA count (0 = library default)")
     ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    global N_LAYERS
+    global N_LAYERS, SCALES_TEXT
     N_LAYERS = args.layers
+    if args.scales == "per_token":
+        SCALES_TEXT = "per-(token,kv-head)"
     if args.workload == "cfg4":
         if args.impl == "reference":
             raise SystemExit("--impl reference times the bs=1 workloads (cfg1..cfg3)")

@@ -42,17 +42,20 @@ int resolve(const B200AttnShape* s, Geometry* g) {
 // head_dim 128 and query groups of at most 5; the mma.sync kernel (three CTAs per SM, 64-token
 // tiles, finer split) for short ones, where it measured faster (depth 512: 22 vs 25 us).  The
 // lengths live on the device, so the cache capacity stands in for them: at least 2048 token slots
-// and at least 24 tiles per CTA at capacity.  An explicit request that cannot be met is an error.
+// and at least 24 tiles per CTA at capacity.  The all-tcgen05 kernel also takes the per-token scale
+// layout (each softmax thread owns one token and applies its two scales); the mma.sync kernels do not.
+// An explicit request that cannot be met is an error.
 int resolve_variant(int variant, const Geometry& g) {
   const bool mma_ok = g.scale_mode == B200ATTN_SCALE_PER_HEAD && g.batch <= 2048;
-  if (variant == B200ATTN_VARIANT_AUTO && mma_ok && umma2_supported(g) && g.head_dim == 128 && g.capacity >= 2048) {
+  const bool umma2_ok = g.batch <= 2048 && umma2_supported(g);
+  if (variant == B200ATTN_VARIANT_AUTO && umma2_ok && g.head_dim == 128 && g.capacity >= 2048) {
     const long long tiles = (long long)g.n_layers * g.batch * g.h_kv * ((g.capacity + 127) / 128);
     if (tiles >= 24LL * 148) return B200ATTN_VARIANT_UMMA2;
   }
   if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
   if (variant == B200ATTN_VARIANT_SIMT) return variant;
   if (variant == B200ATTN_VARIANT_MMA || variant == B200ATTN_VARIANT_UMMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
-  if (variant == B200ATTN_VARIANT_UMMA2) return mma_ok && umma2_supported(g) ? variant : B200ATTN_ERR_SHAPE;
+  if (variant == B200ATTN_VARIANT_UMMA2) return umma2_ok ? variant : B200ATTN_ERR_SHAPE;
   return B200ATTN_ERR_VARIANT;
 }
 
@@ -276,8 +279,9 @@ static int step_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, c
     if (workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
   }
   if (!aligned16(q) || !aligned16(out) || !aligned16(workspace)) return B200ATTN_ERR_ALIGN;
-  if (v == B200ATTN_VARIANT_UMMA2) {
+  if (v == B200ATTN_VARIANT_UMMA2 && g.scale_mode == B200ATTN_SCALE_PER_HEAD) {
     // one launch: the attention kernel appends the new rows and advances the positions itself
+    // (per-token scales are computed by the append kernel: three launches below)
     if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale) return B200ATTN_ERR_NULL;
     if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return B200ATTN_ERR_ALIGN;
     const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr, barrier_flags};

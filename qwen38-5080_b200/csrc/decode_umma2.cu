@@ -50,6 +50,11 @@ constexpr int kIssuerS2 = kSoftmaxWarps2 + 2;        // query operand, S = K q^T
 constexpr int kIssuerPV2 = kSoftmaxWarps2 + 3;       // O += V^T P^T issue
 constexpr int kThreads2 = (kSoftmaxWarps2 + 4) * 32;
 constexpr int kQRing2 = 4;                           // query operands / score scales in flight (segments)
+#ifdef B200ATTN_U2_HINT_ALWAYS
+constexpr bool kHintAlways = true;
+#else
+constexpr bool kHintAlways = false;
+#endif
 constexpr float kTau = 2.0f;                         // lazy-rescale threshold, log2 units
 constexpr float kPScale = 8192.f;                    // 2^13: p * 2^13 <= 2^15 < 57344 (e5m2 max)
 
@@ -166,7 +171,8 @@ __device__ __noinline__ void append_new_rows(int n_layers, int batch, int h_kv, 
   }
 }
 
-template <int D>
+// PT: per-token scale layout (an instance of its own: the per-head tile loop stays as it is).
+template <int D, bool PT>
 __global__ void __launch_bounds__(kThreads2, (kGroups2 <= 2 && D == 128 && kMaxRingTiles2 <= 5) ? 2 : 1)
 attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                           const MmaParams p) {
@@ -188,6 +194,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   const int kstages = p.kstages, vstages = p.stages;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t q_bytes = (uint32_t)G * D * 2;
+  constexpr bool per_token = PT;   // scales [n_layers][batch][capacity][h_kv]
 
 #ifdef B200ATTN_TRACE
   __shared__ unsigned int s_launch;
@@ -293,6 +300,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     // tile per ~1300 cycles: stage indices, ring rounds and rows are carried, not recomputed)
     if (lane == 0 && has_work) {
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
+      const uint64_t kv_policy = (PT || kHintAlways) ? l2_policy_evict_first() : 0;
+      (void)kv_policy;
       const int total_it = (int)(r1 - r0);
       int seg = 0, ks = 0, kround = 0, vs = 0, vround = 0, kissued = 0, vissued = 0, row = 0;
       bool seg_start = true, ok = true, need_append = p.k_new != nullptr;
@@ -316,8 +325,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         if (kround && !TWAIT(w_kempty, mbar_wait_lean(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status))) break;
         mbar_arrive_expect_tx(kfull0 + 8u * ks, TILE_BYTES);
 #pragma unroll
-        for (int hf = 0; hf < DH; ++hf)
-          tma_load_3d(smem_u32(sK) + ks * TILE_BYTES + hf * kTile2 * 128, &kmap, hf * 128, row, c.layer, kfull0 + 8u * ks);
+        for (int hf = 0; hf < DH; ++hf) {
+          // per-token layout: K/V lines are used once, the scale sectors once per KV head: keep those in L2
+          if (PT || kHintAlways) tma_load_3d_hint(smem_u32(sK) + ks * TILE_BYTES + hf * kTile2 * 128, &kmap, hf * 128, row, c.layer, kfull0 + 8u * ks, kv_policy);
+          else tma_load_3d(smem_u32(sK) + ks * TILE_BYTES + hf * kTile2 * 128, &kmap, hf * 128, row, c.layer, kfull0 + 8u * ks);
+        }
         ++kissued;
 #ifdef B200ATTN_TRACE
         if (it == 0) TSTAMP(18);
@@ -327,8 +339,10 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         if (vround && !TWAIT(w_vempty, mbar_wait_lean(vempty0 + 8u * vs, (vround - 1) & 1, timed_out, p.status))) break;
         mbar_arrive_expect_tx(vfull0 + 8u * vs, TILE_BYTES);
 #pragma unroll
-        for (int hf = 0; hf < DH; ++hf)
-          tma_load_3d(smem_u32(sV) + vs * TILE_BYTES + hf * kTile2 * 128, &vmap, hf * 128, row, c.layer, vfull0 + 8u * vs);
+        for (int hf = 0; hf < DH; ++hf) {
+          if (PT || kHintAlways) tma_load_3d_hint(smem_u32(sV) + vs * TILE_BYTES + hf * kTile2 * 128, &vmap, hf * 128, row, c.layer, vfull0 + 8u * vs, kv_policy);
+          else tma_load_3d(smem_u32(sV) + vs * TILE_BYTES + hf * kTile2 * 128, &vmap, hf * 128, row, c.layer, vfull0 + 8u * vs);
+        }
         ++vissued;
         if (++vs == vstages) { vs = 0; ++vround; }
         row += kTile2;
@@ -342,7 +356,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     }
   } else if (warp == kEpilogue2) {
     if (has_work)
-      epilogue_warp<D, 1, NG, true>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+      epilogue_warp<D, 1, NG, true, PT>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
   } else if (warp == kIssuerS2) {
     // ===================== S issuer warp: query operand, S = K q^T =====================
     if (has_work) {
@@ -394,7 +408,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
                 sts32(qop + off + (uint32_t)h * 128u, whi);
                 sts32(qop + off + (uint32_t)(8 + h) * 128u, wlo);
               }
-              if (lane == 0) sScale[qb * 8 + h] = up * p.k_scale[c.layer * g.h_kv + c.h] * p.score_scale;
+              // per-token scales are applied by the softmax threads, one token each
+              if (lane == 0) sScale[qb * 8 + h] = up * (per_token ? 1.f : p.k_scale[c.layer * g.h_kv + c.h]) * p.score_scale;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand bytes -> visible to the tensor core
             __syncwarp();
@@ -522,10 +537,24 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       // this group's tiles: CTA-wide tile index j with j mod NG == grp
       const int jfirst = it0 + (((grp - it0) % NG) + NG) % NG;
       int jlast = -1;
+      float kst_next = 1.f, vst_next = 1.f;
+      if (per_token && jfirst < it0 + ntiles && (c.tile + (jfirst - it0)) * kTile2 + tok_in_tile < c.len_b) {
+        const long long si = (((long long)c.layer * g.batch + c.b) * g.capacity + (c.tile + (jfirst - it0)) * kTile2 + tok_in_tile) * g.h_kv + c.h;
+        kst_next = __ldg(p.k_scale + si);
+        vst_next = __ldg(p.v_scale + si);
+      }
       for (int j = jfirst; j < it0 + ntiles; j += NG) {
         jlast = j;
         const int ph = (j / NG) & 1;
         const int tile_tok0 = (c.tile + (j - it0)) * kTile2;
+        // this token's K scale and V scale (the latter folded into the probability scaling): loaded one tile
+        // of the group ahead, so the loads have a whole tile period to land
+        const float kst = kst_next, vst = vst_next * kPScale;
+        if (per_token && j + NG < it0 + ntiles && tile_tok0 + NG * kTile2 + tok_in_tile < c.len_b) {
+          const long long si = (((long long)c.layer * g.batch + c.b) * g.capacity + tile_tok0 + NG * kTile2 + tok_in_tile) * g.h_kv + c.h;
+          kst_next = __ldg(p.k_scale + si);
+          vst_next = __ldg(p.v_scale + si);
+        }
         const bool sok = TWAIT(w_sfull, mbar_wait_lean(sfull, ph, timed_out, p.status));
         uint32_t r[16];
 #pragma unroll
@@ -545,7 +574,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         for (int h = 0; h < 5; ++h) {
           s[h] = -INFINITY;
           if (h < G) {
-            if (valid) s[h] = (__uint_as_float(r[h]) + __uint_as_float(r[8 + h])) * sc[h];
+            if (valid) s[h] = (__uint_as_float(r[h]) + __uint_as_float(r[8 + h])) * (sc[h] * kst);
             const float wm = warp_max(s[h]);
             if (lane == 0) wm_w[wq * 8 + h] = wm;
           }
@@ -591,7 +620,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             float pr = 0.f;
             if (h < G && valid) pr = ex2(s[h] - mref[h]);
             l[h] += pr;
-            const float q = pr * kPScale;
+            const float q = pr * vst;
             const float t1 = e5m2_head(q), r1f = q - t1, t2 = e5m2_head(r1f), t3 = r1f - t2;
             const uint32_t b12 = pack_e5m2x2(t1, t2), b3 = pack_e5m2x2(t3, 0.f);
             sts8(pop + (3 * h) * 128 + (pcol ^ ((uint32_t)((3 * h) & 7) << 4)) + pwithin, b12);
@@ -775,7 +804,7 @@ int umma2_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
 }
 
 cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStream_t stream) {
-  if (g.scale_mode != B200ATTN_SCALE_PER_HEAD || g.batch > kMaxBatchMma || !umma2_supported(g)) return cudaErrorNotSupported;
+  if (g.batch > kMaxBatchMma || !umma2_supported(g)) return cudaErrorNotSupported;
   CUtensorMap kmap, vmap;
   if (!encode_cache_map(&kmap, a.k_cache, g, g.k_layer_stride, kTile2) ||
       !encode_cache_map(&vmap, a.v_cache, g, g.v_layer_stride, kTile2))
@@ -817,7 +846,9 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
     kernel<<<n, kThreads2, pl.bytes, stream>>>(kmap, vmap, p);
     return cudaGetLastError();
   };
-  return g.head_dim == 128 ? launch(attn_streamk_umma2_kernel<128>) : launch(attn_streamk_umma2_kernel<256>);
+  if (g.scale_mode == B200ATTN_SCALE_PER_TOKEN)
+    return g.head_dim == 128 ? launch(attn_streamk_umma2_kernel<128, true>) : launch(attn_streamk_umma2_kernel<256, true>);
+  return g.head_dim == 128 ? launch(attn_streamk_umma2_kernel<128, false>) : launch(attn_streamk_umma2_kernel<256, false>);
 }
 
 }  // namespace b200attn

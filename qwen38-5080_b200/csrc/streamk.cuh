@@ -116,6 +116,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
+// The same copy with an L2 eviction policy (createpolicy) for the fetched lines.
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -285,12 +297,12 @@ __device__ __forceinline__ void store_out(const MmaParams& p, long long idx, lon
 // ---------------------------------------------------------------------------------------------
 // epilogue warp: walks the CTA's segments in the consumers' order.  For each it waits for the
 // NW dumped states (m[8], l[8], acc[G][D]; head rows in the xor layout of dump_pos, or in plain
-// dim order when PLAIN), merges them,
+// dim order when PLAIN), merges them (UNIT_V: the V scales are already in the accumulators: per-token layout),
 // and either writes the normalised bf16 output (pair fully owned by this CTA) or writes an
 // (m, l, acc) partial, takes an arrival ticket and, if it is the last owner to arrive, merges all
 // partials of the pair in CTA order and resets the ticket.
 // ---------------------------------------------------------------------------------------------
-template <int D, int NDUMP, int NW = kConsumerWarps, bool PLAIN = false>
+template <int D, int NDUMP, int NW = kConsumerWarps, bool PLAIN = false, bool UNIT_V = false>
 __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long long r0, long long r1,
                                               long long total, int n_eff, const int* sCum, const int* sLen,
                                               const float* sDump, const float* sML, uint32_t dfull0,
@@ -310,7 +322,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     const long long lb = (long long)c.layer * g.batch + c.b;
     const long long pair = lb * g.h_kv + c.h;
     const bool complete = cur == pair_start && seg_end == pair_end;
-    const float vs = p.v_scale[c.layer * g.h_kv + c.h];
+    const float vs = UNIT_V ? 1.f : p.v_scale[c.layer * g.h_kv + c.h];
     const int db = seg % NDUMP;
     const bool ok = mbar_wait(dfull0 + 8u * db, (seg / NDUMP) & 1, timed_out, p.status);
     const float* dump = sDump + db * NW * dump_warp_floats;

@@ -267,6 +267,59 @@ def test_per_token_scale_mode_decode(pkg, oracle, cuda_device):
     assert_parity(oracle, out, ref, "per-token")
 
 
+def test_per_token_scales_on_the_tensor_cores(pkg, oracle, cuda_device):
+    """The per-token scale layout through the all-tcgen05 kernel (each softmax thread applies its
+    token's K and V scales): parity with the oracle on a ragged batch, agreement with the SIMT
+    kernel, and the decode step (append kernel computes the scales, then attention)."""
+    n_layers, batch, h_q, h_kv, d, cap = 2, 3, 40, 8, 128, 640
+    lens = [300, 1, 513]
+    q = torch.zeros(n_layers, batch, h_q, d, dtype=torch.bfloat16)
+    kc = torch.full((n_layers, batch, h_kv, cap, d), 0xFF, dtype=torch.uint8)     # NaN patterns beyond the lengths
+    vc = torch.full_like(kc, 0xFF)
+    ks = torch.full((n_layers, batch, cap, h_kv), float("nan"))
+    vs = torch.full_like(ks, float("nan"))
+    for layer in range(n_layers):
+        for b, L in enumerate(lens):
+            qq, k, v = oracle.make_inputs(300 + 10 * layer + b, h_q, h_kv, d, L)
+            q[layer, b] = qq.view(h_q, d)
+            sk, sv = oracle.token_scales(k), oracle.token_scales(v)
+            ks[layer, b, :L], vs[layer, b, :L] = sk[0], sv[0]
+            kc[layer, b, :, :L] = oracle.quantize_per_token(k, sk)[0]
+            vc[layer, b, :, :L] = oracle.quantize_per_token(v, sv)[0]
+    case = {"q": q, "k_cache": kc, "v_cache": vc, "k_scale": ks, "v_scale": vs, "lens": lens, "capacity": cap}
+    ref = oracle.decode_step_reference(q, torch.where(kc == 0xFF, torch.zeros_like(kc), kc), torch.where(vc == 0xFF, torch.zeros_like(vc), vc),
+                                       torch.nan_to_num(ks), torch.nan_to_num(vs), lens, cap)
+    outs = {}
+    for variant in ("simt", "umma2"):
+        outs[variant], status = run_decode(pkg, case, cuda_device, variant)
+        assert status == 0
+        assert not torch.isnan(outs[variant].float()).any(), variant
+        assert_parity(oracle, outs[variant], ref, f"per-token {variant}")
+    m = oracle.error_metrics(outs["umma2"], outs["simt"])
+    assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, m
+    with pytest.raises(pkg.B200AttnError):        # the mma.sync kernel has no per-token path
+        run_decode(pkg, case, cuda_device, "mma")
+    # the decode step with per-token scales: append kernel (scales + bytes), attention, position kernel
+    caches = {}
+    for variant in ("simt", "umma2"):
+        c = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant=variant, scale_mode="per_token")
+        c.k_cache.copy_(torch.where(kc == 0xFF, torch.zeros_like(kc), kc))
+        c.v_cache.copy_(torch.where(vc == 0xFF, torch.zeros_like(vc), vc))
+        c.k_scale.copy_(torch.nan_to_num(ks))
+        c.v_scale.copy_(torch.nan_to_num(vs))
+        c.seq_pos.copy_(torch.tensor(lens, dtype=torch.int32))
+        caches[variant] = c
+    g = torch.Generator().manual_seed(77)
+    kn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    vn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    step_out = {v: caches[v].step(q.to(cuda_device), kn, vn, count=False).cpu() for v in caches}
+    torch.cuda.synchronize()
+    a, u = caches["simt"], caches["umma2"]
+    assert torch.equal(a.k_cache, u.k_cache) and torch.equal(a.k_scale, u.k_scale) and torch.equal(a.seq_pos, u.seq_pos)
+    ref2 = oracle.decode_step_reference(q, u.k_cache.cpu(), u.v_cache.cpu(), u.k_scale.cpu(), u.v_scale.cpu(), [x + 1 for x in lens], cap)
+    assert_parity(oracle, step_out["umma2"], ref2, "per-token step")
+
+
 @pytest.mark.parametrize("variant", VARIANTS)
 def test_decode_steps_and_cuda_graph_replay(pkg, oracle, cuda_device, variant):
     """Append + attend + advance, eagerly and under CUDA-graph replay: the graph advances the
