@@ -160,8 +160,10 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         const int row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTileT;
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf) {
-          tma_load_3d(smem_u32(sK + (size_t)s * TILE_BYTES + hf * kTileT * 128), &kmap, hf * 128, row, c.layer, fb);
-          tma_load_3d(smem_u32(sV + (size_t)s * TILE_BYTES + hf * kTileT * 128), &vmap, hf * 128, row, c.layer, fb);
+          // K/V lines are used once: an L2 evict-first policy on the copies keeps L2 for what is used again
+          // (queries, partials, outputs): 175.5 -> 169 us at depth 8192
+          tma_load_3d_hint(smem_u32(sK + (size_t)s * TILE_BYTES + hf * kTileT * 128), &kmap, hf * 128, row, c.layer, fb, l2_policy_evict_first());
+          tma_load_3d_hint(smem_u32(sV + (size_t)s * TILE_BYTES + hf * kTileT * 128), &vmap, hf * 128, row, c.layer, fb, l2_policy_evict_first());
         }
         if (++c.tile == c.tiles_b) {
           seg_start = true;
