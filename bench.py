@@ -68,7 +68,7 @@ DTYPES["umma"] = DTYPES["mma"]
 
 
 KERNEL_NAMES = {"simt": "attn_splitk_simt_kernel<128,5>", "mma": "attn_streamk_mma_kernel<128>",
-                "umma": "attn_streamk_umma_kernel<128>", "umma2": "attn_streamk_umma2_kernel<128>"}
+                "umma": "attn_streamk_umma_kernel<128>", "umma2": "attn_streamk_umma2_kernel<128, false>"}
 
 
 def load_traffic(workload: str, variant: str):
