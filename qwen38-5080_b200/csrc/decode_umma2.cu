@@ -739,13 +739,15 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       *p.exit_count = 0;   // ready for the next launch
       if (p.bar_world) {
         // Same protocol as the stand-alone barrier kernel: bump the own epoch, publish it to every rank
-        // (system-scope release: all peer stores of this launch are ordered before it through the exit
-        // counter), wait (bounded, 1 s) until every rank's epoch has reached it.
+        // (all peer stores of this launch are ordered before it through the exit counter and the fence), wait
+        // (bounded, 1 s) until every rank's epoch has reached it.
         int* mine = p.bar_flags[p.bar_rank];
         const int e = mine[p.bar_world] + 1;
+        // one system-scope fence orders every peer store of the launch before the flags; the flag stores
+        // themselves are then relaxed and go out back to back (a release per flag costs a round trip each)
         __threadfence_system();
         for (int r = 0; r < p.bar_world; ++r)
-          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.bar_flags[r] + p.bar_rank), "r"(e) : "memory");
+          asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.bar_flags[r] + p.bar_rank), "r"(e) : "memory");
         const unsigned long long t0 = global_timer_ns();
         for (int r = 0; r < p.bar_world; ++r) {
           for (;;) {
