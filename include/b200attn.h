@@ -294,6 +294,35 @@ int b200attn_decode_static(const B200AttnShape* shape,
 size_t b200attn_static_scratch_bytes(void);
 
 /*
+ * Producer side of the attention block fused with A: head-dim RMS norm of the query and key
+ * heads (weight 1 + w, fp32 inside, one bf16 rounding), rotary embedding on the first
+ * rotary_dim dims in bf16 arithmetic (two rounded products, one rounded sum), then the rotated
+ * key and the value are quantised and appended at seq_pos exactly as b200attn_kv_quant_append
+ * does; the rotated query is written for the attention call.  These are the steps between the
+ * projections and the cache update / attention call of the attention block the reference runs
+ * (transformers' Qwen3.5 model: q_norm, k_norm, apply_rotary_pos_emb; loaded by
+ * runner/loader/nvfp4_model.py:82-88, rotary module rebuilt at :145) and the producer half of
+ * the elementwise work the reference lists around its fused attention
+ * (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150).  One launch for all layers.
+ *   q_raw  : bf16 [n_layers][batch][h_q][head_dim]   (query half of the q projection)
+ *   k_raw, v_new : bf16 [n_layers][batch][h_kv][head_dim]
+ *   q_norm_weight, k_norm_weight : bf16 [n_layers][head_dim]
+ *   cos, sin : bf16 [batch][rotary_dim] for each sequence's position (shared by all layers)
+ *   rotary_dim : 0 .. head_dim, a multiple of head_dim / 16
+ *   q_out  : bf16 [n_layers][batch][h_q][head_dim] (may be q_raw)
+ *   k_out  : optional bf16 [n_layers][batch][h_kv][head_dim] copy of the rotated key, or NULL
+ */
+int b200attn_qk_norm_rope_append(const B200AttnShape* shape,
+                                 const void* q_raw_bf16, const void* k_raw_bf16, const void* v_new_bf16,
+                                 const void* q_norm_weight_bf16, const void* k_norm_weight_bf16, float eps,
+                                 const void* cos_bf16, const void* sin_bf16, int rotary_dim,
+                                 void* q_out_bf16, void* k_out_bf16,
+                                 void* k_cache_u8, void* v_cache_u8,
+                                 float* k_scale, float* v_scale,
+                                 int* seq_pos, int advance_pos,
+                                 int* status, void* stream);
+
+/*
  * Fused convenience for one decode step: A (append at seq_pos) then B+C attending
  * seq_pos[b]+1 tokens, then seq_pos[b] += 1 if advance_pos.  Same stream, no host sync.
  * With B200ATTN_VARIANT_UMMA2 (or AUTO resolving to it) the step is ONE launch: the CTA that

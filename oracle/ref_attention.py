@@ -271,5 +271,35 @@ def cpu_attention_seconds(h_q: int, h_kv: int, d: int, depth: int, capacity: int
             "threads": threads, "samples": len(full)}
 
 
+
+# ------------------------------------------------------------------------------------------
+# producer side of the attention block: q_norm / k_norm + rotary embedding
+# ------------------------------------------------------------------------------------------
+def qk_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """The head-dim RMS norm the reference's model applies to query and key heads before the
+    rotary embedding (Qwen3_5Attention.q_norm / k_norm of transformers 5.5.0, the model class the
+    reference loads: runner/loader/nvfp4_model.py:82-88,145).  Zero-centred weight: computed in
+    fp32 as x * rsqrt(mean(x^2) + eps) * (1 + w), then rounded to x's dtype."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + weight.float())).to(x.dtype)
+
+
+def partial_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding on the first cos.shape[-1] dims of every head, the rest passes through
+    (apply_rotary_pos_emb of the same model file).  x [B, H, T, D]; cos, sin [B, T, R] in x's
+    dtype.  Evaluated in x's dtype as the model does: two rounded products and a rounded sum."""
+    r = cos.shape[-1]
+    c, s = cos.unsqueeze(1), sin.unsqueeze(1)
+    xr, xp = x[..., :r], x[..., r:]
+    rot = torch.cat([-xr[..., r // 2:], xr[..., : r // 2]], dim=-1)
+    return torch.cat([(xr * c) + (rot * s), xp], dim=-1)
+
+
+def producer_reference(q_raw, k_raw, wq, wk, eps, cos, sin):
+    """q_raw [B, H_q, 1, D], k_raw [B, H_kv, 1, D] (projection outputs of one decode step, bf16)
+    -> (q, k) as the attention function and the cache update receive them."""
+    return partial_rope(qk_norm(q_raw, wq, eps), cos, sin), partial_rope(qk_norm(k_raw, wk, eps), cos, sin)
+
+
 def softmax_scale(d: int) -> float:
     return 1.0 / math.sqrt(d)

@@ -68,6 +68,9 @@ PROTOTYPES = {
     "b200attn_append_decode_peers": (c_int, [ctypes.POINTER(B200AttnShape), ctypes.POINTER(B200AttnPeerOut), c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int,
                                              c_int, c_void_p, c_size_t, ctypes.POINTER(c_void_p), c_void_p, c_void_p]),
+    "b200attn_qk_norm_rope_append": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "b200attn_dequant_prefix": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_void_p, c_ll, c_void_p, c_void_p,
                                         c_void_p]),
     "b200attn_calibrate_scales": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_void_p, c_void_p, c_void_p]),

@@ -13,7 +13,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libb200attn.so"
-SOURCES = ["api.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_umma.cu", "decode_umma2.cu", "static_scratch.cu", "peer_barrier.cu"]
+SOURCES = ["api.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_umma.cu", "decode_umma2.cu", "static_scratch.cu", "peer_barrier.cu", "producer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

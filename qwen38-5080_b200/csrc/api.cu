@@ -325,6 +325,28 @@ int b200attn_append_decode_peers(const B200AttnShape* shape, const B200AttnPeerO
                    variant, num_splits, workspace, workspace_bytes, nullptr, status, stream, barrier_flags);
 }
 
+int b200attn_qk_norm_rope_append(const B200AttnShape* shape, const void* q_raw, const void* k_raw, const void* v_new,
+                                 const void* q_norm_weight, const void* k_norm_weight, float eps, const void* cos,
+                                 const void* sin, int rotary_dim, void* q_out, void* k_out, void* k_cache, void* v_cache,
+                                 float* k_scale, float* v_scale, int* seq_pos, int advance_pos, int* status, void* stream) {
+  Geometry g;
+  int rc = resolve(shape, &g);
+  if (rc) return rc;
+  if (!q_raw || !k_raw || !v_new || !q_norm_weight || !k_norm_weight || !cos || !sin || !q_out || !k_cache || !v_cache ||
+      !k_scale || !v_scale || !seq_pos || !status)
+    return B200ATTN_ERR_NULL;
+  // the rotated half must be a whole number of lanes away: rotary_dim a multiple of 2 * head_dim / 32
+  if (rotary_dim < 0 || rotary_dim > g.head_dim || rotary_dim % (2 * (g.head_dim / 32)) != 0) return B200ATTN_ERR_SHAPE;
+  if (!(eps >= 0.f)) return B200ATTN_ERR_SHAPE;
+  if (!aligned16(q_raw) || !aligned16(k_raw) || !aligned16(v_new) || !aligned16(q_out) || !aligned16(k_out) ||
+      !aligned16(k_cache) || !aligned16(v_cache))
+    return B200ATTN_ERR_ALIGN;
+  cudaError_t e = launch_producer(g, rotary_dim, eps, q_raw, k_raw, v_new, q_norm_weight, k_norm_weight, cos, sin, q_out,
+                                  k_out, k_cache, v_cache, k_scale, v_scale, seq_pos, advance_pos, status,
+                                  (cudaStream_t)stream);
+  return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
+}
+
 int b200attn_dequant_prefix(const B200AttnShape* shape, int n_tokens, const void* cache, long long layer_stride,
                             const float* scale, void* out, void* stream) {
   Geometry g;

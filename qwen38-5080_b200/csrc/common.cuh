@@ -79,6 +79,12 @@ cudaError_t launch_dequant_prefix(const Geometry& g, int n_tokens, const void* c
 cudaError_t launch_calibrate(const Geometry& g, int n_tokens, const void* x, float* scale,
                              cudaStream_t stream);
 
+// Producer side: q_norm / k_norm + rotary embedding + quantize-and-append (producer.cu).
+cudaError_t launch_producer(const Geometry& g, int rotary_dim, float eps, const void* q_raw, const void* k_raw,
+                            const void* v_new, const void* wq, const void* wk, const void* cosp, const void* sinp,
+                            void* q_out, void* k_out, void* k_cache, void* v_cache, float* k_scale, float* v_scale,
+                            int* seq_pos, int advance_pos, int* status, cudaStream_t stream);
+
 struct DecodeArgs {
   const void* q;
   const void* k_cache;

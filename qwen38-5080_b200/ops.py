@@ -210,6 +210,36 @@ def append_decode(q, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 
     return out
 
 
+def qk_norm_rope_append(q_raw, k_raw, v_new, q_norm_weight, k_norm_weight, cos, sin, k_cache, v_cache, k_scale, v_scale,
+                        seq_pos, *, eps: float = 1e-6, advance: bool = False, status: torch.Tensor,
+                        q_out: torch.Tensor | None = None, k_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Producer side of the attention block for one decode step of all layers: q_norm / k_norm, rotary
+    embedding, FP8 quantize-and-append of the rotated key and the value.  Returns the rotated query
+    (bf16, q_raw's shape) for `decode_attention`.  cos, sin: bf16 [batch, rotary_dim]."""
+    _need_cuda(q_raw, k_raw, v_new, q_norm_weight, k_norm_weight, cos, sin, k_scale, v_scale, seq_pos, status)
+    h_q, d = q_raw.shape[-2], q_raw.shape[-1]
+    shape = make_shape(h_q, k_cache, v_cache, k_scale)
+    for t in (q_raw, k_raw, v_new, q_norm_weight, k_norm_weight, cos, sin):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError("q_raw, k_raw, v_new, norm weights, cos and sin must be contiguous bf16")
+    if q_raw.numel() != shape.n_layers * shape.batch * h_q * d or k_raw.numel() != shape.n_layers * shape.batch * shape.h_kv * d \
+            or v_new.numel() != k_raw.numel():
+        raise ValueError("q_raw / k_raw / v_new must be [n_layers, batch, heads, head_dim]")
+    if q_norm_weight.numel() != shape.n_layers * d or k_norm_weight.numel() != shape.n_layers * d:
+        raise ValueError("norm weights must be [n_layers, head_dim]")
+    rotary_dim = cos.shape[-1]
+    if cos.numel() != shape.batch * rotary_dim or sin.shape != cos.shape:
+        raise ValueError("cos and sin must be [batch, rotary_dim]")
+    if q_out is None:
+        q_out = torch.empty_like(q_raw)
+    rc = _lib.lib().b200attn_qk_norm_rope_append(
+        ctypes.byref(shape), _ptr(q_raw), _ptr(k_raw), _ptr(v_new), _ptr(q_norm_weight), _ptr(k_norm_weight), eps, _ptr(cos),
+        _ptr(sin), rotary_dim, _ptr(q_out), _ptr(k_out) if k_out is not None else None, _ptr(k_cache), _ptr(v_cache),
+        _ptr(k_scale), _ptr(v_scale), _ptr(seq_pos), int(advance), _ptr(status), _stream())
+    check(rc, "b200attn_qk_norm_rope_append")
+    return q_out
+
+
 def dequant_prefix(cache, scale, n_tokens: int, *, h_q: int | None = None) -> torch.Tensor:
     """bf16 [n_layers, batch, h_kv, n_tokens, head_dim] view of the first n_tokens slots."""
     c5 = _as5(cache)
@@ -234,4 +264,5 @@ def calibrate_scales(x: torch.Tensor, capacity: int) -> torch.Tensor:
 
 
 __all__ = ["B200AttnError", "B200AttnShape", "Workspace", "make_shape", "pick_splits", "workspace_bytes",
-           "kv_quant_append", "decode_attention", "peer_barrier", "append_decode", "dequant_prefix", "calibrate_scales"]
+           "kv_quant_append", "decode_attention", "peer_barrier", "append_decode", "dequant_prefix", "calibrate_scales",
+           "qk_norm_rope_append"]

@@ -35,6 +35,16 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def producer_golden():
+    """Fixtures made by transformers' own q_norm / k_norm / rotary functions (tests/golden/make_golden_producer.py)."""
+    import json
+    import numpy as np
+    data = np.load(ROOT / "tests" / "golden" / "producer_golden.npz")
+    meta = json.loads(bytes(data["meta_json"]).decode())
+    return data, meta
+
+
+@pytest.fixture(scope="session")
 def cuda_device():
     import torch
     if not torch.cuda.is_available():

@@ -172,3 +172,34 @@ def test_per_token_quantisation_roundtrip(oracle):
     kd = oracle.dequantize(kb, s.permute(0, 2, 1).unsqueeze(-1))
     m = oracle.error_metrics(kd, k)
     assert 0.02 < m["nrmse"] < 0.03 and m["cosine"] > 0.9995, m
+
+
+def _bf16(data, key, shape):
+    return torch.from_numpy(data[key].view(np.int16).copy()).view(torch.bfloat16).view(*shape)
+
+
+def producer_case(data, name, m):
+    b, h_q, h_kv, d, r = m["batch"], m["h_q"], m["h_kv"], m["d"], m["rotary_dim"]
+    return {"q_raw": _bf16(data, f"{name}/q_raw", (b, h_q, 1, d)), "k_raw": _bf16(data, f"{name}/k_raw", (b, h_kv, 1, d)),
+            "wq": _bf16(data, f"{name}/wq", (d,)), "wk": _bf16(data, f"{name}/wk", (d,)),
+            "cos": _bf16(data, f"{name}/cos", (b, 1, r)), "sin": _bf16(data, f"{name}/sin", (b, 1, r)),
+            "q_out": _bf16(data, f"{name}/q_out", (b, h_q, 1, d)), "k_out": _bf16(data, f"{name}/k_out", (b, h_kv, 1, d))}
+
+
+def test_producer_oracle_matches_the_model_code(oracle, producer_golden):
+    """q_norm / k_norm + partial rotary embedding: the restatement equals, bit for bit, what the
+    third-party model code the reference runs produced for the committed fixtures."""
+    data, meta = producer_golden
+    names = [n for n in meta if n != "transformers"]
+    assert len(names) >= 4
+    for name in names:
+        m = meta[name]
+        c = producer_case(data, name, m)
+        q, k = oracle.producer_reference(c["q_raw"], c["k_raw"], c["wq"], c["wk"], m["eps"], c["cos"], c["sin"])
+        assert torch.equal(q.view(torch.int16), c["q_out"].view(torch.int16)), name
+        assert torch.equal(k.view(torch.int16), c["k_out"].view(torch.int16)), name
+        # the pass-through dims really pass through, the rotated ones really change
+        r = m["rotary_dim"]
+        normed = oracle.qk_norm(c["q_raw"], c["wq"], m["eps"])
+        assert torch.equal(q[..., r:], normed[..., r:])
+        assert not torch.equal(q[..., :r], normed[..., :r])
