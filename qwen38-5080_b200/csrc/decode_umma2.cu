@@ -35,14 +35,9 @@ namespace b200attn {
 namespace {
 
 constexpr int kTile2 = 128;
-#ifndef B200ATTN_U2_GROUPS
-#define B200ATTN_U2_GROUPS 4
-#endif
-#ifndef B200ATTN_U2_MAXTILES
-#define B200ATTN_U2_MAXTILES 12
-#endif
-constexpr int kGroups2 = B200ATTN_U2_GROUPS;         // softmax groups of four warps; group = tile index mod kGroups2
-constexpr int kMaxRingTiles2 = B200ATTN_U2_MAXTILES; // K + V tiles staged per CTA, at most
+constexpr int kGroups2 = 4;                          // softmax groups of four warps; group = tile index mod kGroups2
+                                                     // (measured at depth 8192: 2 CTAs x 2 groups 175 us, 1 x 4 169 us)
+constexpr int kMaxRingTiles2 = 12;                   // K + V tiles staged per CTA, at most (4 K + 8 V; 3 + 9 and 6 + 6 the same)
 constexpr int kSoftmaxWarps2 = 4 * kGroups2;
 constexpr int kProducer2 = kSoftmaxWarps2;           // TMA issue
 constexpr int kEpilogue2 = kSoftmaxWarps2 + 1;       // merge, output, fused combine
@@ -88,23 +83,14 @@ __device__ __forceinline__ void bar_group(int grp) {
 }
 
 #ifdef B200ATTN_TRACE
-// Development-only stall accounting: cycles spent inside each class of wait, 16 slots per CTA.
-static __device__ unsigned long long g_trace2[4096 * 32];
-// per launch (in issue order, modulo 64): earliest CTA entry, latest CTA exit
+// Development-only time stamps (%globaltimer): per CTA eight stamps of the latest launch (entry, prologue
+// done, first K copy issued / landed, first tile through the softmax, last K copy issued, softmax group 0
+// done, exit); per launch (in issue order, modulo 64) the earliest CTA entry and the latest CTA exit.
+static __device__ unsigned long long g_trace2[4096 * 8];
 static __device__ unsigned long long g_launch_span[64 * 2];
 static __device__ unsigned int g_entry_ctr;
-#ifdef B200ATTN_TRACE_LIGHT   // time stamps only
-#define TWAIT(acc, expr) (expr)
+#define TSTAMP(slot) g_trace2[blockIdx.x * 8 + (slot)] = global_timer_ns()
 #else
-#define TWAIT(acc, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); (acc) += clock64() - t_; return r_; }()
-#endif
-#define TDECL(...) long long __VA_ARGS__
-#define TSTORE(slot, v) g_trace2[blockIdx.x * 32 + (slot)] = (unsigned long long)(v)
-#define TSTAMP(slot) g_trace2[blockIdx.x * 32 + (slot)] = global_timer_ns()
-#else
-#define TWAIT(acc, expr) (expr)
-#define TDECL(...) do { } while (0)
-#define TSTORE(slot, v) do { } while (0)
 #define TSTAMP(slot) do { } while (0)
 #endif
 
@@ -168,7 +154,7 @@ __device__ __noinline__ void append_new_rows(int n_layers, int batch, int h_kv, 
 
 // PT: per-token scale layout (an instance of its own: the per-head tile loop stays as it is).
 template <int D, bool PT>
-__global__ void __launch_bounds__(kThreads2, (kGroups2 <= 2 && D == 128 && kMaxRingTiles2 <= 5) ? 2 : 1)
+__global__ void __launch_bounds__(kThreads2, 1)
 attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                           const MmaParams p) {
   constexpr int NG = kGroups2;
@@ -194,7 +180,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
 #ifdef B200ATTN_TRACE
   __shared__ unsigned int s_launch;
   if (tid == 0) {
-    TSTAMP(16);
+    TSTAMP(0);
     s_launch = (atomicAdd(&g_entry_ctr, 1u) / gridDim.x) % 64u;
     atomicMin(&g_launch_span[2 * s_launch], global_timer_ns());
   }
@@ -268,7 +254,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)sFlags[1];
-  if (tid == 0) TSTAMP(17);
+  if (tid == 0) TSTAMP(1);
 
   if (sFlags[2] & 1) {   // sequences of length 0 have no tiles: their outputs are zero
     const long long rows = (long long)g.n_layers * g.batch;
@@ -299,7 +285,6 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       const int total_it = (int)(r1 - r0);
       int seg = 0, ks = 0, kround = 0, vs = 0, vround = 0, kissued = 0, vissued = 0, row = 0;
       bool seg_start = true, ok = true, need_append = p.k_new != nullptr;
-      TDECL(w_kempty = 0, w_vempty = 0, t_begin = clock64());
       for (int it = 0; it < total_it && ok; ++it) {
         if (seg_start) {
           const int qb = seg & 1;
@@ -316,7 +301,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           asm volatile("fence.proxy.async.global;" ::: "memory");
           need_append = false;
         }
-        if (kround && !TWAIT(w_kempty, mbar_wait_lean(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status))) break;
+        if (kround && !mbar_wait_lean(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status)) break;
         mbar_arrive_expect_tx(kfull0 + 8u * ks, TILE_BYTES);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf) {
@@ -326,11 +311,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         }
         ++kissued;
 #ifdef B200ATTN_TRACE
-        if (it == 0) TSTAMP(18);
-        if (it == total_it - 1) TSTAMP(21);
+        if (it == 0) TSTAMP(2);
+        if (it == total_it - 1) TSTAMP(5);
 #endif
         if (++ks == kstages) { ks = 0; ++kround; }
-        if (vround && !TWAIT(w_vempty, mbar_wait_lean(vempty0 + 8u * vs, (vround - 1) & 1, timed_out, p.status))) break;
+        if (vround && !mbar_wait_lean(vempty0 + 8u * vs, (vround - 1) & 1, timed_out, p.status)) break;
         mbar_arrive_expect_tx(vfull0 + 8u * vs, TILE_BYTES);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf) {
@@ -345,7 +330,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         }
       }
       sFlags[3] = kissued; sFlags[4] = vissued; sFlags[5] = seg;   // read by the drain after a timed-out wait
-      TSTORE(0, clock64() - t_begin); TSTORE(1, w_kempty); TSTORE(2, w_vempty);
+     
     }
   } else if (warp == kEpilogue2) {
     if (has_work)
@@ -358,16 +343,15 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       int seg = 0, qb = 0, ks = 0, kround = 0, issued = 0;
       bool seg_start = true, alive = true;
       const uint64_t descK0 = smem_desc_k128(smem_u32(sK)), descQ0 = smem_desc_k128(smem_u32(sQop));
-      TDECL(w_sempty = 0, w_kfull = 0, w_q = 0, t_begin = clock64());
       for (int it = 0; it < total_it && alive; ++it) {
         const int sb = it % NG;
-        if (it >= NG) alive = TWAIT(w_sempty, mbar_wait_lean(sempty0 + 8u * sb, ((it / NG) - 1) & 1, timed_out, p.status));
+        if (it >= NG) alive = mbar_wait_lean(sempty0 + 8u * sb, ((it / NG) - 1) & 1, timed_out, p.status);
         if (alive && seg_start) {
           qb = seg % kQRing2;
-          alive = TWAIT(w_q, mbar_wait_lean(qrfull0 + 8u * (seg & 1), (seg >> 1) & 1, timed_out, p.status));
+          alive = mbar_wait_lean(qrfull0 + 8u * (seg & 1), (seg >> 1) & 1, timed_out, p.status);
           // every softmax warp has taken the scales of the segment that used this slot before; its
           // score products completed before the score buffer waits above could pass
-          if (alive && seg >= kQRing2) alive = TWAIT(w_q, mbar_wait_lean(qfree0 + 8u * qb, ((seg / kQRing2) - 1) & 1, timed_out, p.status));
+          if (alive && seg >= kQRing2) alive = mbar_wait_lean(qfree0 + 8u * qb, ((seg / kQRing2) - 1) & 1, timed_out, p.status);
           if (alive) {
             // Each head h: row h = leading e4m3 part of q * 2^e, row 8+h = remainder; lane owns 4 dims
             // per 128-dim block.  2^e puts the head's largest |q| into [128, 256).
@@ -414,9 +398,9 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           ++seg;
         }
         seg_start = false;
-        if (alive) alive = TWAIT(w_kfull, mbar_wait_lean(kfull0 + 8u * ks, kround & 1, timed_out, p.status));
+        if (alive) alive = mbar_wait_lean(kfull0 + 8u * ks, kround & 1, timed_out, p.status);
 #ifdef B200ATTN_TRACE
-        if (it == 0 && lane == 0) TSTAMP(19);
+        if (it == 0 && lane == 0) TSTAMP(3);
 #endif
         if (alive) {
           tc_fence_after();
@@ -442,7 +426,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           if (it + 1 < total_it) next_pair(c, sCum, sLen, g.batch, g.h_kv);
         }
       }
-      if (lane == 0) { sFlags[6] = issued; TSTORE(3, clock64() - t_begin); TSTORE(4, w_sempty); TSTORE(5, w_kfull); TSTORE(6, w_q); }
+      if (lane == 0) { sFlags[6] = issued; }
     }
   } else if (warp == kIssuerPV2) {
     // ===================== P V issuer warp: O[group] += V^T P^T =====================
@@ -452,12 +436,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       int seg_pos = 0, vs = 0, vround = 0, issued = 0;
       bool alive = true;
       const uint64_t descV0 = smem_desc_k128(smem_u32(sV)), descP0 = smem_desc_k128(smem_u32(sPop));
-      TDECL(w_pfull = 0, w_vfull = 0, t_begin = clock64());
       for (int j = 0; j < total_it && alive; ++j) {
         const int pb = j % NG;
         const bool fresh = seg_pos < NG;   // the group's first tile of this segment: its accumulator starts over
-        alive = TWAIT(w_pfull, mbar_wait_lean(pfull0 + 8u * pb, (j / NG) & 1, timed_out, p.status));
-        if (alive) alive = TWAIT(w_vfull, mbar_wait_lean(vfull0 + 8u * vs, vround & 1, timed_out, p.status));
+        alive = mbar_wait_lean(pfull0 + 8u * pb, (j / NG) & 1, timed_out, p.status);
+        if (alive) alive = mbar_wait_lean(vfull0 + 8u * vs, vround & 1, timed_out, p.status);
         if (alive) {
           tc_fence_after();
           if (lane == 0) {
@@ -482,7 +465,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           if (j + 1 < total_it) next_pair(c, sCum, sLen, g.batch, g.h_kv);
         }
       }
-      if (lane == 0) { sFlags[7] = issued; TSTORE(7, clock64() - t_begin); TSTORE(8, w_pfull); TSTORE(9, w_vfull); }
+      if (lane == 0) { sFlags[7] = issued; }
     }
   } else if (has_work) {
     // ===== softmax warps: groups of four; group = tile index mod NG; one thread = one token / one output dim =====
@@ -508,7 +491,6 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     float* wmax = sWmax + grp * 64;
     float* wl = sWl + grp * 32;
     float* dump = sDump + grp * G * DP;
-    TDECL(w_sfull = 0, w_pvdone = 0, w_bar = 0, w_seg = 0, t_begin = clock64());
 
     while (cur < r1) {
       const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
@@ -548,7 +530,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           kst_next = __ldg(p.k_scale + si);
           vst_next = __ldg(p.v_scale + si);
         }
-        const bool sok = TWAIT(w_sfull, mbar_wait_lean(sfull, ph, timed_out, p.status));
+        const bool sok = mbar_wait_lean(sfull, ph, timed_out, p.status);
         uint32_t r[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) r[i] = 0;
@@ -572,7 +554,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             if (lane == 0) wm_w[wq * 8 + h] = wm;
           }
         }
-        TWAIT(w_bar, (bar_group(grp), true));
+        bar_group(grp);
         bool rescale = false;
         float alpha[5];
 #pragma unroll
@@ -591,7 +573,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         // The P V of this group's previous tile has completed: the probability operand is free and the
         // accumulator holds everything up to that tile.
         bool pok = true;
-        if (j >= NG) pok = TWAIT(w_pvdone, mbar_wait_lean(pvdone, ph ^ 1, timed_out, p.status));
+        if (j >= NG) pok = mbar_wait_lean(pvdone, ph ^ 1, timed_out, p.status);
         if (rescale && pok) {   // O *= alpha per head, in tensor memory: thread = dim row
           tc_fence_after();
 #pragma unroll
@@ -640,12 +622,11 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(pfull);
 #ifdef B200ATTN_TRACE
-        if (tid == 0 && j == 0) TSTAMP(20);
+        if (tid == 0 && j == 0) TSTAMP(4);
 #endif
       }
 
       // ---------------- end of segment: read O once, hand the group's state to the epilogue warp ----------------
-      TDECL(t_seg = clock64());
       const bool ook = jlast < 0 || mbar_wait_lean(pvdone, (jlast / NG) & 1, timed_out, p.status);
 #pragma unroll
       for (int h = 0; h < 5; ++h) {
@@ -690,20 +671,17 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(dfull0);
       bar_group(grp);   // the sums are reused by the next segment
-#ifdef B200ATTN_TRACE
-      w_seg += clock64() - t_seg;
-#endif
       ++seg;
       it0 += ntiles;
       cur = seg_end;
       if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
     }
-    if (tid == 0) { TSTAMP(22); TSTORE(10, clock64() - t_begin); TSTORE(11, w_sfull); TSTORE(12, w_pvdone); TSTORE(13, w_bar); TSTORE(14, w_seg); }
+    if (tid == 0) { TSTAMP(6); }
   }
   tc_fence_before();
   __syncthreads();
 #ifdef B200ATTN_TRACE
-  if (tid == 0) { TSTAMP(23); atomicMax(&g_launch_span[2 * s_launch + 1], global_timer_ns()); }
+  if (tid == 0) { TSTAMP(7); atomicMax(&g_launch_span[2 * s_launch + 1], global_timer_ns()); }
 #endif
   if (warp == kIssuerS2) {
     if (sFlags[0] && lane == 0) {
@@ -770,11 +748,7 @@ Plan2 plan2_for(const Geometry& g) {
   const size_t budget = 227 * 1024 - 1024;
   Plan2 pl{2, 2, 0};
   for (int total = kMaxRingTiles2; total >= 4; --total) {
-#ifdef B200ATTN_U2_KSTAGES
-    const int ks = total >= 9 ? B200ATTN_U2_KSTAGES : total >= 6 ? 3 : 2, vs = total - ks;
-#else
     const int ks = total >= 9 ? 4 : total >= 6 ? 3 : 2, vs = total - ks;
-#endif
     const size_t b = fixed + (size_t)total * tile + (size_t)2 * total * 8;
     if (b <= budget && vs <= 8) { pl.kstages = ks; pl.vstages = vs; pl.bytes = (b + 15) & ~(size_t)15; return pl; }
   }
@@ -851,10 +825,10 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
 #ifdef B200ATTN_TRACE
 extern "C" int b200attn_debug_trace2(unsigned long long* host_out, int n_ctas, int clear) {
   if (clear) {
-    static unsigned long long zeros[4096 * 32];
+    static unsigned long long zeros[4096 * 8];
     return (int)cudaMemcpyToSymbol(b200attn::g_trace2, zeros, sizeof(zeros));
   }
-  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_trace2, (size_t)n_ctas * 32 * sizeof(unsigned long long));
+  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_trace2, (size_t)n_ctas * 8 * sizeof(unsigned long long));
 }
 extern "C" int b200attn_debug_launch_spans(unsigned long long* host_out, int reset) {
   if (reset) {
