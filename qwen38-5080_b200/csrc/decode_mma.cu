@@ -1,4 +1,5 @@
-// Tensor-core stream-K variant of the FP8-KV decode attention (the default path).
+// mma.sync stream-K variant of the FP8-KV decode attention (the library's choice for short caches and for
+// shapes the all-tcgen05 kernel does not take: query groups above 5, head_dim 256 by default).
 //
 // One persistent launch covers every (layer, sequence, kv head) of a decode step:
 //   * the KV cache is cut into tiles of TILE_T tokens; all tiles of the step form one linear
@@ -20,8 +21,8 @@
 //     epilogue warp merges the four states off the critical path.  A pair owned by one CTA is
 //     normalised and written directly; otherwise each owner writes an (m, l, acc) partial and
 //     takes an arrival ticket; the last arriver merges the partials in CTA order (deterministic,
-//     so replays are bitwise identical) and resets the ticket.  Nothing ever spins on another CTA.  The only waits are on the CTA's own copy barriers, and those
-//     are bounded: on expiry the CTA flags B200ATTN_STATUS_WAIT_TIMEOUT, stops waiting, drains
+//     so replays are bitwise identical) and resets the ticket.  Nothing ever spins on another CTA.
+//     The only waits are on the CTA's own copy barriers, and those are bounded: on expiry the CTA flags B200ATTN_STATUS_WAIT_TIMEOUT, stops waiting, drains
 //     its copies and returns.
 //
 // It replaces repeat_kv + eager attention + the capacity mask of the reference

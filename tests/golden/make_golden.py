@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generate tests/golden/attn_golden.npz from the reference's OWN functions.
 
-Run in a container that has the reference checkout (default /root/reference); the fixtures
+Run where the reference checkout is available (pass its root with --reference); the fixtures
 are committed because the checkout does not travel to the GPU box.
 
 For every case the inputs are seeded exactly as bench/micro/attn_length_effect.py:99-102 does
@@ -13,7 +13,7 @@ set to the case's head shape.  Stored per case: the bf16 output bits, the fp64 o
 float32), the scales, and sha256 digests of q and of the quantised K/V bytes so a test can
 prove it rebuilt the same inputs.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <reference checkout>
 """
 from __future__ import annotations
 
@@ -61,7 +61,7 @@ def sha(t: torch.Tensor) -> str:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", type=Path, default=Path("/root/reference"))
+    ap.add_argument("--reference", type=Path, required=True, help="root of the reference checkout")
     args = ap.parse_args()
     ref = load_reference_module(args.reference)
     torch.set_num_threads(1)  # one thread: the stored bits do not depend on the thread count
