@@ -476,6 +476,64 @@ def test_fused_step_equals_separate_launches(pkg, oracle, cuda_device):
             c.workspace.status.zero_()
 
 
+def test_random_shapes_against_the_oracle(pkg, oracle, cuda_device):
+    """Seeded random geometries: layers, batch, heads, group size, head_dim, capacity, CTA count and
+    ragged lengths that hit the awkward places (0, 1, one token short of / exactly / one token past
+    a tile, full capacity), NaN bytes beyond every length; every tensor-core kernel that takes the
+    shape against the oracle, and the one-launch step against the three-launch step."""
+    rng = np.random.default_rng(20260)
+    for trial in range(14):
+        d = 256 if trial % 5 == 4 else 128
+        h_kv = int(rng.choice([1, 2, 4, 8]))
+        group = int(rng.integers(1, 6)) if trial % 3 else int(rng.integers(1, 9))
+        n_layers, batch = int(rng.integers(1, 5)), int(rng.integers(1, 6))
+        cap = int(rng.choice([128, 192, 640, 1100]))
+        special = [0, 1, 127, 128, 129, 255, 256, 257, cap - 1, cap]
+        lens = [int(min(cap, rng.choice(special) if rng.random() < 0.6 else rng.integers(0, cap + 1))) for _ in range(batch)]
+        if not any(lens):
+            lens[0] = 1
+        case = build_case(oracle, n_layers, batch, h_kv * group, h_kv, d, lens, cap, seed=1000 + trial, fill_byte=0xFF)
+        clean = dict(case)
+        clean["k_cache"] = case["k_cache"].clone()
+        clean["v_cache"] = case["v_cache"].clone()
+        for b, L in enumerate(lens):
+            clean["k_cache"][:, b, :, L:] = 0
+            clean["v_cache"][:, b, :, L:] = 0
+        ref = oracle.decode_step_reference(case["q"], clean["k_cache"], clean["v_cache"], case["k_scale"], case["v_scale"], lens, cap)
+        for b, L in enumerate(lens):
+            if L == 0:
+                ref[:, b] = 0          # an empty sequence has no attention output: defined as zeros
+        what = f"trial {trial}: layers {n_layers} batch {batch} h_kv {h_kv} group {group} d {d} cap {cap} lens {lens}"
+        n_ctas = int(rng.choice([0, 0, 7, 148, 333]))
+        for variant in ("mma", "umma2"):
+            if unsupported(pkg, variant, h_kv * group, h_kv):
+                continue
+            out, status = run_decode(pkg, case, cuda_device, variant, num_splits=n_ctas)
+            assert status == 0, (what, variant)
+            assert not torch.isnan(out.float()).any(), (what, variant)
+            assert_parity(oracle, out, ref, f"{what} {variant} ctas {n_ctas}")
+        if group <= 5 and max(lens) < cap:
+            # one decode step, fused launch vs append + attention + position kernels
+            g = torch.Generator().manual_seed(trial)
+            kn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
+            vn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
+            res = {}
+            for variant in ("mma", "umma2"):
+                c = pkg.FP8StaticCache(n_layers, batch, h_kv * group, h_kv, d, cap, device=cuda_device, variant=variant)
+                c.set_scales(case["k_scale"].to(cuda_device), case["v_scale"].to(cuda_device))
+                c.k_cache.copy_(case["k_cache"])
+                c.v_cache.copy_(case["v_cache"])
+                c.seq_pos.copy_(torch.tensor(lens, dtype=torch.int32))
+                out = c.step(case["q"].to(cuda_device), kn, vn, count=False)
+                torch.cuda.synchronize()
+                res[variant] = (out.cpu(), c.k_cache.cpu(), c.v_cache.cpu(), c.seq_pos.cpu(), int(c.status.cpu().view(-1)[0]))
+            a, u = res["mma"], res["umma2"]
+            assert a[4] == 0 and u[4] == 0, what
+            assert torch.equal(a[1], u[1]) and torch.equal(a[2], u[2]) and torch.equal(a[3], u[3]), what
+            m = oracle.error_metrics(u[0], a[0])
+            assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, (what, m)
+
+
 def test_peer_barrier_wait_is_bounded(pkg, cuda_device):
     """The cross-GPU barrier gives up after its 1 s budget when a peer never arrives (here: a second
     flag buffer that nobody writes), reports it in the status word, and leaves the context usable."""
