@@ -78,7 +78,7 @@ def test_null_and_misaligned_arguments_launch_nothing(pkg):
     assert lib.b200attn_decode(ctypes.byref(s), a, a, a, a, a, a, 0, 0.1, 0, -3, a, 1 << 30, a, a, None) == L.ERR_SPLITS
     assert lib.b200attn_kv_quant_append(ctypes.byref(s), None, a, a, a, a, a, a, 1, a, None) == L.ERR_NULL
     assert lib.b200attn_kv_quant_append_bulk(ctypes.byref(s), 9000, a, a, a, a, a, a, a, 1, a, None) == L.ERR_CAPACITY
-    tok = _shape(pkg, scale_mode=1)   # per-token scales are served by the SIMT kernel only
+    tok = _shape(pkg, scale_mode=1)   # per-token scales: the SIMT and all-tcgen05 kernels, not the mma.sync ones
     assert lib.b200attn_decode(ctypes.byref(tok), a, a, a, a, a, a, 0, 0.1, L.VARIANT_MMA, 0, a, 1 << 30, a, a, None) == L.ERR_SHAPE
     assert b"aligned" in lib.b200attn_error_string(L.ERR_ALIGN)
 
@@ -92,3 +92,58 @@ def test_python_wrappers_refuse_cpu_tensors(pkg):
     with pytest.raises(ValueError):
         pkg.kv_quant_append(torch.zeros(1, 1, 8, 128, dtype=torch.bfloat16), torch.zeros(1, 1, 8, 128, dtype=torch.bfloat16),
                             kc, kc, sc, sc, torch.zeros(1, dtype=torch.int32), status=torch.zeros(1, dtype=torch.int32))
+
+
+def test_kernel_choice_is_a_pure_host_function(pkg):
+    """b200attn_resolve_variant: what AUTO stands for on a shape, explicit requests echoed or refused."""
+    lib, L = pkg._lib.lib(), pkg._lib
+    r = lambda shape, v=0: lib.b200attn_resolve_variant(ctypes.byref(shape), v)   # noqa: E731
+    assert r(_shape(pkg)) == L.VARIANT_UMMA2                                   # the benchmark shape, depth 8192
+    assert r(_shape(pkg, capacity=32768 + 256)) == L.VARIANT_UMMA2
+    assert r(_shape(pkg, capacity=1024)) == L.VARIANT_MMA                       # short cache
+    assert r(_shape(pkg, n_layers=1, capacity=2048)) == L.VARIANT_MMA           # too few tiles per CTA
+    assert r(_shape(pkg, h_q=24, h_kv=4, head_dim=256)) == L.VARIANT_MMA        # group 6, head_dim 256
+    assert r(_shape(pkg, scale_mode=1)) == L.VARIANT_UMMA2                      # per-token scales, long cache
+    assert r(_shape(pkg, scale_mode=1, capacity=512)) == L.VARIANT_SIMT         # per-token scales, short cache
+    assert r(_shape(pkg, h_q=8, h_kv=1, batch=16, capacity=16640)) == L.VARIANT_MMA   # group 8
+    for v in (L.VARIANT_SIMT, L.VARIANT_MMA, L.VARIANT_UMMA, L.VARIANT_UMMA2):
+        assert r(_shape(pkg), v) == v
+    assert r(_shape(pkg, h_q=48, h_kv=8), L.VARIANT_UMMA2) == L.ERR_SHAPE       # group 6: refused, not substituted
+    assert r(_shape(pkg, scale_mode=1), L.VARIANT_MMA) == L.ERR_SHAPE
+    assert r(_shape(pkg), 9) == L.ERR_VARIANT
+    assert r(_shape(pkg, head_dim=96)) == L.ERR_SHAPE
+    # the workspace follows the resolved kernel: one CTA per SM for the all-tcgen05 kernel
+    s = _shape(pkg)
+    n = lib.b200attn_pick_splits(ctypes.byref(s), 8192, 148, 0)
+    assert n == 148
+    out = ctypes.c_size_t(0)
+    assert lib.b200attn_workspace_bytes(ctypes.byref(s), n, 0, ctypes.byref(out)) == 0
+    assert out.value >= n * 2 * (5 * 128 + 16) * 4 + (64 * 8 + 1) * 4
+
+
+def test_step_and_producer_entry_points_validate_before_launching(pkg):
+    lib, L = pkg._lib.lib(), pkg._lib
+    s = _shape(pkg)
+    a = 0x10000  # fake, aligned, never dereferenced: validation fails first
+    # b200attn_append_decode: NULL new rows with the one-launch kernel, bad variant
+    assert lib.b200attn_append_decode(ctypes.byref(s), a, None, a, a, a, a, a, a, 1, 0.1, 0, 0, a, 1 << 30, a, a, None) == L.ERR_NULL
+    assert lib.b200attn_append_decode(ctypes.byref(s), a, a, a, a, a, a, a, a, 1, 0.1, 0, 0, a, 16, a, a, None) == L.ERR_WORKSPACE
+    assert lib.b200attn_append_decode(ctypes.byref(s), a, a, a, a, a, a, a, a, 1, 0.1, 0, 0, a, 1 << 30, None, a, None) == L.ERR_NULL
+    # b200attn_append_decode_peers: peers missing, wrong head total, NULL peer buffer, NULL flag
+    peers = L.B200AttnPeerOut(2, 0, 80, 0, (ctypes.c_void_p * 8)(a, a))
+    args = (a, a, a, a, a, a, a, a, 1, 0.1, 0, 0, a, 1 << 30)
+    assert lib.b200attn_append_decode_peers(ctypes.byref(s), None, *args, None, a, None) == L.ERR_NULL
+    bad_total = L.B200AttnPeerOut(2, 0, 40, 0, (ctypes.c_void_p * 8)(a, a))
+    assert lib.b200attn_append_decode_peers(ctypes.byref(s), ctypes.byref(bad_total), *args, None, a, None) == L.ERR_SHAPE
+    hole = L.B200AttnPeerOut(2, 0, 80, 0, (ctypes.c_void_p * 8)(a, None))
+    assert lib.b200attn_append_decode_peers(ctypes.byref(s), ctypes.byref(hole), *args, None, a, None) == L.ERR_NULL
+    flags = (ctypes.c_void_p * 8)(a, None)
+    assert lib.b200attn_append_decode_peers(ctypes.byref(s), ctypes.byref(peers), *args, flags, a, None) == L.ERR_NULL
+    # b200attn_qk_norm_rope_append: NULL input, rotary_dim not a whole number of lanes / too large, misaligned
+    pargs = lambda **kw: [kw.get("q", a), a, a, a, a, ctypes.c_float(kw.get("eps", 1e-6)), a, a, kw.get("r", 64), kw.get("qo", a), None,  # noqa: E731
+                          a, a, a, a, a, 1, a, None]
+    assert lib.b200attn_qk_norm_rope_append(ctypes.byref(s), *pargs(q=None)) == L.ERR_NULL
+    assert lib.b200attn_qk_norm_rope_append(ctypes.byref(s), *pargs(r=12)) == L.ERR_SHAPE
+    assert lib.b200attn_qk_norm_rope_append(ctypes.byref(s), *pargs(r=136)) == L.ERR_SHAPE
+    assert lib.b200attn_qk_norm_rope_append(ctypes.byref(s), *pargs(eps=float("nan"))) == L.ERR_SHAPE
+    assert lib.b200attn_qk_norm_rope_append(ctypes.byref(s), *pargs(qo=a + 8)) == L.ERR_ALIGN
