@@ -45,9 +45,9 @@ PEAK_FALLBACK_GBS = 6650.0
 REF_SAMPLE_LAYERS = 4
 
 
-def kv_bytes_per_step(depth: int, h_kv: int = H_KV) -> int:
+def kv_bytes_per_step(depth: int, h_kv: int | None = None) -> int:
     """Algorithmic bytes of one step: K and V e4m3 bytes of every attended token, all layers."""
-    return N_LAYERS * h_kv * depth * D * 2
+    return N_LAYERS * (H_KV if h_kv is None else h_kv) * depth * D * 2
 
 
 def load_peak() -> tuple[float, str]:
@@ -639,13 +639,17 @@ def main() -> int:
                     help="N > 1: fused peer-store all-gather (default) or NCCL all-gather + reorder copy")
     ap.add_argument("--scales", choices=["per_head", "per_token"], default="per_head",
                     help="scale granularity of the FP8 cache (per_token = the reference's frozen [capacity, kv_heads] layout)")
+    ap.add_argument("--heads", default="", help="H_q,H_kv,head_dim instead of the metric's 40,8,128 (e.g. 24,4,256: the "
+                    "reference model's own attention shape; not the metric)")
     ap.add_argument("--ctas", type=int, default=0, help="override the split / CTA count (0 = library default)")
     ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    global N_LAYERS, SCALES_TEXT
+    global N_LAYERS, SCALES_TEXT, H_Q, H_KV, D
     N_LAYERS = args.layers
+    if args.heads:
+        H_Q, H_KV, D = (int(x) for x in args.heads.split(","))
     if args.scales == "per_token":
         SCALES_TEXT = "per-(token,kv-head)"
     if args.workload == "cfg4":

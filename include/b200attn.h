@@ -54,7 +54,7 @@ extern "C" {
                                          tensor cores from shared memory unconverted, scores in tensor memory */
 #define B200ATTN_VARIANT_UMMA2    4   /* both products on tcgen05.mma: S = K q^T and O += V^T P^T read the staged FP8 tiles
                                          directly (V as an MN-major operand), scores and the output accumulator live in
-                                         tensor memory; query groups of at most 5 heads; both scale layouts */
+                                         tensor memory; both scale layouts */
 
 /* scale granularity of the FP8 cache */
 #define B200ATTN_SCALE_PER_HEAD   0   /* fp32 scale per (layer, kv_head): [n_layers][h_kv] */

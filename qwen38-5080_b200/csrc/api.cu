@@ -38,9 +38,9 @@ int resolve(const B200AttnShape* s, Geometry* g) {
 
 // AUTO = a tensor-core stream-K kernel wherever one applies (per-head scales); the per-token
 // scale layout is served by the SIMT kernel.  Between the tensor-core kernels: the all-tcgen05
-// kernel (one CTA per SM, 128-token tiles, ~19 us of fixed cost per launch) for long caches with
-// head_dim 128 and query groups of at most 5; the mma.sync kernel (three CTAs per SM, 64-token
-// tiles, finer split) for short ones, where it measured faster (depth 512: 22 vs 25 us).  The
+// kernel (one CTA per SM, 128-token tiles, ~19 us of fixed cost per launch) for long caches; the
+// mma.sync kernel (three CTAs per SM, 64-token tiles, finer split) for short ones, where it
+// measured faster (depth 512: 22 vs 25 us).  The
 // lengths live on the device, so the cache capacity stands in for them: at least 2048 token slots
 // and at least 24 tiles per CTA at capacity.  The all-tcgen05 kernel also takes the per-token scale
 // layout (each softmax thread owns one token and applies its two scales); the mma.sync kernels do not.
@@ -48,7 +48,7 @@ int resolve(const B200AttnShape* s, Geometry* g) {
 int resolve_variant(int variant, const Geometry& g) {
   const bool mma_ok = g.scale_mode == B200ATTN_SCALE_PER_HEAD && g.batch <= 2048;
   const bool umma2_ok = g.batch <= 2048 && umma2_supported(g);
-  if (variant == B200ATTN_VARIANT_AUTO && umma2_ok && g.head_dim == 128 && g.capacity >= 2048) {
+  if (variant == B200ATTN_VARIANT_AUTO && umma2_ok && g.capacity >= 2048) {
     const long long tiles = (long long)g.n_layers * g.batch * g.h_kv * ((g.capacity + 127) / 128);
     if (tiles >= 24LL * 148) return B200ATTN_VARIANT_UMMA2;
   }

@@ -1,5 +1,5 @@
-// mma.sync stream-K variant of the FP8-KV decode attention (the library's choice for short caches and for
-// shapes the all-tcgen05 kernel does not take: query groups above 5, head_dim 256 by default).
+// mma.sync stream-K variant of the FP8-KV decode attention (the library's choice for short caches, where its
+// finer split over three CTAs per SM beats the all-tcgen05 kernel's fixed cost).
 //
 // One persistent launch covers every (layer, sequence, kv head) of a decode step:
 //   * the KV cache is cut into tiles of TILE_T tokens; all tiles of the step form one linear

@@ -24,7 +24,8 @@
 //      zeroed in shared memory first (their bytes may be NaN patterns);
 //   5. at the end of a pair each group reads its O once (one thread per dim), adds the three
 //      terms per head, and hands its state (m, l, acc) to the epilogue warp, which merges the two.
-// G <= 5 query heads per KV head (3 G <= 16 operand rows).
+// Query groups of up to 5 heads use 16 probability-operand rows (3 G <= 16), groups of 6 to 8 an instance
+// with 32 rows.
 //
 // All waits are bounded as in the other kernels; tensor memory is allocated by the issuer warp at
 // kernel start and always freed by it after the final barrier.
@@ -103,7 +104,7 @@ __host__ __device__ inline size_t umma2_fixed_bytes(int group, int head_dim, int
   const int dh = head_dim / 128;
   size_t b = 1024;                                                   // alignment slack
   b += (size_t)kQRing2 * dh * 16 * 128;                              // query operands
-  b += (size_t)kGroups2 * 16 * 128;                                  // probability operands
+  b += (size_t)kGroups2 * (group <= 5 ? 16 : 32) * 128;              // probability operands
   b += (size_t)2 * group * head_dim * 2;                             // raw query rows
   b += (size_t)(kQRing2 * 8 + kGroups2 * 64 + kGroups2 * 32) * 4;    // scales, per-warp maxima and sums
   b += (size_t)kGroups2 * group * (head_dim + 4) * 4;                // dumped states
@@ -152,8 +153,9 @@ __device__ __noinline__ void append_new_rows(int n_layers, int batch, int h_kv, 
   }
 }
 
-// PT: per-token scale layout (an instance of its own: the per-head tile loop stays as it is).
-template <int D, bool PT>
+// PT: per-token scale layout; GM: largest query group the instance takes, 5 (16 probability-operand rows) or 8 (32 rows).
+// Instances of their own: the tile loop of the benchmark configuration (GM 5, per-head scales) stays as it is.
+template <int D, bool PT, int GM>
 __global__ void __launch_bounds__(kThreads2, 1)
 attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                           const MmaParams p) {
@@ -162,12 +164,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   constexpr int TILE_BYTES = kTile2 * D;
   constexpr int DP = D + 4;
   constexpr int QOP_BYTES = DH * 16 * 128;   // query operand
-  constexpr int POP_BYTES = 16 * 128;        // probability operand: 16 rows x 128 tokens
+  constexpr int PROWS = GM <= 5 ? 16 : 32;   // rows of the probability operand / columns of an output accumulator
+  constexpr int POP_BYTES = PROWS * 128;     // probability operand: PROWS rows x 128 tokens
   // The four 32-token products of a tile go to separate accumulators (summed once per segment): products
   // into one accumulator execute back to back at full latency, independent ones overlap.
-  constexpr int OSPLIT = DH == 1 ? 4 : 1;
+  constexpr int OSPLIT = DH == 1 ? (GM <= 5 ? 4 : 2) : 1;
   constexpr uint32_t O_COL0 = NG * 16;       // tensor memory: S of each group, then O of each group
-  constexpr uint32_t O_COLS = 16 * DH * OSPLIT;   // per group
+  constexpr uint32_t O_COLS = PROWS * DH * OSPLIT;   // per group
+  constexpr uint32_t kIdescPVg = GM <= 5 ? kIdescPV : ((kIdescPV & ~(0x3Fu << 17)) | ((32u >> 3) << 17));   // N = PROWS
   constexpr uint32_t TMEM_NEED = NG * (16 + O_COLS);
   constexpr uint32_t TMEM_COLS = TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   const Geometry& g = p.g;
@@ -449,9 +453,10 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
 #pragma unroll
             for (int hf = 0; hf < DH; ++hf)
 #pragma unroll
-              for (int kb = 0; kb < 4; ++kb)   // 32 tokens per instruction: 32 rows of 128 bytes further in V, 32 bytes further in P
-                umma_f8(d0 + 16u * hf + (OSPLIT > 1 ? 16u * kb : 0u), a0 + (uint64_t)(hf * (kTile2 * 128 >> 4) + kb * (4096 >> 4)),
-                        b0 + (uint64_t)(kb * 2), kIdescPV, ((OSPLIT == 1 && kb) || !fresh) ? 1u : 0u);
+              for (int kb = 0; kb < 4; ++kb)   // 32 tokens per instruction: 32 rows of 128 bytes further in V, 32 bytes further in P;
+                                             // accumulator block kb mod OSPLIT, started over by its first product of a fresh tile
+                umma_f8(d0 + (uint32_t)PROWS * (hf + (OSPLIT > 1 ? kb % OSPLIT : 0)), a0 + (uint64_t)(hf * (kTile2 * 128 >> 4) + kb * (4096 >> 4)),
+                        b0 + (uint64_t)(kb * 2), kIdescPVg, (kb >= OSPLIT || !fresh) ? 1u : 0u);
             umma_commit(pvdone0 + 8u * pb);    // O holds tile j; the group's probability operand is free
             umma_commit(vempty0 + 8u * vs);    // V tile has been read
           }
@@ -491,23 +496,27 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     float* wmax = sWmax + grp * 64;
     float* wl = sWl + grp * 32;
     float* dump = sDump + grp * G * DP;
+    if (GM > 5) {   // rows 24..31 of the probability operand are never written again: make them finite once
+#pragma unroll
+      for (int n = 24; n < 32; ++n) sts8(pop + n * 128 + (pcol ^ ((uint32_t)(n & 7) << 4)) + pwithin, 0u);
+    }
 
     while (cur < r1) {
       const long long pair_start = cur - c.tile, pair_end = pair_start + c.tiles_b;
       const long long seg_end = pair_end < r1 ? pair_end : r1;
       const int ntiles = (int)(seg_end - cur);
       const int qb = seg % kQRing2;
-      float sc[5];
+      float sc[GM];
       {
         const bool ok = mbar_wait_lean(qinfo0 + 8u * qb, (seg / kQRing2) & 1, timed_out, p.status);
 #pragma unroll
-        for (int h = 0; h < 5; ++h) sc[h] = (ok && h < G) ? sScale[qb * 8 + h] : 0.f;
+        for (int h = 0; h < GM; ++h) sc[h] = (ok && h < G) ? sScale[qb * 8 + h] : 0.f;
         __syncwarp();
         if (lane == 0) mbar_arrive(qfree0 + 8u * qb);
       }
-      float mref[5], l[5];
+      float mref[GM], l[GM];
 #pragma unroll
-      for (int h = 0; h < 5; ++h) { mref[h] = -INFINITY; l[h] = 0.f; }
+      for (int h = 0; h < GM; ++h) { mref[h] = -INFINITY; l[h] = 0.f; }
 
       // this group's tiles: CTA-wide tile index j with j mod NG == grp
       const int jfirst = it0 + (((grp - it0) % NG) + NG) % NG;
@@ -543,10 +552,10 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         if (lane == 0) mbar_arrive(sempty);
         const bool valid = sok && tile_tok0 + tok_in_tile < c.len_b;
         // scores and the tile maximum per head (over the group's 128 tokens)
-        float s[5];
+        float s[GM];
         float* wm_w = wmax + ph * 32;
 #pragma unroll
-        for (int h = 0; h < 5; ++h) {
+        for (int h = 0; h < GM; ++h) {
           s[h] = -INFINITY;
           if (h < G) {
             if (valid) s[h] = (__uint_as_float(r[h]) + __uint_as_float(r[8 + h])) * (sc[h] * kst);
@@ -556,9 +565,9 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         }
         bar_group(grp);
         bool rescale = false;
-        float alpha[5];
+        float alpha[GM];
 #pragma unroll
-        for (int h = 0; h < 5; ++h) {
+        for (int h = 0; h < GM; ++h) {
           alpha[h] = 1.f;
           if (h < G) {
             const float tmax = fmaxf(fmaxf(wm_w[h], wm_w[8 + h]), fmaxf(wm_w[16 + h], wm_w[24 + h]));
@@ -577,21 +586,22 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         if (rescale && pok) {   // O *= alpha per head, in tensor memory: thread = dim row
           tc_fence_after();
 #pragma unroll
-          for (int hf = 0; hf < DH * OSPLIT; ++hf) {
+          for (int blk = 0; blk < DH * OSPLIT * (PROWS / 16); ++blk) {   // 16 columns at a time; column c belongs to head c / 3
             uint32_t o[16];
-            tmem_ld16(tmem_o + 16u * hf, o);
+            tmem_ld16(tmem_o + 16u * blk, o);
 #pragma unroll
-            for (int h = 0; h < 5; ++h)
-#pragma unroll
-              for (int t = 0; t < 3; ++t) o[3 * h + t] = __float_as_uint(__uint_as_float(o[3 * h + t]) * alpha[h]);
-            tmem_st16(tmem_o + 16u * hf, o);
+            for (int i = 0; i < 16; ++i) {
+              const int col = (blk % (PROWS / 16)) * 16 + i;
+              if (col < 3 * GM) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha[col / 3]);
+            }
+            tmem_st16(tmem_o + 16u * blk, o);
           }
           tc_fence_before();
         }
         // probabilities: p <= 2^kTau; p * 2^13 as three e5m2 terms, rows 3h..3h+2 of the operand
         if (pok) {
 #pragma unroll
-          for (int h = 0; h < 5; ++h) {
+          for (int h = 0; h < GM; ++h) {
             float pr = 0.f;
             if (h < G && valid) pr = ex2(s[h] - mref[h]);
             l[h] += pr;
@@ -602,7 +612,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             sts8(pop + (3 * h + 1) * 128 + (pcol ^ ((uint32_t)((3 * h + 1) & 7) << 4)) + pwithin, b12 >> 8);
             sts8(pop + (3 * h + 2) * 128 + (pcol ^ ((uint32_t)((3 * h + 2) & 7) << 4)) + pwithin, b3);
           }
-          sts8(pop + 15 * 128 + (pcol ^ (7u << 4)) + pwithin, 0u);   // unused 16th row: keep it finite
+          if (GM <= 5) sts8(pop + 15 * 128 + (pcol ^ (7u << 4)) + pwithin, 0u);   // unused 16th row: keep it finite (rows 24..31: zeroed once)
         }
         if (tile_tok0 + kTile2 > c.len_b) {
           // A token slot at or beyond the valid length: its V row may hold anything (NaN patterns
@@ -629,7 +639,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       // ---------------- end of segment: read O once, hand the group's state to the epilogue warp ----------------
       const bool ook = jlast < 0 || mbar_wait_lean(pvdone, (jlast / NG) & 1, timed_out, p.status);
 #pragma unroll
-      for (int h = 0; h < 5; ++h) {
+      for (int h = 0; h < GM; ++h) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], off);
         if (lane == 0) wl[wq * 8 + h] = l[h];
@@ -641,17 +651,21 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           tc_fence_after();
 #pragma unroll
           for (int hf = 0; hf < DH; ++hf) {
-            float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+            float acc[GM];
+#pragma unroll
+            for (int h = 0; h < GM; ++h) acc[h] = 0.f;
 #pragma unroll
             for (int sp = 0; sp < OSPLIT; ++sp) {
-              uint32_t o[16];
-              tmem_ld16(tmem_o + 16u * (hf + sp), o);   // OSPLIT > 1 only with DH == 1
+              uint32_t o[PROWS];
 #pragma unroll
-              for (int h = 0; h < 5; ++h)
+              for (int cb = 0; cb < PROWS / 16; ++cb)
+                tmem_ld16(tmem_o + (uint32_t)PROWS * (hf + sp) + 16u * cb, *reinterpret_cast<uint32_t(*)[16]>(o + 16 * cb));   // OSPLIT > 1 only with DH == 1
+#pragma unroll
+              for (int h = 0; h < GM; ++h)
                 acc[h] += __uint_as_float(o[3 * h]) + __uint_as_float(o[3 * h + 1]) + __uint_as_float(o[3 * h + 2]);
             }
 #pragma unroll
-            for (int h = 0; h < 5; ++h)
+            for (int h = 0; h < GM; ++h)
               if (h < G) dump[h * DP + hf * 128 + tok_in_tile] = acc[h] * (1.f / kPScale);
           }
           tc_fence_before();
@@ -660,10 +674,10 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
 #pragma unroll
             for (int hf = 0; hf < DH; ++hf) dump[h * DP + hf * 128 + tok_in_tile] = 0.f;
         }
-        if (wq == 0 && lane < 5) {
+        if (wq == 0 && lane < GM) {
           float m = mref[0];
 #pragma unroll
-          for (int h = 1; h < 5; ++h) m = lane == h ? mref[h] : m;
+          for (int h = 1; h < GM; ++h) m = lane == h ? mref[h] : m;
           sML[grp * 16 + lane] = m;
           sML[grp * 16 + 8 + lane] = wl[lane] + wl[8 + lane] + wl[16 + lane] + wl[24 + lane];
         }
@@ -758,7 +772,7 @@ Plan2 plan2_for(const Geometry& g) {
 
 }  // namespace
 
-bool umma2_supported(const Geometry& g) { return g.group <= 5; }
+bool umma2_supported(const Geometry& g) { return g.group <= 8; }
 
 int umma2_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
   (void)max_seq_len;
@@ -815,9 +829,13 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
     kernel<<<n, kThreads2, pl.bytes, stream>>>(kmap, vmap, p);
     return cudaGetLastError();
   };
-  if (g.scale_mode == B200ATTN_SCALE_PER_TOKEN)
-    return g.head_dim == 128 ? launch(attn_streamk_umma2_kernel<128, true>) : launch(attn_streamk_umma2_kernel<256, true>);
-  return g.head_dim == 128 ? launch(attn_streamk_umma2_kernel<128, false>) : launch(attn_streamk_umma2_kernel<256, false>);
+  const bool pt = g.scale_mode == B200ATTN_SCALE_PER_TOKEN, wide = g.group > 5;
+  if (g.head_dim == 128) {
+    if (wide) return pt ? launch(attn_streamk_umma2_kernel<128, true, 8>) : launch(attn_streamk_umma2_kernel<128, false, 8>);
+    return pt ? launch(attn_streamk_umma2_kernel<128, true, 5>) : launch(attn_streamk_umma2_kernel<128, false, 5>);
+  }
+  if (wide) return pt ? launch(attn_streamk_umma2_kernel<256, true, 8>) : launch(attn_streamk_umma2_kernel<256, false, 8>);
+  return pt ? launch(attn_streamk_umma2_kernel<256, true, 5>) : launch(attn_streamk_umma2_kernel<256, false, 5>);
 }
 
 }  // namespace b200attn

@@ -102,13 +102,13 @@ def test_kernel_choice_is_a_pure_host_function(pkg):
     assert r(_shape(pkg, capacity=32768 + 256)) == L.VARIANT_UMMA2
     assert r(_shape(pkg, capacity=1024)) == L.VARIANT_MMA                       # short cache
     assert r(_shape(pkg, n_layers=1, capacity=2048)) == L.VARIANT_MMA           # too few tiles per CTA
-    assert r(_shape(pkg, h_q=24, h_kv=4, head_dim=256)) == L.VARIANT_MMA        # group 6, head_dim 256
+    assert r(_shape(pkg, h_q=24, h_kv=4, head_dim=256)) == L.VARIANT_UMMA2      # the reference model's shape: group 6, head_dim 256
     assert r(_shape(pkg, scale_mode=1)) == L.VARIANT_UMMA2                      # per-token scales, long cache
     assert r(_shape(pkg, scale_mode=1, capacity=512)) == L.VARIANT_SIMT         # per-token scales, short cache
-    assert r(_shape(pkg, h_q=8, h_kv=1, batch=16, capacity=16640)) == L.VARIANT_MMA   # group 8
+    assert r(_shape(pkg, h_q=8, h_kv=1, batch=16, capacity=16640)) == L.VARIANT_UMMA2   # group 8
     for v in (L.VARIANT_SIMT, L.VARIANT_MMA, L.VARIANT_UMMA, L.VARIANT_UMMA2):
         assert r(_shape(pkg), v) == v
-    assert r(_shape(pkg, h_q=48, h_kv=8), L.VARIANT_UMMA2) == L.ERR_SHAPE       # group 6: refused, not substituted
+    assert r(_shape(pkg, h_q=48, h_kv=8), L.VARIANT_UMMA2) == L.VARIANT_UMMA2   # group 6
     assert r(_shape(pkg, scale_mode=1), L.VARIANT_MMA) == L.ERR_SHAPE
     assert r(_shape(pkg), 9) == L.ERR_VARIANT
     assert r(_shape(pkg, head_dim=96)) == L.ERR_SHAPE
