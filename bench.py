@@ -67,8 +67,12 @@ DTYPES = {"umma2": "fp8-e4m3 KV fed to tcgen05 as stored; query as two e4m3 term
 DTYPES["umma"] = DTYPES["mma"]
 
 
-KERNEL_NAMES = {"simt": "attn_splitk_simt_kernel<128,5>", "mma": "attn_streamk_mma_kernel<128>",
-                "umma": "attn_streamk_umma_kernel<128>", "umma2": "attn_streamk_umma2_kernel<128, false>"}
+def kernel_name(variant: str, per_token: bool = False) -> str:
+    """Name of the dominant kernel as a profiler lists it, for the head shape of this run."""
+    group = H_Q // H_KV
+    return {"simt": f"attn_splitk_simt_kernel<{D},{group}>", "mma": f"attn_streamk_mma_kernel<{D}>",
+            "umma": f"attn_streamk_umma_kernel<{D}>",
+            "umma2": f"attn_streamk_umma2_kernel<{D}, {'true' if per_token else 'false'}, {5 if group <= 5 else 8}>"}[variant]
 
 
 def load_traffic(workload: str, variant: str):
@@ -509,7 +513,7 @@ def run_ours(args) -> int:
         "hbm_gbs": kv_bytes_per_step(depth) / sec / 1e9,
         "frac_of_8TBs": kv_bytes_per_step(depth) / world / sec / 8e12,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": load_traffic(key, runner.cache.workspace.resolved), "kernel": KERNEL_NAMES[runner.cache.workspace.resolved], "peak_kind": peak_kind,
+                     "traffic": load_traffic(key, runner.cache.workspace.resolved), "kernel": kernel_name(runner.cache.workspace.resolved, runner.cache.per_token), "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": bytes_per_launch, "launch_us": ksec * 1e6},
         "e2e": {"value": e2e_sec * 1e6, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": runner.kernels_per_step() * steps,
