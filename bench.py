@@ -283,9 +283,9 @@ class StepRunner:
             self.gather()
 
     def kernels_per_step(self) -> int:
-        fused = self.cache.workspace.resolved == "umma2" and not self.cache.per_token
+        fused = self.cache.workspace.resolved in ("umma2", "mma") and not self.cache.per_token
         if self.peer is not None:                # (append, bump,) attention with fused gather, barrier
-            return 1 if fused else (3 if self.advance else 2) + 1
+            return (1 if self.cache.workspace.resolved == "umma2" else 2) if fused else (3 if self.advance else 2) + 1
         if fused:
             return 1                         # the fused step: append, attention, combine and position bump in one launch
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump
@@ -621,9 +621,9 @@ def run_cfg4(args) -> int:
             "config": {"workload": f"cfg4: {N_LAYERS}-layer batched decode, bs=16, ragged depths U[1024,16384] seed 0 "
                                    f"(sum {sum(depths_all)}), capacity {cap}, fused one-token append per sequence per step",
                        "sharding": f"by sequence x{world} (greedy longest-first on depth), no collective",
-                       "execution": "CUDA graph replay of " + ("one fused launch: append + attention + position bump" if cache.workspace.resolved == "umma2" else "append + attention + position bump")},
+                       "execution": "CUDA graph replay of " + ("one fused launch: append + attention + position bump" if cache.workspace.resolved in ("umma2", "mma") else "append + attention + position bump")},
             "hbm_gbs": total_bytes / sec / 1e9, "frac_of_8TBs": total_bytes / world / sec / 8e12,
-            "tokens_per_s": 16 / sec, "gpu_launches": (1 if cache.workspace.resolved == "umma2" else 3) * steps, "clocks": sampler.summary()}
+            "tokens_per_s": 16 / sec, "gpu_launches": (1 if cache.workspace.resolved in ("umma2", "mma") else 3) * steps, "clocks": sampler.summary()}
     if rank == 0:
         print(json.dumps(line), flush=True)
     finish(torch, dist, world)

@@ -238,8 +238,8 @@ int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* pee
 /*
  * The decode step of b200attn_append_decode with the gathered output of b200attn_decode_peers:
  * append this rank's new K/V rows, attend seq_pos[b]+1 tokens, store the results into every
- * rank's gathered buffer, advance seq_pos if advance_pos.  One launch with
- * B200ATTN_VARIANT_UMMA2, three otherwise.  With barrier_flags == NULL, follow it with
+ * rank's gathered buffer, advance seq_pos if advance_pos.  One launch with the stream-K
+ * kernels, three otherwise.  With barrier_flags == NULL, follow it with
  * b200attn_peer_barrier as for b200attn_decode_peers.  With barrier_flags (the flag buffers
  * b200attn_peer_barrier takes) the cross-GPU arrive-and-wait is part of the call: done by the
  * last CTA of the attention launch with B200ATTN_VARIANT_UMMA2, by the barrier kernel launched
@@ -325,10 +325,11 @@ int b200attn_qk_norm_rope_append(const B200AttnShape* shape,
 /*
  * Fused convenience for one decode step: A (append at seq_pos) then B+C attending
  * seq_pos[b]+1 tokens, then seq_pos[b] += 1 if advance_pos.  Same stream, no host sync.
- * With B200ATTN_VARIANT_UMMA2 (or AUTO resolving to it) the step is ONE launch: the CTA that
- * owns the tile holding a pair's new token quantises that row first, and the last CTA to
- * finish advances the positions; the other variants launch append, attention and the
- * position kernel one after the other.  Cache bytes, positions and status bits are the same
+ * With the stream-K kernels (B200ATTN_VARIANT_UMMA2, B200ATTN_VARIANT_MMA, i.e. whatever AUTO
+ * resolves to for per-head scales) the step is ONE launch: the CTA that owns the tile holding a
+ * pair's new token quantises that row first, and the last CTA to finish advances the
+ * positions; the other variants, and the per-token scale layout, launch append, attention and
+ * the position kernel one after the other.  Cache bytes, positions and status bits are the same
  * either way.
  */
 int b200attn_append_decode(const B200AttnShape* shape,

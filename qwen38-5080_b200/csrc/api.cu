@@ -182,7 +182,8 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
   DecodeArgs a{q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                num_splits, workspace, workspace_bytes, out, status, gate, 0, 0, 0, {}};
   if (fused) {
-    if (v != B200ATTN_VARIANT_UMMA2) return B200ATTN_ERR_VARIANT;
+    if (v != B200ATTN_VARIANT_UMMA2 && v != B200ATTN_VARIANT_MMA) return B200ATTN_ERR_VARIANT;
+    if (fused->barrier_flags && v != B200ATTN_VARIANT_UMMA2) return B200ATTN_ERR_VARIANT;
     a.k_new = fused->k_new;
     a.v_new = fused->v_new;
     a.seq_pos = fused->seq_pos;
@@ -279,14 +280,18 @@ static int step_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, c
     if (workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
   }
   if (!aligned16(q) || !aligned16(out) || !aligned16(workspace)) return B200ATTN_ERR_ALIGN;
-  if (v == B200ATTN_VARIANT_UMMA2 && g.scale_mode == B200ATTN_SCALE_PER_HEAD) {
+  if ((v == B200ATTN_VARIANT_UMMA2 || v == B200ATTN_VARIANT_MMA) && g.scale_mode == B200ATTN_SCALE_PER_HEAD) {
     // one launch: the attention kernel appends the new rows and advances the positions itself
-    // (per-token scales are computed by the append kernel: three launches below)
+    // (per-token scales are computed by the append kernel: three launches below); the in-launch
+    // cross-GPU barrier exists in the all-tcgen05 kernel only: the barrier kernel follows otherwise
     if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale) return B200ATTN_ERR_NULL;
     if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return B200ATTN_ERR_ALIGN;
-    const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr, barrier_flags};
-    return decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
-                       workspace, workspace_bytes, out, status, stream, &fused);
+    const bool barrier_inside = v == B200ATTN_VARIANT_UMMA2;
+    const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr, barrier_inside ? barrier_flags : nullptr};
+    rc = decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
+                     workspace, workspace_bytes, out, status, stream, &fused);
+    if (rc || barrier_inside || !barrier_flags) return rc;
+    return b200attn_peer_barrier(barrier_flags, peers->rank, peers->n_peers, status, stream);
   }
   if (peers && v == B200ATTN_VARIANT_SIMT) return B200ATTN_ERR_VARIANT;
   rc = b200attn_kv_quant_append_bulk(shape, 1, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 0,

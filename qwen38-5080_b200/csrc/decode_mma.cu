@@ -48,6 +48,45 @@ constexpr int kCtasPerSm = 3;                      // D = 128: the kernel is lat
                                                    // copy issue to one consumer's progress costs more than the spills.
 constexpr int kDumpBufs = 2;                       // dump buffers per CTA
 
+// Fused step: quantise the new token of every pair whose last tile (the tile that holds it) lies in the CTA's
+// range [r0, r1), exactly as the append kernel does; called by all 32 lanes of the
+// epilogue warp, which then releases the producer lane's wait in front of the first such tile.  Out of line: it runs
+// once per launch and must not cost the tile loop registers or instruction-cache room.
+template <int D>
+__device__ __noinline__ void append_rows_by_warp(int batch, int h_kv, int capacity, long long k_layer_stride,
+                                                 long long v_layer_stride, const uint16_t* k_new, const uint16_t* v_new,
+                                                 uint8_t* k_cache, uint8_t* v_cache, const float* k_scale, const float* v_scale,
+                                                 const int* seq_pos, int lane, long long r0, long long r1,
+                                                 const int* sCum, const int* sLen) {
+  Cursor a = locate(r0, sCum, sLen, batch, h_kv);
+  long long cur = r0;
+  while (cur < r1) {
+    const long long pair_end = cur - a.tile + a.tiles_b;
+    if (pair_end <= r1) {
+      const int pos = seq_pos[a.b];
+      if (pos >= 0 && pos < capacity) {
+        const long long rowi = ((long long)a.layer * batch + a.b) * h_kv + a.h;
+        for (int e = lane; e < D / 2; e += 32) {   // 4 values of the K row (e < D/4) or of the V row
+          const int which = e >= D / 4 ? 1 : 0, el = (e % (D / 4)) * 4;
+          const uint2 raw = *reinterpret_cast<const uint2*>((which ? v_new : k_new) + rowi * D + el);
+          const float sc = (which ? v_scale : k_scale)[a.layer * h_kv + a.h];
+          const uint32_t bytes = (uint32_t)quantize_e4m3(bf16_bits_to_float(raw.x & 0xFFFFu), sc) |
+                                 ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.x >> 16), sc) << 8) |
+                                 ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.y & 0xFFFFu), sc) << 16) |
+                                 ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.y >> 16), sc) << 24);
+          uint8_t* dst = (which ? v_cache : k_cache) + (long long)a.layer * (which ? v_layer_stride : k_layer_stride) +
+                         (((long long)a.b * h_kv + a.h) * capacity + pos) * D + el;
+          *reinterpret_cast<uint32_t*>(dst) = bytes;
+        }
+      }
+    }
+    cur = pair_end < r1 ? pair_end : r1;
+    if (cur < r1) next_pair(a, sCum, sLen, batch, h_kv);
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");   // the rows -> visible to the CTA's TMA loads
+  __syncwarp();
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads, D == 128 ? kCtasPerSm : 1)
 attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -74,13 +113,13 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   float* sDump = reinterpret_cast<float*>(sQ + 2 * q_bytes);                          // [2][4][G][DP]
   float* sML = sDump + kDumpBufs * kConsumerWarps * dump_warp_floats;                         // [2][4][16]: m[8], l[8]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sML + kDumpBufs * kConsumerWarps * 16);
-  int* sFlags = reinterpret_cast<int*>(bars + 2 * stages + 8);                        // [0] timed_out [2] any_empty [3] copies
+  int* sFlags = reinterpret_cast<int*>(bars + 2 * stages + 9);                        // [0] timed_out [2] any_empty [3] copies
   int* sLen = sFlags + 4;                                                             // [batch]
   int* sCum = sLen + g.batch;                                                         // [batch+1]
   volatile int* timed_out = sFlags;
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * stages;
   const uint32_t qfull0 = empty0 + 8u * stages, qempty0 = qfull0 + 16u;
-  const uint32_t dfull0 = qempty0 + 16u, dempty0 = dfull0 + 16u;
+  const uint32_t dfull0 = qempty0 + 16u, dempty0 = dfull0 + 16u, appended0 = dempty0 + 16u;
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -93,12 +132,14 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       mbar_init(dfull0 + 8u * i, kConsumerWarps);
       mbar_init(dempty0 + 8u * i, 1);
     }
+    mbar_init(appended0, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     sFlags[0] = 0; sFlags[1] = 0; sFlags[3] = 0;
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
       int len = p.seq_len[b] + p.seq_len_offset;
+      if (p.k_new && (len < 1 || len > g.capacity)) st |= B200ATTN_STATUS_POS_AT_CAPACITY;   // the new token has no slot
       if (len < 0) { len = 0; st |= B200ATTN_STATUS_LEN_NEGATIVE; }
       if (len > g.capacity) { len = g.capacity; st |= B200ATTN_STATUS_LEN_OVER_CAP; }
       sLen[b] = len;
@@ -141,6 +182,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   if (warp == kProducerWarp) {
     // ===================== producer warp: one elected lane issues the copies =====================
     if (lane == 0 && has_work) {
+      bool need_append = p.k_new != nullptr;   // fused step: the epilogue warp appends the new rows meanwhile
       Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
       int it = 0, seg = 0;
       bool seg_start = true;
@@ -155,6 +197,11 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
           seg_start = false;
         }
         const int s = it % stages;
+        if (need_append && c.tile == c.tiles_b - 1) {   // the tile that holds the new token: its row must be in the cache
+          if (!mbar_wait(appended0, 0, timed_out, p.status)) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          need_append = false;
+        }
         if (it >= stages && !mbar_wait(empty0 + 8u * s, ((it / stages) - 1) & 1, timed_out, p.status)) break;
         const uint32_t fb = full0 + 8u * s;
         mbar_arrive_expect_tx(fb, 2u * TILE_BYTES);
@@ -175,6 +222,13 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       sFlags[1] = seg;  // query copies issued
     }
   } else if (warp == kEpilogueWarp) {
+    if (p.k_new && has_work) {
+      // fused step: this warp is idle until the first segment ends; it appends the new rows of the pairs
+      // whose last tile this CTA loads while the producer is already streaming the tiles before them
+      append_rows_by_warp<D>(g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new, p.k_cache_w,
+                             p.v_cache_w, p.k_scale, p.v_scale, p.seq_len, lane, r0, r1, sCum, sLen);
+      if (lane == 0) mbar_arrive(appended0);
+    }
     if (has_work)
       epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
     TRACE_LANE0(7);
@@ -411,6 +465,18 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       while (!mbar_try_wait(qfull0 + 8u * qb, (last_seg >> 1) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
     }
   }
+  if (p.seq_pos && tid == 0) {
+    // Fused step: every CTA read the positions before it got here; the last one to arrive advances them.
+    int arrived;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.exit_count) : "memory");
+    if (arrived == (int)gridDim.x - 1) {
+      for (int b = 0; b < g.batch; ++b) {
+        const int pos = p.seq_pos[b];
+        if (pos >= 0 && pos + 1 <= g.capacity) p.seq_pos[b] = pos + 1;
+      }
+      *p.exit_count = 0;   // ready for the next launch
+    }
+  }
 }
 
 int stages_for(const Geometry& g) { return 3; }
@@ -421,7 +487,7 @@ size_t smem_bytes_for(const Geometry& g, int stages) {
   b += (size_t)2 * g.group * g.head_dim * 2;                  // query rows, double buffered
   b += (size_t)kDumpBufs * kConsumerWarps * g.group * (g.head_dim + 4) * 4;   // dumped warp states
   b += (size_t)kDumpBufs * kConsumerWarps * 16 * 4;                   // their m, l
-  b += (size_t)(2 * stages + 8) * 8;                          // barriers
+  b += (size_t)(2 * stages + 9) * 8;                          // barriers
   b += 16;                                                    // flags
   b += (size_t)(2 * g.batch + 1) * 4;                         // sLen, sCum
   return (b + 15) & ~(size_t)15;
@@ -471,6 +537,12 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
   p.status = a.status;
   p.stages = stages_for(g);
+  p.k_new = (const uint16_t*)a.k_new;
+  p.v_new = (const uint16_t*)a.v_new;
+  p.k_cache_w = (uint8_t*)a.k_cache;
+  p.v_cache_w = (uint8_t*)a.v_cache;
+  p.seq_pos = a.seq_pos;
+  p.exit_count = p.tickets + (size_t)g.n_layers * g.batch * g.h_kv;
   const size_t smem = smem_bytes_for(g, p.stages);
   auto launch = [&](auto kernel) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -428,9 +428,9 @@ def test_full_size_properties(pkg, oracle, cuda_device):
 
 
 def test_fused_step_equals_separate_launches(pkg, oracle, cuda_device):
-    """The all-tcgen05 variant does a decode step in ONE launch (new rows quantised by the CTA that
-    owns the pair's last tile, positions advanced by the last CTA to finish).  Against the
-    three-launch path of the mma variant: cache bytes and positions identical, outputs in tolerance;
+    """The stream-K kernels do a decode step in ONE launch (new rows quantised by the CTA that owns
+    the pair's last tile, positions advanced by the last CTA to finish).  Against the separate
+    append / attention / position launches of the SIMT variant: cache bytes and positions identical, outputs in tolerance;
     ragged lengths that cross a tile boundary, and a sequence already at capacity (flagged, neither
     written nor advanced)."""
     n_layers, batch, h_q, h_kv, d, cap, steps = 3, 4, 40, 8, 128, 256, 4
@@ -442,7 +442,7 @@ def test_fused_step_equals_separate_launches(pkg, oracle, cuda_device):
     kn = torch.randn(steps, n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
     vn = torch.randn(steps, n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
     caches = {}
-    for variant in ("mma", "umma2"):
+    for variant in ("simt", "mma", "umma2"):
         c = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant=variant)
         c.set_scales(pkg.calibrate_scales(k0, cap), pkg.calibrate_scales(v0, cap))
         # ragged prefill: every sequence gets its own prefix; garbage (0xFF = NaN) beyond it
@@ -459,19 +459,20 @@ def test_fused_step_equals_separate_launches(pkg, oracle, cuda_device):
     for i in range(steps):
         outs = {v: caches[v].step(qs[i], kn[i], vn[i], count=False).clone() for v in caches}
         torch.cuda.synchronize()
-        a, u = caches["mma"], caches["umma2"]
-        assert torch.equal(a.k_cache, u.k_cache) and torch.equal(a.v_cache, u.v_cache), f"step {i}: cache bytes differ"
-        assert a.seq_pos.cpu().tolist() == u.seq_pos.cpu().tolist(), f"step {i}"
+        a = caches["simt"]
         want_pos = [min(L + i + 1, cap) for L in lens]
-        assert u.seq_pos.cpu().tolist() == want_pos
         full_already = lens[3] + i >= cap
-        st_a, st_u = int(a.status.cpu().view(-1)[0]), int(u.status.cpu().view(-1)[0])
-        assert bool(st_u & pkg._lib.STATUS_POS_AT_CAPACITY) == full_already and bool(st_a & pkg._lib.STATUS_POS_AT_CAPACITY) == full_already
-        m = oracle.error_metrics(outs["umma2"].cpu(), outs["mma"].cpu())
-        assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, (i, m)
-        ref = oracle.decode_step_reference(qs[i].cpu(), u.k_cache.cpu(), u.v_cache.cpu(), u.k_scale.cpu(), u.v_scale.cpu(),
+        ref = oracle.decode_step_reference(qs[i].cpu(), a.k_cache.cpu(), a.v_cache.cpu(), a.k_scale.cpu(), a.v_scale.cpu(),
                                            want_pos, cap)
-        assert_parity(oracle, outs["umma2"].cpu(), ref, f"fused step {i}")
+        for fused in ("mma", "umma2"):
+            u = caches[fused]
+            assert torch.equal(a.k_cache, u.k_cache) and torch.equal(a.v_cache, u.v_cache), f"step {i} {fused}: cache bytes differ"
+            assert a.seq_pos.cpu().tolist() == u.seq_pos.cpu().tolist() == want_pos, f"step {i} {fused}"
+            st_a, st_u = int(a.status.cpu().view(-1)[0]), int(u.status.cpu().view(-1)[0])
+            assert bool(st_u & pkg._lib.STATUS_POS_AT_CAPACITY) == full_already and bool(st_a & pkg._lib.STATUS_POS_AT_CAPACITY) == full_already
+            m = oracle.error_metrics(outs[fused].cpu(), outs["simt"].cpu())
+            assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, (i, fused, m)
+            assert_parity(oracle, outs[fused].cpu(), ref, f"fused step {i} {fused}")
         for c in caches.values():
             c.workspace.status.zero_()
 
@@ -512,13 +513,13 @@ def test_random_shapes_against_the_oracle(pkg, oracle, cuda_device):
             assert status == 0, (what, variant)
             assert not torch.isnan(out.float()).any(), (what, variant)
             assert_parity(oracle, out, ref, f"{what} {variant} ctas {n_ctas}")
-        if group <= 5 and max(lens) < cap:
+        if max(lens) < cap:
             # one decode step, fused launch vs append + attention + position kernels
             g = torch.Generator().manual_seed(trial)
             kn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
             vn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
             res = {}
-            for variant in ("mma", "umma2"):
+            for variant in ("simt", "mma", "umma2"):
                 c = pkg.FP8StaticCache(n_layers, batch, h_kv * group, h_kv, d, cap, device=cuda_device, variant=variant)
                 c.set_scales(case["k_scale"].to(cuda_device), case["v_scale"].to(cuda_device))
                 c.k_cache.copy_(case["k_cache"])
@@ -527,11 +528,13 @@ def test_random_shapes_against_the_oracle(pkg, oracle, cuda_device):
                 out = c.step(case["q"].to(cuda_device), kn, vn, count=False)
                 torch.cuda.synchronize()
                 res[variant] = (out.cpu(), c.k_cache.cpu(), c.v_cache.cpu(), c.seq_pos.cpu(), int(c.status.cpu().view(-1)[0]))
-            a, u = res["mma"], res["umma2"]
-            assert a[4] == 0 and u[4] == 0, what
-            assert torch.equal(a[1], u[1]) and torch.equal(a[2], u[2]) and torch.equal(a[3], u[3]), what
-            m = oracle.error_metrics(u[0], a[0])
-            assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, (what, m)
+            a = res["simt"]
+            for fused in ("mma", "umma2"):
+                u = res[fused]
+                assert a[4] == 0 and u[4] == 0, (what, fused)
+                assert torch.equal(a[1], u[1]) and torch.equal(a[2], u[2]) and torch.equal(a[3], u[3]), (what, fused)
+                m = oracle.error_metrics(u[0], a[0])
+                assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, (what, fused, m)
 
 
 def test_peer_barrier_wait_is_bounded(pkg, cuda_device):
