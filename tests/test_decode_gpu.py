@@ -563,3 +563,47 @@ def test_peer_barrier_wait_is_bounded(pkg, cuda_device):
     torch.cuda.synchronize()
     assert status.item() == 0
     assert float((torch.ones(8, device=cuda_device) * 2).sum()) == 16.0
+
+
+def test_in_launch_barrier_wait_is_bounded(pkg, oracle, cuda_device):
+    """The arrive-and-wait inside the attention launch (tensor-parallel decode step, all-tcgen05
+    kernel): with a peer that never arrives — a second flag buffer that nobody writes — the last CTA
+    gives up after its 1 s budget, the status word says so, both gathered buffers hold this rank's
+    heads all the same, the cache and the positions are advanced, and the context stays usable."""
+    import ctypes
+    import time
+    n_layers, batch, h_q, h_kv, d, cap, lens = 2, 1, 20, 4, 128, 256, [130]
+    case = build_case(oracle, n_layers, batch, h_q, h_kv, d, lens, cap, seed=3)
+    dev = cuda_device
+    c = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=dev, variant="umma2")
+    c.set_scales(case["k_scale"].to(dev), case["v_scale"].to(dev))
+    c.k_cache.copy_(case["k_cache"])
+    c.v_cache.copy_(case["v_cache"])
+    c.seq_pos.copy_(torch.tensor(lens, dtype=torch.int32))
+    g = torch.Generator().manual_seed(4)
+    kn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(dev)
+    vn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(dev)
+    full = [torch.full((n_layers, batch, 2 * h_q, d), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    mine = torch.zeros(64, dtype=torch.int32, device=dev)
+    silent_peer = torch.zeros(64, dtype=torch.int32, device=dev)     # stands in for a rank that never arrives
+    peers = pkg._lib.B200AttnPeerOut(2, 0, 2 * h_q, 0, (ctypes.c_void_p * 8)(full[0].data_ptr(), full[1].data_ptr()))
+    flags = (ctypes.c_void_p * 8)(mine.data_ptr(), silent_peer.data_ptr())
+    q = case["q"].to(dev)
+    ws = c.workspace
+    t0 = time.perf_counter()
+    rc = pkg._lib.lib().b200attn_append_decode_peers(
+        ctypes.byref(c.shape), ctypes.byref(peers), q.data_ptr(), kn.data_ptr(), vn.data_ptr(), c.k_cache.data_ptr(),
+        c.v_cache.data_ptr(), c.k_scale.data_ptr(), c.v_scale.data_ptr(), c.seq_pos.data_ptr(), 1, d ** -0.5,
+        pkg._lib.VARIANTS["umma2"], ws.num_splits, ws.buf.data_ptr(), ws.nbytes, flags, ws.status.data_ptr(),
+        torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert rc == 0
+    assert ws.read_status() == pkg._lib.STATUS_WAIT_TIMEOUT
+    assert 0.5 < dt < 5.0, dt
+    assert silent_peer[0].item() == 1 and c.seq_pos.cpu().tolist() == [131]
+    ref = oracle.decode_step_reference(case["q"], c.k_cache.cpu(), c.v_cache.cpu(), case["k_scale"], case["v_scale"], [131], cap)
+    for buf in full:
+        assert_parity(oracle, buf[:, :, :h_q].cpu(), ref, "gathered buffer")
+        assert torch.isnan(buf[:, :, h_q:].float()).all()          # the other rank's heads: untouched
+    assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
