@@ -26,6 +26,8 @@ int resolve(const B200AttnShape* s, Geometry* g) {
   if (s->scale_mode != B200ATTN_SCALE_PER_HEAD && s->scale_mode != B200ATTN_SCALE_PER_TOKEN) return B200ATTN_ERR_SHAPE;
   if (s->reserved != 0) return B200ATTN_ERR_SHAPE;
   if ((long long)s->n_layers * s->batch > 65535) return B200ATTN_ERR_SHAPE;
+  // token rows of one layer are a 32-bit TMA coordinate
+  if ((long long)s->batch * s->h_kv * s->capacity > 0x7fffffffLL) return B200ATTN_ERR_SHAPE;
   const long long dense = (long long)s->batch * s->h_kv * s->capacity * s->head_dim;
   g->n_layers = s->n_layers; g->batch = s->batch; g->h_q = s->h_q; g->h_kv = s->h_kv;
   g->head_dim = s->head_dim; g->capacity = s->capacity; g->scale_mode = s->scale_mode; g->group = group;

@@ -1,33 +1,40 @@
-// Full tcgen05 variant of the stream-K decode attention: BOTH products run on the 5th-generation
+// All-tcgen05 variant of the stream-K decode attention: BOTH products run on the 5th-generation
 // tensor cores straight from the TMA-staged FP8 tiles; no K or V byte passes through a register.
 //
-// Same persistent stream-K skeleton, producer warp, epilogue warp and fused combine as the other
-// tensor-core kernels, 128-token tiles.  Per tile:
-//   1. issuer warp: S[128 tokens x 16] = K q^T with tcgen05.mma kind::f8f6f4 — the K tile's TMA
+// One persistent CTA per SM, 128-token tiles, twenty warps:
+//   1. producer warp: one lane streams K and V tiles with TMA into two shared-memory rings (and the
+//      query rows of each pair);
+//   2. S issuer warp: S[128 tokens x 16] = K q^T with tcgen05.mma kind::f8f6f4 — the K tile's TMA
 //      128-byte-swizzle layout is the K-major canonical operand layout; the query is the B operand
 //      as two e4m3 rows per head (leading part + remainder = the bf16 value exactly); scores land
-//      in tensor memory (two buffers);
-//   2. eight softmax warps in two groups of four; a group owns the tiles of one parity with its own
-//      score buffer, probability operand, running state and output accumulator, so two tiles are
-//      in flight per CTA.  One thread per token: tcgen05.ld of the token's scores, one group-wide
-//      reference maximum per head (redux.sync per warp + a shared-memory exchange), p =
-//      2^(s - m_ref).  The reference only moves when a tile's maximum exceeds it by more than
-//      kTau (lazy rescale: p stays <= 2^kTau), so the accumulator in tensor memory is rescaled
-//      (tcgen05.ld -> multiply -> tcgen05.st) only in the first tiles of a pair;
-//   3. the probabilities become the B operand of the second product: p * 2^13 is written as three
+//      in tensor memory (one buffer per softmax group);
+//   3. sixteen softmax warps in four groups of four; group = tile index mod 4, each with its own
+//      score buffer, probability operand, running state and output accumulators, so four tiles are
+//      in flight and tiles are consumed strictly in ring order.  One thread per token: tcgen05.ld of
+//      the token's scores, one group-wide reference maximum per head (redux.sync per warp + a
+//      shared-memory exchange), p = 2^(s - m_ref).  The reference only moves when a tile's maximum
+//      exceeds it by more than kTau (lazy rescale: p stays <= 2^kTau), so the accumulators in
+//      tensor memory are rescaled (tcgen05.ld -> multiply -> tcgen05.st) only in the first tiles
+//      of a pair;
+//   4. the probabilities become the B operand of the second product: p * 2^13 is written as three
 //      e5m2 terms (leading 3 significant bits, then the remainder twice: 9 significant bits, the
 //      precision class of the reference's bf16 P, with e5m2's range down to 2^-29 of the
-//      reference) into a 16-row x 128-token shared-memory operand (rows 3h..3h+2 for head h);
-//   4. issuer warp: O[128 dims x 16] += V^T P^T with tcgen05.mma, A = the V tile read MN-major
-//      (its swizzled [token][dim] layout is the MN-major canonical layout), accumulating in the
-//      group's tensor-memory accumulator over the whole pair; rows beyond the valid length are
-//      zeroed in shared memory first (their bytes may be NaN patterns);
-//   5. at the end of a pair each group reads its O once (one thread per dim), adds the three
-//      terms per head, and hands its state (m, l, acc) to the epilogue warp, which merges the two.
+//      reference) into a 128-token shared-memory operand (rows 3h..3h+2 for head h);
+//   5. P V issuer warp: O[128 dims x rows] += V^T P^T with tcgen05.mma, A = the V tile read
+//      MN-major (its swizzled [token][dim] layout is the MN-major canonical layout), accumulating
+//      in the group's tensor-memory accumulators over the whole segment; rows beyond the valid
+//      length are zeroed in shared memory first (their bytes may be NaN patterns);
+//   6. at the end of a segment each group reads its O once (one thread per dim), adds the terms
+//      per head, and hands its state (m, l, acc) to the epilogue warp, which merges the four
+//      states, writes the output or a split-K partial, and as the last owner of a pair to arrive
+//      merges the pair's partials.
+// The same launch can be the whole decode step: the new token's K/V rows are quantised into the
+// cache by the CTA that is going to load the tile that holds them, and the last CTA to finish
+// advances the positions (and, tensor-parallel, does the cross-GPU arrive-and-wait).
 // Query groups of up to 5 heads use 16 probability-operand rows (3 G <= 16), groups of 6 to 8 an instance
 // with 32 rows.
 //
-// All waits are bounded as in the other kernels; tensor memory is allocated by the issuer warp at
+// All waits are bounded as in the other kernels; tensor memory is allocated by the S issuer warp at
 // kernel start and always freed by it after the final barrier.
 #include "tcgen05.cuh"
 
