@@ -64,14 +64,12 @@ DTYPES = {"umma2": "fp8-e4m3 KV fed to tcgen05 as stored; query as two e4m3 term
                     "fp32 accumulate/softmax, bf16 in/out",
           "mma": "fp8-e4m3 KV, f16 tensor-core products, fp32 accumulate/softmax, bf16 in/out",
           "simt": "fp8-e4m3 KV, fp32 CUDA-core products, fp32 accumulate/softmax, bf16 in/out"}
-DTYPES["umma"] = DTYPES["mma"]
 
 
 def kernel_name(variant: str, per_token: bool = False) -> str:
     """Name of the dominant kernel as a profiler lists it, for the head shape of this run."""
     group = H_Q // H_KV
     return {"simt": f"attn_splitk_simt_kernel<{D},{group}>", "mma": f"attn_streamk_mma_kernel<{D}>",
-            "umma": f"attn_streamk_umma_kernel<{D}>",
             "umma2": f"attn_streamk_umma2_kernel<{D}, {'true' if per_token else 'false'}, {5 if group <= 5 else 8}>"}[variant]
 
 
@@ -638,7 +636,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cfg4"], default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
-    ap.add_argument("--variant", choices=["auto", "mma", "umma", "umma2", "simt"], default="auto", help="attention kernel variant")
+    ap.add_argument("--variant", choices=["auto", "mma", "umma2", "simt"], default="auto", help="attention kernel variant")
     ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
                     help="N > 1: fused peer-store all-gather (default) or NCCL all-gather + reorder copy")
     ap.add_argument("--scales", choices=["per_head", "per_token"], default="per_head",

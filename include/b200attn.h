@@ -50,8 +50,7 @@ extern "C" {
 #define B200ATTN_VARIANT_AUTO     0   /* the library's default (the fastest validated variant) */
 #define B200ATTN_VARIANT_SIMT     1   /* CUDA-core split-K partial kernel + separate combine kernel */
 #define B200ATTN_VARIANT_MMA      2   /* TMA/mbarrier staged, tensor-core (mma.sync f16) stream-K kernel with fused combine */
-#define B200ATTN_VARIANT_UMMA     3   /* the same stream-K kernel with S = K q^T on tcgen05.mma kind::f8f6f4: K tiles feed the
-                                         tensor cores from shared memory unconverted, scores in tensor memory */
+/* 3 is retired (an intermediate kernel with only the score product on tcgen05): B200ATTN_ERR_VARIANT */
 #define B200ATTN_VARIANT_UMMA2    4   /* both products on tcgen05.mma: S = K q^T and O += V^T P^T read the staged FP8 tiles
                                          directly (V as an MN-major operand), scores and the output accumulator live in
                                          tensor memory; both scale layouts */
@@ -73,7 +72,7 @@ extern "C" {
  * Tensor-parallel sharding by KV head is expressed by passing the local h_kv / h_q.
  */
 typedef struct B200AttnShape {
-  int n_layers;      /* 64 (BASELINE), 16 (reference model), or 1 for the per-layer drop-in */
+  int n_layers;      /* 64 (the benchmark), 16 (the reference model), or 1 for the per-layer drop-in */
   int batch;         /* sequences, >= 1 */
   int h_q;           /* query heads (40 | 24); must be a multiple of h_kv, group size <= 8 */
   int h_kv;          /* KV heads (8 | 4) */
@@ -103,6 +102,10 @@ typedef struct B200AttnPeerOut {
 
 /* Library version (B200ATTN_VERSION of the build). */
 int b200attn_version(void);
+
+/* Hash of the sources the library was compiled from ("" for a build that did not record one); a
+ * loader compares it with the sources beside the library to refuse a stale binary. */
+const char* b200attn_source_hash(void);
 
 /* Text for a host-side error code. */
 const char* b200attn_error_string(int code);
@@ -360,7 +363,7 @@ int b200attn_dequant_prefix(const B200AttnShape* shape, int n_tokens,
  * Per-(layer, kv_head) scale calibration over a bf16 prefix on the device:
  *     scale[l][h] = max_{b,t<n_tokens,d} |x| / 448
  *   x : bf16 [n_layers][batch][h_kv][n_tokens][head_dim]
- * (BASELINE config: "quantised to FP8-e4m3 with a per-(layer, kv-head) fp32 absmax/448 scale").
+ * (the benchmark's cache is "quantised to FP8-e4m3 with a per-(layer, kv-head) fp32 absmax/448 scale").
  */
 int b200attn_calibrate_scales(const B200AttnShape* shape, int n_tokens,
                               const void* x_bf16, float* scale, void* stream);

@@ -64,9 +64,11 @@ float oracle_e4m3_to_f32(uint8_t b) {
   return (b & 0x80) ? -v : v;
 }
 
-/* q = clamp(float(x)/s, -448, 448) -> e4m3; NaN stays NaN (torch.clamp propagates NaN). */
+/* q = clamp(float(x)/s, -448, 448) -> e4m3; NaN stays NaN (torch.clamp propagates NaN); a zero
+ * scale (an all-zero row or head) gives zero bytes. */
 void oracle_quantize(const uint16_t* x_bf16, float scale, uint8_t* out, long n) {
   for (long i = 0; i < n; ++i) {
+    if (scale == 0.0f) { out[i] = 0; continue; }
     float y = bf16_to_f32(x_bf16[i]) / scale;
     if (y == y) y = y < -448.0f ? -448.0f : (y > 448.0f ? 448.0f : y);
     out[i] = oracle_f32_to_e4m3(y);

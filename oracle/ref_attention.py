@@ -97,8 +97,10 @@ def pad_and_mask(k, v, capacity: int, fill: float = 0.0):
 # FP8 e4m3 (docs/journal/2026-10-23-phase2-r3-coordinator.md:43-49)
 # --------------------------------------------------------------------------------------
 def head_scales(x: torch.Tensor) -> torch.Tensor:
-    """Per-(kv head) scale of x [B,H_kv,L,D] bf16: amax|x| / 448 in fp32 -> [H_kv]."""
-    return x.float().abs().amax(dim=(0, 2, 3)) / E4M3_MAX
+    """Per-(kv head) scale of x [B,H_kv,L,D] bf16: amax|x| / 448 in fp32 -> [H_kv].  A head that is
+    zero everywhere gets scale 1 (the formula's 0 would turn every later x/s into NaN or +-448)."""
+    s = x.float().abs().amax(dim=(0, 2, 3)) / E4M3_MAX
+    return torch.where(s == 0, torch.ones_like(s), s)
 
 
 def token_scales(x: torch.Tensor) -> torch.Tensor:
@@ -108,9 +110,13 @@ def token_scales(x: torch.Tensor) -> torch.Tensor:
 
 
 def quantize_e4m3(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
-    """clamp(x/s, -448, 448).to(e4m3fn) -> uint8 bytes.  `scale` broadcasts against x."""
-    y = (x.float() / scale).clamp(-E4M3_MAX, E4M3_MAX)
-    return y.to(torch.float8_e4m3fn).view(torch.uint8)
+    """clamp(x/s, -448, 448).to(e4m3fn) -> uint8 bytes.  `scale` broadcasts against x.  A zero scale
+    (an all-zero row or head; the formula's 0/0 has no frozen meaning) gives zero bytes."""
+    scale = torch.as_tensor(scale, dtype=torch.float32)
+    zero = scale == 0
+    y = (x.float() / torch.where(zero, torch.ones_like(scale), scale)).clamp(-E4M3_MAX, E4M3_MAX)
+    q = y.to(torch.float8_e4m3fn).view(torch.uint8)
+    return torch.where(zero.expand_as(q), torch.zeros_like(q), q)
 
 
 def quantize_per_head(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -121,9 +127,7 @@ def quantize_per_head(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
 def quantize_per_token(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """x [B,H_kv,L,D] bf16, scale [B,L,H_kv] -> uint8 [B,H_kv,L,D].  An all-zero head row
     has scale 0; its bytes are defined as 0 (the formula's 0/0 has no frozen meaning)."""
-    s = scale.permute(0, 2, 1).unsqueeze(-1)
-    q = quantize_e4m3(x, torch.where(s == 0, torch.ones_like(s), s))
-    return torch.where(s == 0, torch.zeros_like(q), q)
+    return quantize_e4m3(x, scale.permute(0, 2, 1).unsqueeze(-1))
 
 
 def dequantize(bytes_u8: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:

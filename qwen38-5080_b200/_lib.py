@@ -10,7 +10,7 @@ import os
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
-LIB_PATH = Path(os.environ.get("B200ATTN_LIB") or PKG_DIR / "libb200attn.so")   # override: an alternative build
+LIB_PATH = PKG_DIR / "libb200attn.so"
 
 c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_longlong
 
@@ -18,8 +18,8 @@ c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes
 OK = 0
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_SPLITS, ERR_CUDA, ERR_CAPACITY, ERR_VARIANT, ERR_TOO_LARGE = range(-1, -10, -1)
 STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEGATIVE = 1, 2, 4, 8
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA, VARIANT_UMMA2 = 0, 1, 2, 3, 4
-VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma": VARIANT_UMMA, "umma2": VARIANT_UMMA2}
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA2 = 0, 1, 2, 4
+VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma2": VARIANT_UMMA2}
 SCALE_PER_HEAD, SCALE_PER_TOKEN = 0, 1
 
 
@@ -39,6 +39,7 @@ class B200AttnPeerOut(ctypes.Structure):
 # name -> (restype, argtypes); every symbol include/b200attn.h declares
 PROTOTYPES = {
     "b200attn_version": (c_int, []),
+    "b200attn_source_hash": (ctypes.c_char_p, []),
     "b200attn_error_string": (ctypes.c_char_p, [c_int]),
     "b200attn_last_cuda_error": (c_int, []),
     "b200attn_pick_splits": (c_int, [ctypes.POINTER(B200AttnShape), c_int, c_int, c_int]),
@@ -91,19 +92,25 @@ class B200AttnError(ValueError):
 
 
 def lib() -> ctypes.CDLL:
-    """Load (building first if the shared object is absent and nvcc exists)."""
+    """Load the library, building it first when it is absent or was compiled from other sources than
+    the ones beside it (the hash the build baked in is compared with the sources' hash)."""
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists() or os.environ.get("B200ATTN_REBUILD") == "1":
-        from . import build as _build  # raises if nvcc is missing: no fallback
-        _build.build()
+    from . import build as _build
+    want = _build.source_hash()
+    if _build.needs_build() or os.environ.get("B200ATTN_REBUILD") == "1":
+        _build.build(force=os.environ.get("B200ATTN_REBUILD") == "1")   # raises if nvcc is missing: no fallback
     if not LIB_PATH.exists():
         raise RuntimeError(f"{LIB_PATH} is missing: build it with `python {PKG_DIR / 'build.py'}`")
     handle = ctypes.CDLL(str(LIB_PATH))
     for name, (res, args) in PROTOTYPES.items():
         fn = getattr(handle, name)  # AttributeError if the build lost a symbol
         fn.restype, fn.argtypes = res, args
+    have = handle.b200attn_source_hash().decode()
+    if have != want:
+        raise RuntimeError(f"{LIB_PATH} was built from other sources (library {have}, sources {want}): rebuild it with "
+                           f"`python {PKG_DIR / 'build.py'}`")
     _lib = handle
     return _lib
 

@@ -4,6 +4,8 @@
 """
 from __future__ import annotations
 
+import fcntl
+import hashlib
 import os
 import shutil
 import subprocess
@@ -13,7 +15,8 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libb200attn.so"
-SOURCES = ["api.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_umma.cu", "decode_umma2.cu", "static_scratch.cu", "peer_barrier.cu", "producer.cu"]
+STAMP_PATH = PKG_DIR / "libb200attn.so.hash"
+SOURCES = ["api.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_umma2.cu", "static_scratch.cu", "peer_barrier.cu", "producer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
@@ -33,26 +36,49 @@ def sources() -> list[Path]:
     return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
 
 
+def source_hash() -> str:
+    """Hash of everything the library is compiled from; the build bakes it into the library
+    (b200attn_source_hash) so that a loader can tell a stale binary from a current one."""
+    h = hashlib.sha256()
+    deps = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "b200attn.h"]
+    for d in deps:
+        h.update(d.name.encode())
+        h.update(d.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def built_hash() -> str | None:
+    """The source hash recorded beside the library by the build that made it."""
+    return STAMP_PATH.read_text().strip() if STAMP_PATH.exists() and LIB_PATH.exists() else None
+
+
 def needs_build() -> bool:
-    if not LIB_PATH.exists():
-        return True
-    t = LIB_PATH.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "b200attn.h"]
-    return any(d.stat().st_mtime > t for d in deps)
+    return built_hash() != source_hash()
 
 
 def build(verbose: bool = False, force: bool = False) -> Path:
-    """Compile every .cu of csrc/ into libb200attn.so.  Returns the library path."""
+    """Compile every .cu of csrc/ into libb200attn.so.  Returns the library path.  Concurrent callers
+    (the ranks of a multi-process run) are serialised by a file lock; the later ones find the
+    library up to date."""
     if not force and not needs_build():
         return LIB_PATH
+    with open(PKG_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not needs_build():
+            return LIB_PATH
+        return _build_locked(verbose)
+
+
+def _build_locked(verbose: bool) -> Path:
     nvcc = find_nvcc()
+    digest = source_hash()
     objs = []
     build_dir = PKG_DIR / "build"
     build_dir.mkdir(exist_ok=True)
     procs = []
     for src in sources():
         obj = build_dir / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, f'-DB200ATTN_SOURCE_HASH="{digest}"', "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd += ["-Xptxas", "-v"]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -70,6 +96,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         sys.stderr.write(res.stdout)
         raise RuntimeError("link of libb200attn.so failed")
     os.replace(tmp, LIB_PATH)
+    STAMP_PATH.write_text(digest + "\n")
     return LIB_PATH
 
 

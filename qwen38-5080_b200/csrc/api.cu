@@ -1,5 +1,7 @@
 // C-ABI layer of libb200attn: argument validation on the host, then kernel launches on the
 // caller's stream.  Nothing here allocates, synchronises or reads device memory.
+#include <atomic>
+
 #include "common.cuh"
 
 using namespace b200attn;
@@ -8,9 +10,19 @@ namespace {
 
 thread_local int g_last_cuda_error = 0;
 
-int cuda_fail(cudaError_t e) {
-  g_last_cuda_error = (int)e;
-  return B200ATTN_ERR_CUDA;
+int cuda_fail(cudaError_t e) { return b200attn::record_cuda_error(e); }
+
+// SMs of the current device (cached per device); 148, a B200, when no device can be asked (the
+// pure host helpers also run where there is no GPU).
+int device_sms() {
+  static std::atomic<int> cache[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return 148; }
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) { (void)cudaGetLastError(); return 148; }
+  cache[dev].store(n, std::memory_order_relaxed);
+  return n;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -38,41 +50,51 @@ int resolve(const B200AttnShape* s, Geometry* g) {
   return B200ATTN_OK;
 }
 
-// AUTO = a tensor-core stream-K kernel wherever one applies (per-head scales); the per-token
-// scale layout is served by the SIMT kernel.  Between the tensor-core kernels: the all-tcgen05
-// kernel (one CTA per SM, 128-token tiles, ~19 us of fixed cost per launch) for long caches; the
-// mma.sync kernel (three CTAs per SM, 64-token tiles, finer split) for short ones, where it
-// measured faster (depth 512: 22 vs 25 us).  The
-// lengths live on the device, so the cache capacity stands in for them: at least 2048 token slots
-// and at least 24 tiles per CTA at capacity.  The all-tcgen05 kernel also takes the per-token scale
-// layout (each softmax thread owns one token and applies its two scales); the mma.sync kernels do not.
+// AUTO = a tensor-core stream-K kernel wherever one applies.  The all-tcgen05 kernel (one CTA per SM,
+// 128-token tiles, ~19 us of fixed cost per launch) takes long caches and both scale layouts (each
+// softmax thread owns one token and applies its two scales); the mma.sync kernel (three CTAs per SM,
+// 64-token tiles, finer split, per-head scales only) takes short caches, where it measured faster
+// (depth 512: 22 vs 25 us).  The lengths live on the device, so the cache capacity stands in for
+// them: the all-tcgen05 kernel from 2048 token slots and 24 tiles per SM at capacity.  What is left
+// (short caches with per-token scales, batches beyond 2048) goes to the CUDA-core kernel.
 // An explicit request that cannot be met is an error.
 int resolve_variant(int variant, const Geometry& g) {
   const bool mma_ok = g.scale_mode == B200ATTN_SCALE_PER_HEAD && g.batch <= 2048;
   const bool umma2_ok = g.batch <= 2048 && umma2_supported(g);
   if (variant == B200ATTN_VARIANT_AUTO && umma2_ok && g.capacity >= 2048) {
     const long long tiles = (long long)g.n_layers * g.batch * g.h_kv * ((g.capacity + 127) / 128);
-    if (tiles >= 24LL * 148) return B200ATTN_VARIANT_UMMA2;
+    if (tiles >= 24LL * device_sms()) return B200ATTN_VARIANT_UMMA2;
   }
   if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
   if (variant == B200ATTN_VARIANT_SIMT) return variant;
-  if (variant == B200ATTN_VARIANT_MMA || variant == B200ATTN_VARIANT_UMMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
+  if (variant == B200ATTN_VARIANT_MMA) return mma_ok ? variant : B200ATTN_ERR_SHAPE;
   if (variant == B200ATTN_VARIANT_UMMA2) return umma2_ok ? variant : B200ATTN_ERR_SHAPE;
   return B200ATTN_ERR_VARIANT;
 }
 
 int pick(const Geometry& g, int v, int max_seq_len, int num_sms) {
   if (v == B200ATTN_VARIANT_SIMT) return simt_pick_splits(g, max_seq_len, num_sms);
-  if (v == B200ATTN_VARIANT_UMMA) return umma_pick_ctas(g, max_seq_len, num_sms);
   if (v == B200ATTN_VARIANT_UMMA2) return umma2_pick_ctas(g, max_seq_len, num_sms);
   return mma_pick_ctas(g, max_seq_len, num_sms);
 }
 
 }  // namespace
 
+namespace b200attn {
+int record_cuda_error(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return B200ATTN_ERR_CUDA;
+}
+}  // namespace b200attn
+
 extern "C" {
 
 int b200attn_version(void) { return B200ATTN_VERSION; }
+
+#ifndef B200ATTN_SOURCE_HASH
+#define B200ATTN_SOURCE_HASH ""
+#endif
+const char* b200attn_source_hash(void) { return B200ATTN_SOURCE_HASH; }
 
 const char* b200attn_error_string(int code) {
   switch (code) {
@@ -97,7 +119,7 @@ int b200attn_pick_splits(const B200AttnShape* shape, int max_seq_len, int num_sm
   int rc = resolve(shape, &g);
   if (rc) return rc;
   if (max_seq_len < 0) return B200ATTN_ERR_CAPACITY;
-  if (num_sms < 1) num_sms = 148;
+  if (num_sms < 1) num_sms = device_sms();
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
   return pick(g, v, max_seq_len, num_sms);
@@ -159,21 +181,41 @@ struct FusedStep {
   void* const* barrier_flags; // null = no cross-GPU barrier at the end of the launch
 };
 
+}  // extern "C"
+
+// The argument checks of b200attn_decode that need no workspace yet: shape, pointers, alignment, kernel
+// choice and split count.  Fills in the geometry, the resolved kernel, the split count (0 = the
+// default) and the workspace bytes that choice needs.  Shared with the entry point that brings its
+// own scratch, which must know all of this before it touches that scratch.
+int b200attn::decode_precheck(const B200AttnShape* shape, const void* q, const void* k_cache, const void* v_cache,
+                              const float* k_scale, const float* v_scale, const int* seq_len, const void* out,
+                              bool has_peers, const int* status, int variant, int* num_splits, Geometry* g,
+                              int* resolved, size_t* need) {
+  int rc = resolve(shape, g);
+  if (rc) return rc;
+  if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !seq_len || (!out && !has_peers) || !status) return B200ATTN_ERR_NULL;
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out)) return B200ATTN_ERR_ALIGN;
+  const int v = resolve_variant(variant, *g);
+  if (v < 0) return v;
+  if (*num_splits == 0) *num_splits = pick(*g, v, g->capacity, device_sms());
+  if (*num_splits < 1 || *num_splits > 65535) return B200ATTN_ERR_SPLITS;
+  *resolved = v;
+  *need = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(*g, *num_splits) : mma_workspace_bytes(*g, *num_splits);
+  return B200ATTN_OK;
+}
+
+extern "C" {
+
 static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, const void* q, const void* gate, const void* k_cache,
                        const void* v_cache, const float* k_scale, const float* v_scale, const int* seq_len,
                        int seq_len_offset, float softmax_scale, int variant, int num_splits, void* workspace,
                        size_t workspace_bytes, void* out, int* status, void* stream, const FusedStep* fused = nullptr) {
   Geometry g;
-  int rc = resolve(shape, &g);
+  int v = 0;
+  size_t need = 0;
+  int rc = decode_precheck(shape, q, k_cache, v_cache, k_scale, v_scale, seq_len, out, peers != nullptr, status, variant,
+                           &num_splits, &g, &v, &need);
   if (rc) return rc;
-  if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !seq_len || (!out && !peers) || !status) return B200ATTN_ERR_NULL;
-  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out)) return B200ATTN_ERR_ALIGN;
-  const int v = resolve_variant(variant, g);
-  if (v < 0) return v;
-  if (num_splits == 0)
-    num_splits = pick(g, v, g.capacity, 148);
-  if (num_splits < 1 || num_splits > 65535) return B200ATTN_ERR_SPLITS;
-  const size_t need = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(g, num_splits) : mma_workspace_bytes(g, num_splits);
   const bool needs_ws = !(v == B200ATTN_VARIANT_SIMT && num_splits == 1);
   if (needs_ws) {
     if (!workspace) return B200ATTN_ERR_NULL;
@@ -213,7 +255,6 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
     }
   }
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
-                                             : v == B200ATTN_VARIANT_UMMA ? launch_decode_umma(g, a, (cudaStream_t)stream)
                                              : v == B200ATTN_VARIANT_UMMA2 ? launch_decode_umma2(g, a, (cudaStream_t)stream)
                                              : launch_decode_mma(g, a, (cudaStream_t)stream);
   return e == cudaSuccess ? B200ATTN_OK : cuda_fail(e);
@@ -274,7 +315,7 @@ static int step_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, c
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
   if (num_splits == 0)
-    num_splits = pick(g, v, g.capacity, 148);
+    num_splits = pick(g, v, g.capacity, device_sms());
   if (num_splits < 1 || num_splits > 65535) return B200ATTN_ERR_SPLITS;
   const size_t need = v == B200ATTN_VARIANT_SIMT ? simt_workspace_bytes(g, num_splits) : mma_workspace_bytes(g, num_splits);
   if (!(v == B200ATTN_VARIANT_SIMT && num_splits == 1)) {

@@ -71,15 +71,11 @@ append_kernel(Geometry g, int n_tokens, const uint4* __restrict__ k_new, const u
   }
   if (!active || !fits) return;
 
-  uint32_t lo = 0, hi = 0;
-  if (g.scale_mode == B200ATTN_SCALE_PER_TOKEN && s == 0.f) {
-    // all-zero row: bytes are defined as 0
-  } else {
+  uint32_t lo = 0, hi = 0;   // a zero scale (all-zero row or head) gives zero bytes: quantize_e4m3
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      lo |= (uint32_t)quantize_e4m3(x[i], s) << (8 * i);
-      hi |= (uint32_t)quantize_e4m3(x[4 + i], s) << (8 * i);
-    }
+  for (int i = 0; i < 4; ++i) {
+    lo |= (uint32_t)quantize_e4m3(x[i], s) << (8 * i);
+    hi |= (uint32_t)quantize_e4m3(x[4 + i], s) << (8 * i);
   }
   uint8_t* cache = which ? v_cache : k_cache;
   const long long lstride = which ? g.v_layer_stride : g.k_layer_stride;
@@ -131,7 +127,8 @@ dequant_prefix_kernel(Geometry g, int n_tokens, const uint8_t* __restrict__ cach
   out[(row * TPR + c) * 2 + 1] = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-// scale[layer][h] = amax over (batch, token, dim) / 448.  One CTA per (h, layer).
+// scale[layer][h] = amax over (batch, token, dim) / 448, and 1 for a head that is zero everywhere (a
+// zero scale would make every later append of that head meaningless).  One CTA per (h, layer).
 __global__ void __launch_bounds__(256)
 calibrate_kernel(Geometry g, int n_tokens, const uint4* __restrict__ x, float* __restrict__ scale) {
   const int h = blockIdx.x, layer = blockIdx.y;
@@ -156,7 +153,7 @@ calibrate_kernel(Geometry g, int n_tokens, const uint4* __restrict__ x, float* _
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
-    scale[layer * g.h_kv + h] = __fdiv_rn(amax, kE4m3Max);
+    scale[layer * g.h_kv + h] = amax == 0.f ? 1.f : __fdiv_rn(amax, kE4m3Max);
   }
 }
 

@@ -13,7 +13,7 @@ namespace b200attn {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kE4m3Max = 448.0f;
-constexpr int kMaxGroup = 8;  // query heads per KV head the kernels support (BASELINE 5, reference 6)
+constexpr int kMaxGroup = 8;  // query heads per KV head the kernels support (benchmark shape 40/8: 5, reference model 24/4: 6)
 
 // Resolved geometry handed to the launchers (strides in bytes, always filled in).
 struct Geometry {
@@ -51,8 +51,10 @@ __device__ __forceinline__ void e4m3x16_to_float(const uint4& raw, float* out) {
 // clamp(x / s, -448, 448) -> e4m3fn byte, round to nearest even.  IEEE division.  A NaN input
 // keeps its sign and becomes 0x7F / 0xFF, as a float32 -> float8_e4m3fn cast of a clamped NaN
 // does on the host (GPU arithmetic would canonicalise the sign away, so it is taken from x);
-// a NaN produced by the division itself (0/0, inf/inf) becomes 0x7F.
+// a NaN produced by the division itself (inf/inf) becomes 0x7F.  A zero scale (an all-zero row or
+// head: the formula's 0/0 has no frozen meaning) gives the zero byte, in both scale layouts.
 __device__ __forceinline__ uint8_t quantize_e4m3(float x, float s) {
+  if (s == 0.f) return 0;
   if (x != x) return (uint8_t)(0x7F | ((__float_as_uint(x) >> 31) << 7));
   float y = __fdiv_rn(x, s);
   if (y != y) return (uint8_t)0x7F;
@@ -63,6 +65,14 @@ __device__ __forceinline__ uint8_t quantize_e4m3(float x, float s) {
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
   return __uint_as_float(bits16 << 16);
 }
+
+// Remember a failed CUDA call for b200attn_last_cuda_error() on this thread; returns B200ATTN_ERR_CUDA.
+int record_cuda_error(cudaError_t e);
+
+// Host-side argument checks of b200attn_decode short of the workspace (api.cu).
+int decode_precheck(const B200AttnShape* shape, const void* q, const void* k_cache, const void* v_cache,
+                    const float* k_scale, const float* v_scale, const int* seq_len, const void* out, bool has_peers,
+                    const int* status, int variant, int* num_splits, Geometry* g, int* resolved, size_t* need);
 
 // ---- launchers (defined in the .cu files; called by the C-ABI layer in api.cu) ------------
 
@@ -126,9 +136,7 @@ size_t mma_workspace_bytes(const Geometry& g, int num_ctas);
 int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
 cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
 
-// UMMA variant: the same stream-K kernel with the score GEMM on tcgen05.mma (FP8 bytes from shared memory).
-int umma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
-cudaError_t launch_decode_umma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);
+// All-tcgen05 variant: both products on tcgen05.mma straight from the staged FP8 tiles.
 bool umma2_supported(const Geometry& g);
 int umma2_pick_ctas(const Geometry& g, int max_seq_len, int num_sms);
 cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStream_t stream);

@@ -103,7 +103,6 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   const uint32_t q_bytes = (uint32_t)G * D * 2;
   const int dump_warp_floats = G * DP;
 
-  TRACE(0);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -177,7 +176,6 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   long long r0, r1;
   cta_range(total, (int)gridDim.x, (int)blockIdx.x, (sFlags[2] & 2) ? sCum[1] - sCum[0] : 0, n_eff, r0, r1);
   const bool has_work = r0 < r1;
-  TRACE(1);
 
   if (warp == kProducerWarp) {
     // ===================== producer warp: one elected lane issues the copies =====================
@@ -231,7 +229,6 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     }
     if (has_work)
       epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
-    TRACE_LANE0(7);
   } else if (has_work) {
     // ================================ consumer warps ================================
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
@@ -314,15 +311,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       for (int ti = 0; ti < ntiles; ++ti, ++it) {
         const int s = it % stages;
         const bool ok = mbar_wait(full0 + 8u * s, (it / stages) & 1, timed_out, p.status);
-#ifdef B200ATTN_TRACE
-        if (it == 0) TRACE(2);
-#endif
         const int tok0 = (c.tile + ti) * kTileT + warp * 16;   // first token of this warp's 16
-#ifdef B200ATTN_NOCOMPUTE
-        if (false) {
-#else
         if (ok && tok0 < c.len_b) {
-#endif
           // ---------------- S^T[16 tokens x 8 heads] = K q^T ----------------
           float sacc[4] = {0.f, 0.f, 0.f, 0.f}, sacc2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains
           const uint32_t kt = sK_addr + s * TILE_BYTES;
@@ -405,10 +395,6 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8u * s);
       }
-#ifdef B200ATTN_TRACE
-      if (cur == r0) TRACE(3);
-      if (seg_end == r1) TRACE(5);
-#endif
 
       // ---------------- end of segment: hand the warp's state to the epilogue warp ----------------
 #pragma unroll
@@ -436,19 +422,12 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(dfull0 + 8u * db);
-#ifdef B200ATTN_TRACE
-      if (cur == r0) TRACE(4);
-#endif
       ++seg;
       cur = seg_end;
       if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
     }
   }
   __syncthreads();
-  TRACE(6);
-#ifdef B200ATTN_TRACE
-  if (tid == 0) { unsigned smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid)); g_trace[blockIdx.x * 8 + 4] = smid; }
-#endif
   if (sFlags[0] && tid == kConsumerThreads) {
     // A wait gave up.  Copies already issued still land in this CTA's shared memory: wait for
     // them (bounded) so the CTA does not retire underneath them.
@@ -556,12 +535,3 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
 }  // namespace b200attn
 
 
-#ifdef B200ATTN_TRACE
-extern "C" int b200attn_debug_trace(unsigned long long* host_out, int n_ctas, int clear) {
-  if (clear) {
-    static unsigned long long zeros[4096 * 8];
-    return (int)cudaMemcpyToSymbol(b200attn::g_trace, zeros, sizeof(zeros));
-  }
-  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_trace, (size_t)n_ctas * 8 * sizeof(unsigned long long));
-}
-#endif

@@ -90,17 +90,6 @@ __device__ __forceinline__ void bar_group(int grp) {
   }
 }
 
-#ifdef B200ATTN_TRACE
-// Development-only time stamps (%globaltimer): per CTA eight stamps of the latest launch (entry, prologue
-// done, first K copy issued / landed, first tile through the softmax, last K copy issued, softmax group 0
-// done, exit); per launch (in issue order, modulo 64) the earliest CTA entry and the latest CTA exit.
-static __device__ unsigned long long g_trace2[4096 * 8];
-static __device__ unsigned long long g_launch_span[64 * 2];
-static __device__ unsigned int g_entry_ctr;
-#define TSTAMP(slot) g_trace2[blockIdx.x * 8 + (slot)] = global_timer_ns()
-#else
-#define TSTAMP(slot) do { } while (0)
-#endif
 
 // Shared-memory plan, computed the same way on the host and in the kernel.
 struct Plan2 {
@@ -188,14 +177,6 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   const uint32_t q_bytes = (uint32_t)G * D * 2;
   constexpr bool per_token = PT;   // scales [n_layers][batch][capacity][h_kv]
 
-#ifdef B200ATTN_TRACE
-  __shared__ unsigned int s_launch;
-  if (tid == 0) {
-    TSTAMP(0);
-    s_launch = (atomicAdd(&g_entry_ctr, 1u) / gridDim.x) % 64u;
-    atomicMin(&g_launch_span[2 * s_launch], global_timer_ns());
-  }
-#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -265,7 +246,6 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)sFlags[1];
-  if (tid == 0) TSTAMP(1);
 
   if (sFlags[2] & 1) {   // sequences of length 0 have no tiles: their outputs are zero
     const long long rows = (long long)g.n_layers * g.batch;
@@ -321,10 +301,6 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           tma_load_3d_hint(smem_u32(sK) + ks * TILE_BYTES + hf * kTile2 * 128, &kmap, hf * 128, row, c.layer, kfull0 + 8u * ks, kv_policy);
         }
         ++kissued;
-#ifdef B200ATTN_TRACE
-        if (it == 0) TSTAMP(2);
-        if (it == total_it - 1) TSTAMP(5);
-#endif
         if (++ks == kstages) { ks = 0; ++kround; }
         if (vround && !mbar_wait_lean(vempty0 + 8u * vs, (vround - 1) & 1, timed_out, p.status)) break;
         mbar_arrive_expect_tx(vfull0 + 8u * vs, TILE_BYTES);
@@ -410,9 +386,6 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         }
         seg_start = false;
         if (alive) alive = mbar_wait_lean(kfull0 + 8u * ks, kround & 1, timed_out, p.status);
-#ifdef B200ATTN_TRACE
-        if (it == 0 && lane == 0) TSTAMP(3);
-#endif
         if (alive) {
           tc_fence_after();
           if (lane == 0) {
@@ -638,9 +611,6 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(pfull);
-#ifdef B200ATTN_TRACE
-        if (tid == 0 && j == 0) TSTAMP(4);
-#endif
       }
 
       // ---------------- end of segment: read O once, hand the group's state to the epilogue warp ----------------
@@ -697,13 +667,9 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       cur = seg_end;
       if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
     }
-    if (tid == 0) { TSTAMP(6); }
   }
   tc_fence_before();
   __syncthreads();
-#ifdef B200ATTN_TRACE
-  if (tid == 0) { TSTAMP(7); atomicMax(&g_launch_span[2 * s_launch + 1], global_timer_ns()); }
-#endif
   if (warp == kIssuerS2) {
     if (sFlags[0] && lane == 0) {
       // A wait gave up: wait (bounded) for everything already issued into this CTA's shared / tensor memory.
@@ -847,22 +813,3 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
 
 }  // namespace b200attn
 
-#ifdef B200ATTN_TRACE
-extern "C" int b200attn_debug_trace2(unsigned long long* host_out, int n_ctas, int clear) {
-  if (clear) {
-    static unsigned long long zeros[4096 * 8];
-    return (int)cudaMemcpyToSymbol(b200attn::g_trace2, zeros, sizeof(zeros));
-  }
-  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_trace2, (size_t)n_ctas * 8 * sizeof(unsigned long long));
-}
-extern "C" int b200attn_debug_launch_spans(unsigned long long* host_out, int reset) {
-  if (reset) {
-    static unsigned long long init[128];
-    for (int i = 0; i < 64; ++i) { init[2 * i] = ~0ull; init[2 * i + 1] = 0; }
-    unsigned int zero = 0;
-    cudaMemcpyToSymbol(b200attn::g_entry_ctr, &zero, sizeof(zero));
-    return (int)cudaMemcpyToSymbol(b200attn::g_launch_span, init, sizeof(init));
-  }
-  return (int)cudaMemcpyFromSymbol(host_out, b200attn::g_launch_span, 128 * sizeof(unsigned long long));
-}
-#endif

@@ -51,25 +51,25 @@ extern "C" int b200attn_decode_static(const B200AttnShape* shape, const void* q,
                                       const void* v_cache, const float* k_scale, const float* v_scale,
                                       const int* seq_len, int seq_len_offset, float softmax_scale,
                                       int num_splits, void* out, int* status, void* stream) {
-  // Size check first, with the public helpers, so that an oversized request fails before any CUDA call.
+  // Every host-side check of b200attn_decode comes first, the size check among them: a call that is
+  // going to be refused must not have touched the shared scratch, and an oversized request fails
+  // before the array's address is even asked for.
+  b200attn::Geometry g;
+  int resolved = 0;
   size_t need = 0;
-  if (num_splits == 0) {
-    num_splits = b200attn_pick_splits(shape, shape ? shape->capacity : 0, 148, B200ATTN_VARIANT_MMA);
-    if (num_splits < 0) return num_splits;
-  }
-  int rc = b200attn_workspace_bytes(shape, num_splits, B200ATTN_VARIANT_MMA, &need);
+  int rc = b200attn::decode_precheck(shape, q, k_cache, v_cache, k_scale, v_scale, seq_len, out, false, status,
+                                     B200ATTN_VARIANT_MMA, &num_splits, &g, &resolved, &need);
   if (rc) return rc;
   if (need > kStaticScratchBytes) return B200ATTN_ERR_TOO_LARGE;
-  if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !seq_len || !out || !status) return B200ATTN_ERR_NULL;
 
   void* scratch = nullptr;
   cudaError_t e = scratch_address(&scratch);   // first call on a device: looks the address up
-  if (e != cudaSuccess) return B200ATTN_ERR_CUDA;
+  if (e != cudaSuccess) return b200attn::record_cuda_error(e);
   // tickets sit at the end of the workspace layout: one int per (layer, sequence, kv head)
-  const size_t tickets = (size_t)shape->n_layers * shape->batch * shape->h_kv * sizeof(int);
-  const size_t ticket_off = (size_t)num_splits * 2 * ((size_t)(shape->h_q / shape->h_kv) * shape->head_dim + 16) * sizeof(float);
+  const size_t tickets = (size_t)g.n_layers * g.batch * g.h_kv * sizeof(int);
+  const size_t ticket_off = (size_t)num_splits * 2 * ((size_t)g.group * g.head_dim + 16) * sizeof(float);
   e = cudaMemsetAsync((char*)scratch + ticket_off, 0, tickets, (cudaStream_t)stream);
-  if (e != cudaSuccess) return B200ATTN_ERR_CUDA;
+  if (e != cudaSuccess) return b200attn::record_cuda_error(e);
   return b200attn_decode(shape, q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                          B200ATTN_VARIANT_MMA, num_splits, scratch, kStaticScratchBytes, out, status, stream);
 }

@@ -168,17 +168,6 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-#ifdef B200ATTN_TRACE
-// Development-only timeline: per CTA, globaltimer stamps of (0) kernel entry, (1) prologue done,
-// (2) first tile landed, (3) first segment's tiles consumed, (4) first segment's state dumped,
-// (5) last tile consumed, (6) exit, (7) epilogue warp done.
-static __device__ unsigned long long g_trace[4096 * 8];
-#define TRACE(slot) do { if (tid == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
-#define TRACE_LANE0(slot) do { if (lane == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#define TRACE_LANE0(slot) do { } while (0)
-#endif
 
 // Two floats -> two e4m3 bytes in a 16-bit register: `lo` in the low byte, `hi` in the high byte.
 __device__ __forceinline__ uint32_t pack_e4m3x2(float lo, float hi) {
@@ -437,7 +426,6 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     cur = seg_end;
     if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
   }
-  TRACE_LANE0(7);
 }
 }
 

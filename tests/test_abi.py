@@ -106,7 +106,7 @@ def test_kernel_choice_is_a_pure_host_function(pkg):
     assert r(_shape(pkg, scale_mode=1)) == L.VARIANT_UMMA2                      # per-token scales, long cache
     assert r(_shape(pkg, scale_mode=1, capacity=512)) == L.VARIANT_SIMT         # per-token scales, short cache
     assert r(_shape(pkg, h_q=8, h_kv=1, batch=16, capacity=16640)) == L.VARIANT_UMMA2   # group 8
-    for v in (L.VARIANT_SIMT, L.VARIANT_MMA, L.VARIANT_UMMA, L.VARIANT_UMMA2):
+    for v in (L.VARIANT_SIMT, L.VARIANT_MMA, L.VARIANT_UMMA2):
         assert r(_shape(pkg), v) == v
     assert r(_shape(pkg, h_q=48, h_kv=8), L.VARIANT_UMMA2) == L.VARIANT_UMMA2   # group 6
     assert r(_shape(pkg, scale_mode=1), L.VARIANT_MMA) == L.ERR_SHAPE

@@ -8,7 +8,7 @@ import torch
 from helpers import TOL_COSINE, TOL_MAX_ABS, assert_parity, build_case, run_decode
 
 pytestmark = pytest.mark.gpu
-VARIANTS = ["simt", "mma", "umma", "umma2"]
+VARIANTS = ["simt", "mma", "umma2"]
 
 
 def unsupported(pkg, variant, h_q, h_kv):
@@ -111,7 +111,7 @@ def test_split_counts_agree(pkg, oracle, cuda_device):
                                        case["lens"], 1024)
     outs = []
     for variant, counts in (("simt", [1, 2, 3, 4, 7, 8, 16]), ("mma", [1, 2, 3, 16, 37, 148, 296, 500, 2000]),
-                            ("umma", [1, 5, 148, 296, 1000]), ("umma2", [1, 5, 148, 296, 1000])):
+                            ("umma2", [1, 5, 148, 296, 1000])):
         for n in counts:
             out, status = run_decode(pkg, case, cuda_device, variant, num_splits=n)
             assert status == 0
@@ -162,7 +162,7 @@ def test_ragged_batch_with_empty_and_full_sequences(pkg, oracle, cuda_device, va
     assert bool((out[:, 0] == 0).all()) and bool((out[:, 5] == 0).all())   # empty sequences -> zeros
 
 
-@pytest.mark.parametrize("variant", ["mma", "umma", "umma2"])
+@pytest.mark.parametrize("variant", ["mma", "umma2"])
 def test_batched_ragged_decode_steps_bs16(pkg, oracle, cuda_device, variant):
     """The batched configuration in miniature: bs=16 ragged depths (seeded), 8 layers, two decode
     steps with a fused one-token append per sequence; bytes bit-exact, outputs within tolerance."""
@@ -222,7 +222,7 @@ def test_length_beyond_capacity_is_clamped_and_flagged(pkg, oracle, cuda_device,
     assert torch.equal(out.view(torch.int16), ok.view(torch.int16))
 
 
-@pytest.mark.parametrize("variant", ["mma", "umma", "umma2"])
+@pytest.mark.parametrize("variant", ["mma", "umma2"])
 def test_gated_output_fusion(pkg, oracle, cuda_device, variant):
     """attn_output * sigmoid(gate) with two separate bf16 roundings, fused into the output store."""
     lens = [513, 64]
@@ -411,7 +411,7 @@ def test_full_size_properties(pkg, oracle, cuda_device):
         outs[variant] = pkg.decode_attention(q, kc, vc, ks, vs, seq, workspace=ws)
         torch.cuda.synchronize()
         assert ws.read_status() == 0
-    for variant in ("mma", "umma", "umma2"):
+    for variant in ("mma", "umma2"):
         m = oracle.error_metrics(outs[variant].cpu(), outs["simt"].cpu())
         assert m["max_abs"] <= 2.0 ** -7 and m["cosine"] >= 0.99999, (variant, m)
     for layer in (0, 63):
@@ -421,7 +421,7 @@ def test_full_size_properties(pkg, oracle, cuda_device):
     const = torch.arange(h_kv, device=cuda_device).view(1, 1, h_kv, 1, 1).expand_as(vc)
     vconst = (0x30 + const).to(torch.uint8).contiguous()            # e4m3 0x30.. = 0.5, 0.5625, ...
     want = (vconst[0, 0, :, 0, 0].cpu().view(torch.float8_e4m3fn).float() * (4.5 / 448)).repeat_interleave(5)
-    for variant in ("mma", "umma", "umma2"):
+    for variant in ("mma", "umma2"):
         ws = pkg.Workspace(shape, cuda_device, variant=variant)
         out = pkg.decode_attention(q, kc, vconst, ks, vs, seq, workspace=ws).cpu().float()
         assert (out - want.view(1, 1, h_q, 1)).abs().max().item() <= 2.0 ** -8 * want.max().item(), variant

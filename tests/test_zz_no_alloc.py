@@ -53,10 +53,19 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(pkg, oracle, c
 
 
 def test_static_scratch_rejects_what_does_not_fit(pkg, cuda_device):
+    """Refusals happen on the host, before the shared scratch is touched or anything is launched.  The
+    pointers are real (small) tensors all the same: should the order of the checks ever change, the
+    test gets a wrong return code rather than a kernel running on invented addresses."""
     lib = pkg._lib.lib()
     big = pkg.B200AttnShape(64, 16, 40, 8, 128, 1024, 0, 0, 0, 0)
-    a = 0x10000   # never dereferenced: the size check comes first
+    buf = torch.zeros(4096, dtype=torch.uint8, device=cuda_device)
+    a = buf.data_ptr()
     rc = lib.b200attn_decode_static(ctypes.byref(big), a, a, a, a, a, a, 0, 0.1, 4000, a, a, None)
     assert rc == pkg._lib.ERR_TOO_LARGE
     assert b"4 MiB" in lib.b200attn_error_string(rc)
     assert lib.b200attn_decode_static(None, a, a, a, a, a, a, 0, 0.1, 0, a, a, None) == pkg._lib.ERR_NULL
+    small = pkg.B200AttnShape(1, 1, 40, 8, 128, 64, 0, 0, 0, 0)
+    assert lib.b200attn_decode_static(ctypes.byref(small), a + 4, a, a, a, a, a, 0, 0.1, 0, a, a, None) == pkg._lib.ERR_ALIGN
+    assert lib.b200attn_decode_static(ctypes.byref(small), a, a, a, a, a, a, 0, 0.1, -2, a, a, None) == pkg._lib.ERR_SPLITS
+    torch.cuda.synchronize()
+    assert int(buf.max()) == 0
