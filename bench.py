@@ -7,9 +7,16 @@ A "step" is one decode step of the attention path for all 64 layers: quantize-an
 new token's K/V plus split-K GQA attention over the FP8 cache, replayed as one CUDA graph.
 Headline workload (cfg2): depth 8192, capacity 8192, bs=1, H_q=40, H_kv=8, D=128; the cache is
 full, so every step re-quantises the newest token into the last slot and attends 8192 tokens.
-Other depths of the metric (512, 32768) are measured in the same run and reported under
-"per_depth".  With N > 1 ranks the KV heads are sharded (tensor parallel, strong scaling) and
-every step ends with an all-gather of the per-head outputs over NVLink.
+The other depths of the metric (512, 32768) are measured in the same run under "per_depth", the
+batched ragged workload (bs=16, sharded by sequence) under "per_workload".  With N > 1 ranks the KV
+heads of the single-sequence workloads are sharded (tensor parallel, strong scaling) and every
+step ends with the all-gather of the per-head outputs over NVLink, fused into the kernel.
+
+Protocol (the reference's: within-run step distribution apart from between-run spread,
+runner/report.py:228-258): W warm-up steps, then K steps between two CUDA events — that pass is
+`value` — then four more such passes (median / min / max over the five) and one pass with an event
+pair around every step (p50 / p95).  After the clock has stopped, two layers of the step's result
+are compared with the CPU oracle and reported as "parity".
 
 Synthetic data: seeded N(0,1) bf16 K/V quantised to e4m3 with per-(layer, kv head) absmax/448
 scales by the library's own calibration + bulk-append kernels (the reference's fixed-depth
@@ -41,8 +48,12 @@ WORKLOADS = {
     "cfg2": (8192, 8192, False),
     "cfg3": (32768, 32768 + 256, True),
 }
+CFG4_BATCH, CFG4_LO, CFG4_HI, CFG4_CAP = 16, 1024, 16384, 16384 + 256
 PEAK_FALLBACK_GBS = 6650.0
 REF_SAMPLE_LAYERS = 4
+PASSES = 5
+L2_FREE_COPIES = 6
+PARITY_TOL = {"max_abs": 2e-2, "cosine": 0.9999}
 
 
 def kv_bytes_per_step(depth: int, h_kv: int | None = None) -> int:
@@ -74,8 +85,8 @@ def kernel_name(variant: str, per_token: bool = False) -> str:
 
 
 def load_traffic(workload: str, variant: str):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any
-    (keyed by workload, then by kernel variant)."""
+    """DRAM bytes per launch of the dominant kernel on ONE GPU holding all KV heads, from the committed
+    ncu summary, if any (keyed by workload, then by kernel variant)."""
     p = ROOT / "profiles" / "dram_traffic.json"
     if p.exists():
         try:
@@ -86,6 +97,35 @@ def load_traffic(workload: str, variant: str):
     return None
 
 
+SCALES_TEXT = "per-(layer,kv-head)"
+
+
+def workload_name(key: str) -> str:
+    if key == "cfg4":
+        return (f"cfg4: {N_LAYERS}-layer batched decode, bs={CFG4_BATCH}, ragged depths U[{CFG4_LO},{CFG4_HI}] seed 0, "
+                f"capacity {CFG4_CAP}, H_q={H_Q} H_kv={H_KV} D={D}, FP8-e4m3 KV with {SCALES_TEXT} scales, fused one-token "
+                f"append per sequence per step")
+    depth, cap, _ = WORKLOADS[key]
+    return (f"{key}: {N_LAYERS}-layer bs=1 decode attention, depth {depth}, capacity {cap}, H_q={H_Q} H_kv={H_KV} "
+            f"D={D}, FP8-e4m3 KV with {SCALES_TEXT} scales, append+attend per step")
+
+
+def make_config(key: str, world: int) -> dict:
+    """The `config` object of the JSON line: the same for this arm and for the reference arm."""
+    if key == "cfg4":
+        sharding = f"by sequence x{world} (greedy longest-first on depth), no collective"
+        per_gpu = N_LAYERS * H_KV * D * 2 * CFG4_BATCH * (CFG4_LO + CFG4_HI) // 2 // world
+    else:
+        sharding = f"kv-head tensor parallel x{world}"
+        per_gpu = kv_bytes_per_step(WORKLOADS[key][0]) // world
+    l2 = (f"inputs larger than L2 (about {per_gpu / 1e6:.0f} MB of KV per GPU per step)" if per_gpu > 200e6 else
+          f"KV working set ({per_gpu / 1e6:.0f} MB per GPU) smaller than L2: L2-warm figure; an L2-free figure that rotates "
+          f"{L2_FREE_COPIES} cache copies is reported beside it where measured")
+    return {"workload": workload_name(key), "sharding": sharding, "l2": l2,
+            "execution": "one CUDA-graph replay per step: quantize-append + split-K attention + combine"
+                         + (" + output all-gather and cross-GPU barrier" if world > 1 and key != "cfg4" else "")}
+
+
 class ClockSampler:
     """SM clock and throttle reasons read through NVML (read-only) every few ms by a thread
     while the timed region runs."""
@@ -93,7 +133,7 @@ class ClockSampler:
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
                0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, torch, index: int, period_s: float = 0.004):
+    def __init__(self, torch, index: int, period_s: float = 0.002):
         self.samples, self.bits, self.max_mhz, self.period = [], 0, None, period_s
         self.stop_flag = threading.Event()
         self.handle = None
@@ -134,6 +174,15 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
+def percentile(values, q: float) -> float:
+    s = sorted(values)
+    if not s:
+        return float("nan")
+    k = (len(s) - 1) * q
+    lo, hi = int(k), min(int(k) + 1, len(s) - 1)
+    return s[lo] + (s[hi] - s[lo]) * (k - lo)
+
+
 # ------------------------------------------------------------------------------------------
 # reference arm: the oracle port on the host cores
 # ------------------------------------------------------------------------------------------
@@ -146,13 +195,15 @@ def run_reference(args) -> int:
     depth, cap, _ = WORKLOADS[args.workload]
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    q, k, v = oracle.make_inputs(0, H_Q, H_KV, D, depth)
-    sk, sv = oracle.head_scales(k), oracle.head_scales(v)
-    kb, vb = oracle.quantize_per_head(k, sk), oracle.quantize_per_head(v, sv)
     cap = max(cap, depth)
+    layers = []
+    for layer in range(REF_SAMPLE_LAYERS):             # every sampled layer has its own q / K / V
+        q, k, v = oracle.make_inputs(layer, H_Q, H_KV, D, depth)
+        sk, sv = oracle.head_scales(k), oracle.head_scales(v)
+        layers.append((q, oracle.quantize_per_head(k, sk), oracle.quantize_per_head(v, sv), sk, sv))
 
     def sample_step():
-        for _ in range(REF_SAMPLE_LAYERS):
+        for q, kb, vb, sk, sv in layers:
             oracle.padded_fp8_reference(q, kb, vb, sk, sv, cap)
 
     for _ in range(args.warmup):
@@ -162,13 +213,13 @@ def run_reference(args) -> int:
         sample_step()
     dt = (time.perf_counter() - t0) / args.steps
     us_per_step = dt * 1e6 * (N_LAYERS / REF_SAMPLE_LAYERS)
-    sample = (f"each timed step = {REF_SAMPLE_LAYERS} of {N_LAYERS} layers of dequant+pad+padded torch attention "
-              f"at depth {depth}, scaled x{N_LAYERS // REF_SAMPLE_LAYERS}")
+    sample = (f"each timed step = {REF_SAMPLE_LAYERS} of {N_LAYERS} layers (own K/V each) of dequant+pad+padded torch attention "
+              f"at depth {depth}, scaled x{N_LAYERS // REF_SAMPLE_LAYERS}; host wall clock")
     line = {
         "impl": "reference", "metric": METRIC, "value": us_per_step, "unit": "us/step", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": us_per_step / 1e3, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (torch CPU, fp32 softmax)", "data": "synthetic",
-        "config": {"workload": workload_name(args.workload, depth, cap), "timing": "host wall clock"},
+        "config": make_config(args.workload, args.gpus),
         "cpu_baseline": {"value": us_per_step, "unit": "us/step", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": us_per_step, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -177,58 +228,53 @@ def run_reference(args) -> int:
     return 0
 
 
-SCALES_TEXT = "per-(layer,kv-head)"
-
-
-def workload_name(key: str, depth: int, cap: int) -> str:
-    return (f"{key}: {N_LAYERS}-layer bs=1 decode attention, depth {depth}, capacity {cap}, H_q={H_Q} H_kv={H_KV} "
-            f"D={D}, FP8-e4m3 KV with {SCALES_TEXT} scales, append+attend per step")
-
-
 # ------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------
 class StepRunner:
-    """One workload resident on one GPU: cache, static step buffers, captured graph."""
+    """One workload resident on one GPU: cache, static step buffers, captured graph.
 
-    def __init__(self, pkg, torch, device, depth, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto",
-                 num_splits=0, gather="peer", scale_mode="per_head"):
-        self.pkg, self.torch, self.device, self.depth, self.advance = pkg, torch, device, depth, advance
-        self.h_q, self.h_kv, self.dist, self.world = h_q, h_kv, dist, world
+    Single-sequence workloads: `depths` is one depth, the KV heads are this rank's share and, with more
+    than one rank, the results go into every rank's gathered buffers.  Batched workload: `depths` are this
+    rank's sequences, all heads, no exchange."""
+
+    def __init__(self, pkg, torch, device, depths, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto",
+                 num_splits=0, gather="peer", scale_mode="per_head", tensor_parallel=True):
+        self.pkg, self.torch, self.device, self.depths, self.advance = pkg, torch, device, list(depths), advance
+        self.h_q, self.h_kv, self.dist, self.world, self.cap = h_q, h_kv, dist, world, cap
+        batch = len(self.depths)
         g = torch.Generator(device=device).manual_seed(seed)
-        self.cache = pkg.FP8StaticCache(N_LAYERS, 1, h_q, h_kv, D, cap, device=device, variant=variant,
+        self.cache = pkg.FP8StaticCache(N_LAYERS, batch, h_q, h_kv, D, cap, device=device, variant=variant,
                                         num_splits=num_splits, scale_mode=scale_mode)
-        prefix = depth if advance else depth - 1      # cfg2: slot depth-1 is rewritten by every step
-        chunk = 8192
+        longest = max(self.depths)
+        prefix = longest if advance else longest - 1      # cfg2: slot depth-1 is rewritten by every step
+        chunk = 8192 if batch == 1 else 2048
         scales_done = False
-        for t0 in range(0, prefix, chunk):
+        for t0 in range(0, prefix, chunk):                # every slot up to the longest depth; ragged lengths are set below
             n = min(chunk, prefix - t0)
-            k = torch.randn(N_LAYERS, 1, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
-            v = torch.randn(N_LAYERS, 1, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
+            k = torch.randn(N_LAYERS, batch, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
+            v = torch.randn(N_LAYERS, batch, h_kv, n, D, generator=g, device=device, dtype=torch.bfloat16)
             self.cache.prefill(k, v, calibrate=not scales_done and scale_mode == "per_head")
             scales_done = True
-        self.start_pos = prefix
-        self.q = torch.randn(N_LAYERS, 1, h_q, D, generator=g, device=device, dtype=torch.bfloat16)
-        self.k_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
-        self.v_new = torch.randn(N_LAYERS, 1, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
+        self.start_pos = torch.tensor([d if advance else d - 1 for d in self.depths], dtype=torch.int32, device=device)
+        self.q = torch.randn(N_LAYERS, batch, h_q, D, generator=g, device=device, dtype=torch.bfloat16)
+        self.k_new = torch.randn(N_LAYERS, batch, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
+        self.v_new = torch.randn(N_LAYERS, batch, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
         self.out = torch.empty_like(self.q)
         distmod = importlib.import_module("qwen38-5080_b200.dist")
         self.peer = None
         self.gatherer = None
-        if world > 1 and gather == "peer":
+        if world > 1 and tensor_parallel and gather == "peer":
             self.peer = distmod.PeerOutput(self.out, world, dist.get_rank())
-            self.full_out = self.peer.full
-        elif world > 1:
+        elif world > 1 and tensor_parallel:
             self.gatherer = distmod.HeadGather(self.out, world)
-            self.full_out = self.gatherer.full
-        else:
-            self.full_out = None
         self.graph = None
+        self.gather_in_graph = False
 
     def launch_step(self):
         c = self.cache
         if self.peer is not None:
-            # append + attention storing into every rank's gathered buffer (+ position bump), then the cross-GPU barrier
+            # one launch: append + attention storing into every rank's gathered buffer + position bump + cross-GPU barrier
             self.pkg.append_decode(self.q, self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
                                    workspace=c.workspace, advance=self.advance, peer_out=self.peer, barrier=True)
             return
@@ -239,17 +285,22 @@ class StepRunner:
         if self.gatherer is not None:
             self.gatherer.gather(self.out)     # NCCL all-gather + one strided copy into [n, b, h_q, D]
 
+    def result(self):
+        """The step's result as a consumer on this rank sees it (all heads)."""
+        if self.peer is not None:
+            return self.peer.current()
+        return self.gatherer.full if self.gatherer is not None else self.out
+
     def capture(self):
         torch = self.torch
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(3):
+            for _ in range(4):
                 self.launch_step()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.reset_pos()
-        self.gather_in_graph = False
         if self.gatherer is not None:          # the all-gather belongs to the step: capture it with the kernels
             with torch.cuda.stream(side):
                 self.gather()
@@ -273,21 +324,20 @@ class StepRunner:
         self.reset_pos()
 
     def reset_pos(self):
-        self.cache.seq_pos.fill_(self.start_pos)
+        self.cache.seq_pos.copy_(self.start_pos)
 
     def step(self):
         self.graph.replay()
-        if not self.gather_in_graph:
+        if self.gatherer is not None and not self.gather_in_graph:
             self.gather()
 
     def kernels_per_step(self) -> int:
         fused = self.cache.workspace.resolved in ("umma2", "mma") and not self.cache.per_token
-        if self.peer is not None:                # (append, bump,) attention with fused gather, barrier
-            return (1 if self.cache.workspace.resolved == "umma2" else 2) if fused else (3 if self.advance else 2) + 1
         if fused:
-            return 1                         # the fused step: append, attention, combine and position bump in one launch
+            return 1                         # the fused step: append, attention, combine, position bump (and barrier) in one launch
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump
-        return n + (1 if self.cache.workspace.variant == "simt" and self.cache.workspace.num_splits > 1 else 0)
+        n += 1 if self.cache.workspace.resolved == "simt" and self.cache.workspace.num_splits > 1 else 0
+        return n + (1 if self.peer is not None else 0)
 
 
 def barrier(dist, world):
@@ -295,15 +345,34 @@ def barrier(dist, world):
         dist.barrier()
 
 
-def timed_steps(torch, dist, world, runner, steps, warmup, sampler=None) -> float:
-    """Seconds per step on the device: W warm-up steps, then K steps between CUDA events,
-    barrier + synchronize on both sides, max over ranks."""
+def max_over_ranks(torch, dist, world, device, value: float) -> float:
+    if world == 1:
+        return value
+    t = torch.tensor([value], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed_pass(torch, dist, world, runner, steps, warmup, per_step=False):
+    """One pass: W warm-up steps, then K steps between CUDA events (barrier + synchronize on both sides).
+    Returns seconds per step (max over ranks); with per_step=True an event pair brackets every step
+    instead and the list of this rank's step times (seconds) is returned too."""
     runner.reset_pos()
     for _ in range(warmup):
         runner.step()
     torch.cuda.synchronize()
     barrier(dist, world)
     torch.cuda.synchronize()
+    if per_step:
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record()
+        for i in range(steps):
+            runner.step()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        barrier(dist, world)
+        each = [ev[i].elapsed_time(ev[i + 1]) / 1e3 for i in range(steps)]
+        return max_over_ranks(torch, dist, world, runner.device, sum(each) / steps), each
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -311,12 +380,22 @@ def timed_steps(torch, dist, world, runner, steps, warmup, sampler=None) -> floa
     e1.record()
     torch.cuda.synchronize()
     barrier(dist, world)
-    sec = e0.elapsed_time(e1) / 1e3 / steps
-    if world > 1:
-        t = torch.tensor([sec], device=runner.device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec = float(t.item())
-    return sec
+    return max_over_ranks(torch, dist, world, runner.device, e0.elapsed_time(e1) / 1e3 / steps), None
+
+
+def measure(torch, dist, world, runner, steps, warmup) -> dict:
+    """The protocol of the module docstring for one workload; seconds."""
+    passes = [timed_pass(torch, dist, world, runner, steps, warmup)[0] for _ in range(PASSES)]
+    _, each = timed_pass(torch, dist, world, runner, steps, warmup, per_step=True)
+    return {"first": passes[0], "passes": passes, "each": each}
+
+
+def stats_entry(m: dict) -> dict:
+    us = [x * 1e6 for x in m["passes"]]
+    each = [x * 1e6 for x in m["each"]]
+    return {"passes_us": {"n": len(us), "median": statistics.median(us), "min": min(us), "max": max(us)},
+            "step_us": {"n": len(each), "p50": percentile(each, 0.5), "p95": percentile(each, 0.95),
+                        "note": "one event pair per step (this rank); the events add to the gap between replays"}}
 
 
 def timed_kernel(torch, runner, steps, warmup) -> float:
@@ -329,8 +408,6 @@ def timed_kernel(torch, runner, steps, warmup) -> float:
         runner.pkg.decode_attention(runner.q, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
                                     workspace=c.workspace, seq_len_offset=off, out=runner.out)
     runner.reset_pos()
-    if runner.advance:
-        c.seq_pos.fill_(runner.depth)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -358,24 +435,31 @@ def timed_kernel(torch, runner, steps, warmup) -> float:
 
 def timed_e2e(torch, dist, world, runner, steps, warmup) -> tuple[float, int, int]:
     """Through the public API with HOST buffers: per step, pinned-host q/k/v -> device, the decode
-    step, device -> pinned-host output, and a synchronize (the caller needs the result).  The
-    copies and the step are captured into one CUDA graph (memcpy nodes + the library's launches),
-    as a host that replays its decode step would do; if that capture is refused the same sequence
-    is issued call by call."""
+    step, device -> pinned-host result, and a synchronize (the caller needs the result).  With one
+    rank the result is the whole output; tensor-parallel, every rank reads back the heads it computed
+    from its gathered buffer (together the ranks read the whole result once; the gathered tensor itself
+    stays on the device, where its consumer is).  The copies and the step are captured into one CUDA
+    graph (memcpy nodes + the library's launch), as a host that replays its decode step would do; two
+    steps per graph, because the tensor-parallel step alternates between two gathered buffers."""
     hq, hk, hv = (t.cpu().pin_memory() for t in (runner.q, runner.k_new, runner.v_new))
-    src = runner.full_out if world > 1 else runner.out
-    hout = torch.empty(src.shape, dtype=src.dtype).pin_memory()
+    if runner.peer is not None:
+        rank, hq_loc = runner.peer.rank, runner.h_q
+        sources = [runner.peer.buffers[(runner.peer.steps_done() + 1 + i) & 1][:, :, rank * hq_loc:(rank + 1) * hq_loc] for i in range(2)]
+    else:
+        sources = [runner.result()] * 2
+    hout = torch.empty(sources[0].shape, dtype=sources[0].dtype).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
     d2h = hout.numel() * hout.element_size()
 
     def sequence():
-        runner.q.copy_(hq, non_blocking=True)
-        runner.k_new.copy_(hk, non_blocking=True)
-        runner.v_new.copy_(hv, non_blocking=True)
-        runner.launch_step()
-        if runner.gatherer is not None:
-            runner.gather()
-        hout.copy_(src, non_blocking=True)
+        for src in sources:
+            runner.q.copy_(hq, non_blocking=True)
+            runner.k_new.copy_(hk, non_blocking=True)
+            runner.v_new.copy_(hv, non_blocking=True)
+            runner.launch_step()
+            if runner.gatherer is not None:
+                runner.gather()
+            hout.copy_(src, non_blocking=True)
 
     graph = None
     try:
@@ -393,34 +477,111 @@ def timed_e2e(torch, dist, world, runner, steps, warmup) -> tuple[float, int, in
         graph = None
         torch.cuda.synchronize()
 
-    def one():
+    def two_steps():
         if graph is not None:
             graph.replay()
         else:
             sequence()
         torch.cuda.synchronize()
 
+    reps = max(1, (steps + 1) // 2)
     runner.reset_pos()
-    for _ in range(warmup):
-        one()
+    for _ in range(max(1, warmup // 2)):
+        two_steps()
+    runner.reset_pos()
     barrier(dist, world)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        one()
+    for _ in range(reps):
+        two_steps()
     e1.record()
     torch.cuda.synchronize()
-    wall = (time.perf_counter() - t0) / steps
+    wall = (time.perf_counter() - t0) / (2 * reps)
     barrier(dist, world)
     runner.reset_pos()
-    sec = max(e0.elapsed_time(e1) / 1e3 / steps, wall)
+    sec = max(e0.elapsed_time(e1) / 1e3 / (2 * reps), wall)
+    return max_over_ranks(torch, dist, world, runner.device, sec), h2d, d2h * (world if runner.peer is not None else 1)
+
+
+def timed_l2_free(pkg, torch, device, depth, cap, h_q, h_kv, variant, steps, warmup) -> float:
+    """Seconds per step when the cache cannot stay in L2: the step rotates through several copies of the cache
+    (each with its own data), one graph replay = one step on every copy.  This rank's heads, no exchange."""
+    runners = [StepRunner(pkg, torch, device, [depth], cap, True, h_q, h_kv, seed=100 + i, variant=variant)
+               for i in range(L2_FREE_COPIES)]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for r in runners:
+            r.launch_step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for r in runners:
+            r.launch_step()
+    reps = max(1, steps // L2_FREE_COPIES)
+    for r in runners:
+        r.reset_pos()
+    for _ in range(max(1, warmup // L2_FREE_COPIES)):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    for r in runners:
+        if r.cache.workspace.read_status():
+            raise SystemExit("device status set in the L2-free run")
+    return e0.elapsed_time(e1) / 1e3 / (reps * L2_FREE_COPIES)
+
+
+def parity_check(torch, dist, world, runner, seq_plan=None, layers=None) -> dict | None:
+    """Off the clock: one more step from the start positions, then two layers of its result (as rank 0 sees it:
+    the gathered tensor when tensor-parallel) against the CPU oracle — the reference's padded torch attention over
+    the dequantised cache.  The other ranks' K/V bytes, scales and queries of those layers are gathered for it.
+    Sequence-sharded: every rank checks its own sequences; the worst figures over the ranks are reported."""
+    from oracle import ref_attention as oracle
+    layers = [0, N_LAYERS - 1] if layers is None else layers
+    c = runner.cache
+    runner.reset_pos()
+    runner.step()
+    torch.cuda.synchronize()
+    barrier(dist, world)
+    lens = [int(x) + 1 for x in runner.start_pos.cpu().tolist()]
+    longest = max(lens)
+    idx = torch.tensor(layers, device=runner.device)
+    mine = {"k": c.k_cache.index_select(0, idx)[:, :, :, :longest].contiguous(), "v": c.v_cache.index_select(0, idx)[:, :, :, :longest].contiguous(),
+            "ks": c.k_scale.index_select(0, idx).contiguous(), "vs": c.v_scale.index_select(0, idx).contiguous(),
+            "q": runner.q.index_select(0, idx).contiguous()}
+    result = runner.result().index_select(0, idx).contiguous()
+    rank = dist.get_rank() if world > 1 else 0
+    if world > 1 and seq_plan is None:         # tensor parallel: heads of all ranks, in rank order
+        full = {}
+        for name, t in mine.items():
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t)
+            full[name] = torch.cat(parts, dim=t.dim() - 1 if name in ("ks", "vs") else 2)   # the KV-head axis
+        mine = full
+    worst = {"max_abs": 0.0, "cosine": 1.0}
+    if rank == 0 or seq_plan is not None:
+        ref = oracle.decode_step_reference(mine["q"].cpu(), mine["k"].cpu(), mine["v"].cpu(), mine["ks"].cpu(), mine["vs"].cpu(),
+                                           lens, longest)
+        got = result.cpu()
+        for b in range(len(lens)):
+            m = oracle.error_metrics(got[:, b], ref[:, b])
+            worst = {"max_abs": max(worst["max_abs"], m["max_abs"]), "cosine": min(worst["cosine"], m["cosine"])}
     if world > 1:
-        t = torch.tensor([sec], device=runner.device, dtype=torch.float64)
+        t = torch.tensor([worst["max_abs"], -worst["cosine"]], device=runner.device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec = float(t.item())
-    return sec, h2d, d2h
+        worst = {"max_abs": float(t[0].item()), "cosine": -float(t[1].item())}
+    runner.reset_pos()
+    worst.update({"layers": layers, "against": "CPU oracle (the reference's padded torch attention on the dequantised cache)",
+                  "ok": worst["max_abs"] <= PARITY_TOL["max_abs"] and worst["cosine"] >= PARITY_TOL["cosine"]})
+    return worst
 
 
 def cpu_baseline(depth: int, cap: int) -> dict:
@@ -432,6 +593,29 @@ def cpu_baseline(depth: int, cap: int) -> dict:
             "attn_only_us_per_step": r["attn_s_per_layer"] * N_LAYERS * 1e6,
             "sample": f"median of {r['samples']} single-layer runs (dequant + pad + padded torch attention) at depth "
                       f"{depth}, capacity {max(cap, depth)}, scaled x{N_LAYERS} layers"}
+
+
+def cfg4_depths(torch) -> list[int]:
+    return torch.randint(CFG4_LO, CFG4_HI + 1, (CFG4_BATCH,), generator=torch.Generator().manual_seed(0)).tolist()
+
+
+def build_runner(pkg, torch, device, dist, world, rank, key, args):
+    """(runner, steps, extra) for a workload key on this rank."""
+    if key == "cfg4":
+        depths_all = cfg4_depths(torch)
+        plan = pkg.dist.assign_sequences(depths_all, world)
+        depths = [depths_all[i] for i in plan[rank]]
+        steps = max(1, min(args.steps, 256 - args.warmup - 8))
+        runner = StepRunner(pkg, torch, device, depths, CFG4_CAP, True, H_Q, H_KV, seed=rank, dist=dist, world=world,
+                            variant=args.variant, num_splits=args.ctas, tensor_parallel=False)
+        loads = [sum(depths_all[i] for i in p) for p in plan]
+        return runner, steps, {"plan": plan, "depths": depths_all, "loads": loads}
+    depth, cap, advance = WORKLOADS[key]
+    room = cap - depth - args.warmup - 8 if advance else 1 << 30   # the cache must not overflow
+    steps = max(1, min(args.steps, room))
+    runner = StepRunner(pkg, torch, device, [depth], cap, advance, H_Q // world, H_KV // world, seed=rank, dist=dist, world=world,
+                        variant=args.variant, num_splits=args.ctas, gather=args.gather, scale_mode=args.scales)
+    return runner, steps, {}
 
 
 def run_ours(args) -> int:
@@ -452,74 +636,108 @@ def run_ours(args) -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     pkg = importlib.import_module("qwen38-5080_b200")
-    if H_KV % world:
+    if H_KV % world or CFG4_BATCH % world:
         raise SystemExit("KV-head sharding needs a GPU count that divides 8")
-    h_kv, h_q = H_KV // world, H_Q // world
 
-    per_depth, runners = {}, {}
-    order = [args.workload] + [w for w in WORKLOADS if w != args.workload and not args.only]
+    others = [] if args.only else [w for w in list(WORKLOADS) + ["cfg4"] if w != args.workload]
+    if args.scales != "per_head":
+        others = [w for w in others if w != "cfg4"]
+    per_depth, per_workload = {}, {}
     headline = None
-    for key in order:
-        depth, cap, advance = WORKLOADS[key]
-        room = cap - depth - args.warmup - 4 if advance else 1 << 30   # the cache must not overflow
-        steps = max(1, min(args.steps, room))
-        runner = StepRunner(pkg, torch, device, depth, cap, advance, h_q, h_kv, seed=rank, dist=dist, world=world,
-                            variant=args.variant, num_splits=args.ctas, gather=args.gather, scale_mode=args.scales)
+    for key in [args.workload] + others:
+        runner, steps, extra = build_runner(pkg, torch, device, dist, world, rank, key, args)
         runner.capture()
         if world > 1:   # every rank in step before the first timed (or barrier-carrying) launch
             torch.cuda.synchronize()
             dist.barrier()
+        is_headline = key == args.workload
         with ClockSampler(torch, local) as sampler:
-            sec = timed_steps(torch, dist, world, runner, steps, args.warmup)
+            m = measure(torch, dist, world, runner, steps, args.warmup)
             ksec = timed_kernel(torch, runner, steps, args.warmup)
-        status = runner.cache.workspace.read_status()
-        if status:
-            raise SystemExit(f"device status {status} after {key}")
-        total_bytes = kv_bytes_per_step(depth)                 # whole job (all ranks)
-        entry = {"us_per_step": sec * 1e6, "us_per_layer": sec * 1e6 / N_LAYERS,
-                 "hbm_gbs_whole_job": total_bytes / sec / 1e9, "hbm_gbs_per_gpu": total_bytes / world / sec / 1e9,
-                 "frac_of_8TBs_per_gpu": total_bytes / world / sec / 8e12,
-                 "attn_kernel_us": ksec * 1e6, "attn_kernel_gbs_per_gpu": total_bytes / world / ksec / 1e9,
-                 "steps": steps}
-        per_depth[str(depth)] = entry
-        if key == args.workload:
-            headline = (key, runner, sec, ksec, sampler.summary(), steps)
-            e2e_sec, h2d, d2h = timed_e2e(torch, dist, world, runner, steps, args.warmup)
+        sec = m["first"]
+        if runner.cache.workspace.read_status():
+            raise SystemExit(f"device status {runner.cache.workspace.read_status()} after {key}")
+        waits = None
+        if runner.peer is not None:     # how long each rank's last arrive-and-wait took (device time stamps)
+            w = torch.tensor([runner.peer.last_wait_us()], device=device, dtype=torch.float64)
+            allw = [torch.empty_like(w) for _ in range(world)]
+            dist.all_gather(allw, w)
+            waits = [float(x.item()) for x in allw]
+        parity = None if args.no_parity else parity_check(torch, dist, world, runner, seq_plan=extra.get("plan"))
+        if key == "cfg4":
+            mean_len = [d + args.warmup + (steps + 1) / 2 for d in extra["depths"]]      # lengths grow by one per step
+            total_bytes = N_LAYERS * H_KV * D * 2 * sum(mean_len)
+            share = max(extra["loads"]) / sum(extra["loads"])
+            entry = {"us_per_step": sec * 1e6, "hbm_gbs_whole_job": total_bytes / sec / 1e9,
+                     "hbm_gbs_busiest_gpu": total_bytes * share / sec / 1e9, "frac_of_8TBs_busiest_gpu": total_bytes * share / sec / 8e12,
+                     "tokens_per_s": CFG4_BATCH / sec, "sum_depth_per_rank": extra["loads"],
+                     "busiest_rank_share": share, "load_imbalance": max(extra["loads"]) * world / sum(extra["loads"]),
+                     "kernel": runner.cache.workspace.resolved, "gpu_launches_per_step": runner.kernels_per_step(), "steps": steps}
+            bytes_per_launch = total_bytes * share
         else:
-            del runner
-            torch.cuda.empty_cache()
+            depth = WORKLOADS[key][0]
+            total_bytes = kv_bytes_per_step(depth)                 # whole job (all ranks)
+            entry = {"us_per_step": sec * 1e6, "us_per_layer": sec * 1e6 / N_LAYERS,
+                     "hbm_gbs_whole_job": total_bytes / sec / 1e9, "hbm_gbs_per_gpu": total_bytes / world / sec / 1e9,
+                     "frac_of_8TBs_per_gpu": total_bytes / world / sec / 8e12,
+                     "attn_kernel_us": ksec * 1e6, "attn_kernel_gbs_per_gpu": total_bytes / world / ksec / 1e9,
+                     "kernel": runner.cache.workspace.resolved, "steps": steps}
+            bytes_per_launch = kv_bytes_per_step(depth, H_KV // world)
+            if total_bytes / world < 200e6 and not args.no_l2_free:
+                l2f = timed_l2_free(pkg, torch, device, depth, WORKLOADS[key][1], H_Q // world, H_KV // world, args.variant,
+                                    steps, args.warmup)
+                l2f = max_over_ranks(torch, dist, world, device, l2f)
+                entry["l2_free"] = {"us_per_step": l2f * 1e6, "hbm_gbs_per_gpu": total_bytes / world / l2f / 1e9,
+                                    "copies": L2_FREE_COPIES, "note": "this rank's heads, no exchange; the step rotates through "
+                                    f"{L2_FREE_COPIES} caches so that none of them stays in L2"}
+        entry.update(stats_entry(m))
+        if waits is not None:
+            entry["exchange_wait_us"] = {"min": min(waits), "max": max(waits),
+                                         "note": "last step: from a rank's arrival at the in-launch barrier to its release"}
+        if parity is not None:
+            entry["parity"] = parity
+        (per_workload if key == "cfg4" else per_depth)[key if key == "cfg4" else str(WORKLOADS[key][0])] = entry
+        if is_headline:
+            e2e_sec, h2d, d2h = timed_e2e(torch, dist, world, runner, steps, args.warmup)
+            headline = {"key": key, "sec": sec, "ksec": ksec, "clocks": sampler.summary(), "steps": steps, "m": m,
+                        "resolved": runner.cache.workspace.resolved, "per_token": runner.cache.per_token,
+                        "launches": runner.kernels_per_step(), "bytes_per_launch": bytes_per_launch, "total_bytes": total_bytes,
+                        "e2e": (e2e_sec, h2d, d2h), "parity": parity, "entry": entry}
+        del runner
+        torch.cuda.empty_cache()
 
-    key, runner, sec, ksec, clocks, steps = headline
-    depth, cap, advance = WORKLOADS[key]
+    h = headline
+    key = h["key"]
     peak, peak_kind = load_peak()
-    bytes_per_launch = kv_bytes_per_step(depth, h_kv)           # one GPU's launch
-    achieved = bytes_per_launch / ksec / 1e9
+    achieved = h["bytes_per_launch"] / h["ksec"] / 1e9
+    traffic = load_traffic(key, h["resolved"])
+    one_gpu_bytes = kv_bytes_per_step(WORKLOADS[key][0]) if key in WORKLOADS else None
     line = {
-        "metric": METRIC, "value": sec * 1e6, "unit": "us/step", "n_gpus": world, "steps": steps,
-        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": DTYPES[runner.cache.workspace.resolved],
-        "data": "synthetic",
-        "config": {"workload": workload_name(key, depth, cap), "sharding": f"kv-head tensor parallel x{world}",
-                   "l2": f"inputs larger than L2 ({kv_bytes_per_step(depth, h_kv) / 1e6:.0f} MB KV per GPU per step)"
-                         if bytes_per_launch > 200e6 else "KV working set smaller than L2: L2-warm figure",
-                   "execution": "CUDA graph replay of " + ("the fused append + attention launch" if runner.kernels_per_step() == 1 else "append + attention")
-                                + ((" with the output all-gather fused into the attention kernel (peer stores over NVLink into "
-                                     "every rank's gathered buffer) + a cross-GPU barrier kernel, all in the graph"
-                                     if runner.peer is not None else
-                                     " + NCCL all-gather + head reorder copy, captured in the graph" if runner.gather_in_graph
-                                     else " then NCCL all-gather + head reorder copy after the replay") if world > 1 else "")},
-        "hbm_gbs": kv_bytes_per_step(depth) / sec / 1e9,
-        "frac_of_8TBs": kv_bytes_per_step(depth) / world / sec / 8e12,
+        "metric": METRIC, "value": h["sec"] * 1e6, "unit": "us/step", "n_gpus": world, "steps": h["steps"],
+        "warmup": args.warmup, "ms_per_step": h["sec"] * 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": DTYPES[h["resolved"]], "data": "synthetic",
+        "config": make_config(key, world),
+        "hbm_gbs": h["total_bytes"] / h["sec"] / 1e9,
+        "frac_of_8TBs": h["bytes_per_launch"] / h["sec"] / 8e12,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": load_traffic(key, runner.cache.workspace.resolved), "kernel": kernel_name(runner.cache.workspace.resolved, runner.cache.per_token), "peak_kind": peak_kind,
-                     "algorithmic_bytes_per_launch": bytes_per_launch, "launch_us": ksec * 1e6},
-        "e2e": {"value": e2e_sec * 1e6, "unit": "us/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": runner.kernels_per_step() * steps,
-        "clocks": clocks,
-        "per_depth": per_depth,
+                     "traffic": None if traffic is None or not one_gpu_bytes else traffic * h["bytes_per_launch"] / one_gpu_bytes,
+                     "traffic_note": "ncu DRAM bytes of a 16-layer launch on one GPU, scaled by the KV bytes this launch reads",
+                     "kernel": kernel_name(h["resolved"], h["per_token"]), "peak_kind": peak_kind,
+                     "algorithmic_bytes_per_launch": h["bytes_per_launch"], "launch_us": h["ksec"] * 1e6},
+        "e2e": {"value": h["e2e"][0] * 1e6, "unit": "us/step", "h2d_bytes_per_step": h["e2e"][1], "d2h_bytes_per_step": h["e2e"][2]},
+        "gpu_launches": h["launches"] * h["steps"],
+        "clocks": h["clocks"],
     }
-    if world == 1 and rank == 0 and not args.no_cpu:
-        line["cpu_baseline"] = cpu_baseline(depth, cap)
+    line.update(stats_entry(h["m"]))
+    if h["parity"] is not None:
+        line["parity"] = h["parity"]
+    if "exchange_wait_us" in h["entry"]:
+        line["exchange_wait_us"] = h["entry"]["exchange_wait_us"]
+    line["per_depth"] = per_depth
+    if per_workload:
+        line["per_workload"] = per_workload
+    if world == 1 and rank == 0 and not args.no_cpu and key in WORKLOADS:
+        line["cpu_baseline"] = cpu_baseline(*WORKLOADS[key][:2])
     if rank == 0:
         print(json.dumps(line), flush=True)
     finish(torch, dist, world)
@@ -537,95 +755,6 @@ def finish(torch, dist, world) -> None:
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
-
-
-def run_cfg4(args) -> int:
-    """Batched decode (BASELINE config 4): bs=16 ragged depths U[1024, 16384] (seed 0), sharded by
-    sequence over the ranks with no data-path collective; a step = fused one-token K/V
-    quantize-append per sequence + attention, replayed as a CUDA graph."""
-    import torch
-    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
-    pkg = importlib.import_module("qwen38-5080_b200")
-    g0 = torch.Generator().manual_seed(0)
-    depths_all = torch.randint(1024, 16384 + 1, (16,), generator=g0).tolist()
-    plan = pkg.dist.assign_sequences(depths_all, world)
-    depths = [depths_all[i] for i in plan[rank]]
-    batch, cap = len(depths), 16384 + 256
-    room = 256 - args.warmup - 8
-    steps = max(1, min(args.steps, room))
-    g = torch.Generator(device=device).manual_seed(rank)
-    cache = pkg.FP8StaticCache(N_LAYERS, batch, H_Q, H_KV, D, cap, device=device, variant=args.variant,
-                               num_splits=args.ctas)
-    done = False
-    for t0 in range(0, max(depths), 2048):      # fill every slot up to the longest depth, then set the ragged lengths
-        n = min(2048, max(depths) - t0)
-        k = torch.randn(N_LAYERS, batch, H_KV, n, D, generator=g, device=device, dtype=torch.bfloat16)
-        v = torch.randn(N_LAYERS, batch, H_KV, n, D, generator=g, device=device, dtype=torch.bfloat16)
-        cache.prefill(k, v, calibrate=not done)
-        done = True
-    start = torch.tensor(depths, dtype=torch.int32, device=device)
-    q = torch.randn(N_LAYERS, batch, H_Q, D, generator=g, device=device, dtype=torch.bfloat16)
-    kn = torch.randn(N_LAYERS, batch, H_KV, D, generator=g, device=device, dtype=torch.bfloat16)
-    vn = torch.randn(N_LAYERS, batch, H_KV, D, generator=g, device=device, dtype=torch.bfloat16)
-    out = torch.empty_like(q)
-
-    def launch():
-        pkg.append_decode(q, kn, vn, cache.k_cache, cache.v_cache, cache.k_scale, cache.v_scale, cache.seq_pos,
-                          workspace=cache.workspace, advance=True, out=out)
-    cache.seq_pos.copy_(start)
-    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for _ in range(3):
-            launch()
-    torch.cuda.current_stream().wait_stream(side); torch.cuda.synchronize()
-    cache.seq_pos.copy_(start)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        launch()
-    torch.cuda.synchronize()
-    cache.seq_pos.copy_(start)
-    for _ in range(args.warmup):
-        graph.replay()
-    torch.cuda.synchronize(); barrier(dist, world); torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(torch, local) as sampler:
-        e0.record()
-        for _ in range(steps):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-    barrier(dist, world)
-    sec = e0.elapsed_time(e1) / 1e3 / steps
-    if world > 1:
-        t = torch.tensor([sec], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec = float(t.item())
-    status = cache.workspace.read_status()
-    if status:
-        raise SystemExit(f"device status {status}")
-    mean_len = [d + args.warmup + (steps + 1) / 2 for d in depths_all]      # lengths grow by one per step
-    total_bytes = N_LAYERS * H_KV * D * 2 * sum(mean_len)
-    line = {"metric": METRIC, "value": sec * 1e6, "unit": "us/step", "n_gpus": world, "steps": steps, "warmup": args.warmup,
-            "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": DTYPES[cache.workspace.resolved], "data": "synthetic",
-            "config": {"workload": f"cfg4: {N_LAYERS}-layer batched decode, bs=16, ragged depths U[1024,16384] seed 0 "
-                                   f"(sum {sum(depths_all)}), capacity {cap}, fused one-token append per sequence per step",
-                       "sharding": f"by sequence x{world} (greedy longest-first on depth), no collective",
-                       "execution": "CUDA graph replay of " + ("one fused launch: append + attention + position bump" if cache.workspace.resolved in ("umma2", "mma") else "append + attention + position bump")},
-            "hbm_gbs": total_bytes / sec / 1e9, "frac_of_8TBs": total_bytes / world / sec / 8e12,
-            "tokens_per_s": 16 / sec, "gpu_launches": (1 if cache.workspace.resolved in ("umma2", "mma") else 3) * steps, "clocks": sampler.summary()}
-    if rank == 0:
-        print(json.dumps(line), flush=True)
-    finish(torch, dist, world)
-    return 0
 
 
 def main() -> int:
@@ -646,6 +775,8 @@ def main() -> int:
     ap.add_argument("--ctas", type=int, default=0, help="override the split / CTA count (0 = library default)")
     ap.add_argument("--layers", type=int, default=64, help="layers per step (64 = the metric; fewer only for profiling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-parity", action="store_true", help="skip the off-clock comparison with the CPU oracle")
+    ap.add_argument("--no-l2-free", action="store_true", help="skip the L2-free variant of the short-cache workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     global N_LAYERS, SCALES_TEXT, H_Q, H_KV, D
@@ -654,11 +785,9 @@ def main() -> int:
         H_Q, H_KV, D = (int(x) for x in args.heads.split(","))
     if args.scales == "per_token":
         SCALES_TEXT = "per-(token,kv-head)"
-    if args.workload == "cfg4":
-        if args.impl == "reference":
-            raise SystemExit("--impl reference times the bs=1 workloads (cfg1..cfg3)")
-        return run_cfg4(args)
     if args.impl == "reference":
+        if args.workload == "cfg4":
+            raise SystemExit("--impl reference times the bs=1 workloads (cfg1..cfg3)")
         return run_reference(args)
     return run_ours(args)
 

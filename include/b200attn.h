@@ -91,13 +91,24 @@ typedef struct B200AttnShape {
  * the gathered tensor bf16 [n_layers][batch][h_q_total][head_dim] of ALL ranks (plain peer stores
  * over NVLink into symmetric / peer-mapped memory), at head offset rank*h_q.  out[r] is rank r's
  * buffer as addressable from this GPU.  b200attn_peer_barrier then makes the stores visible.
+ *
+ * Double buffering (n_buffers = 2): a fast rank may begin its next step while a slow rank's consumer
+ * still reads the gathered tensor of this one, so every rank holds two gathered tensors and the steps
+ * use them in turn.  Which one a launch writes is decided on the device, from the step counter that
+ * the cross-GPU barrier keeps (word [n_peers] of this rank's flag buffer, see b200attn_peer_barrier):
+ * the launch that finds e there writes out[] when e + 1 is even and out_alt[] when it is odd, and the
+ * barrier that follows makes the counter e + 1.  A replayed CUDA graph therefore alternates by
+ * itself, a consumer on the device reads the same word, and the host finds the tensor of the latest
+ * completed step at parity (counter & 1).  Every step must be followed by exactly one barrier.
  */
 typedef struct B200AttnPeerOut {
   int n_peers;       /* 1..8 */
   int rank;          /* this rank */
   int h_q_total;     /* = n_peers * shape->h_q */
-  int reserved;
+  int n_buffers;     /* 0 or 1: out[] only; 2: out[] and out_alt[] in turn */
   void* out[8];
+  void* out_alt[8];  /* n_buffers == 2: every rank's second gathered tensor */
+  const int* epoch;  /* n_buffers == 2: this rank's step counter, flags[rank] + n_peers (device memory) */
 } B200AttnPeerOut;
 
 /* Library version (B200ATTN_VERSION of the build). */
@@ -245,8 +256,8 @@ int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* pee
  * kernels, three otherwise.  With barrier_flags == NULL, follow it with
  * b200attn_peer_barrier as for b200attn_decode_peers.  With barrier_flags (the flag buffers
  * b200attn_peer_barrier takes) the cross-GPU arrive-and-wait is part of the call: done by the
- * last CTA of the attention launch with B200ATTN_VARIANT_UMMA2, by the barrier kernel launched
- * behind the attention otherwise; same bounded wait and status bit.
+ * last CTA of the attention launch with the stream-K kernels, by the barrier kernel launched
+ * behind the attention otherwise; same bounded wait and status bit.  (Both stream-K kernels do it inside the launch.)
  * (The reference has no multi-GPU path: no counterpart there.)
  */
 int b200attn_append_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* peers,
@@ -261,8 +272,11 @@ int b200attn_append_decode_peers(const B200AttnShape* shape, const B200AttnPeerO
                                  int* status, void* stream);
 
 /*
- * Cross-GPU arrive-and-wait.  flags[r] = rank r's flag buffer (int32[world + 1], zero-initialised,
- * symmetric / peer-mapped memory) as addressable from this GPU.  Every rank launches it once per
+ * Cross-GPU arrive-and-wait.  flags[r] = rank r's flag buffer (int32[24], zero-initialised,
+ * symmetric / peer-mapped memory) as addressable from this GPU: words [0, world) are the arrival
+ * epochs the ranks write, word [world] is the owner's epoch (= step) counter, words [16..19] hold two
+ * 64-bit %globaltimer stamps of the owner's latest arrive-and-wait (arrival, end of the wait), there
+ * for whoever wants to know how long a rank waited for the others.  Every rank launches it once per
  * step; it returns when all ranks have arrived.  The wait is bounded (1 s): on expiry
  * B200ATTN_STATUS_WAIT_TIMEOUT is OR-ed into *status and the kernel returns.  Graph-replayable:
  * the epoch counter lives in the flag buffer.

@@ -32,8 +32,8 @@ class B200AttnShape(ctypes.Structure):
 
 
 class B200AttnPeerOut(ctypes.Structure):
-    _fields_ = [("n_peers", c_int), ("rank", c_int), ("h_q_total", c_int), ("reserved", c_int),
-                ("out", c_void_p * 8)]
+    _fields_ = [("n_peers", c_int), ("rank", c_int), ("h_q_total", c_int), ("n_buffers", c_int),
+                ("out", c_void_p * 8), ("out_alt", c_void_p * 8), ("epoch", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/b200attn.h declares

@@ -72,6 +72,23 @@ int resolve_variant(int variant, const Geometry& g) {
   return B200ATTN_ERR_VARIANT;
 }
 
+// Gathered-output description of a tensor-parallel call.
+int check_peers(const B200AttnPeerOut* peers, const Geometry& g) {
+  if (peers->n_peers < 1 || peers->n_peers > 8 || peers->rank < 0 || peers->rank >= peers->n_peers) return B200ATTN_ERR_SHAPE;
+  if (peers->h_q_total != g.h_q * peers->n_peers) return B200ATTN_ERR_SHAPE;
+  if (peers->n_buffers < 0 || peers->n_buffers > 2) return B200ATTN_ERR_SHAPE;
+  for (int r = 0; r < peers->n_peers; ++r) {
+    if (!peers->out[r]) return B200ATTN_ERR_NULL;
+    if (!aligned16(peers->out[r])) return B200ATTN_ERR_ALIGN;
+    if (peers->n_buffers == 2) {
+      if (!peers->out_alt[r]) return B200ATTN_ERR_NULL;
+      if (!aligned16(peers->out_alt[r])) return B200ATTN_ERR_ALIGN;
+    }
+  }
+  if (peers->n_buffers == 2 && !peers->epoch) return B200ATTN_ERR_NULL;
+  return B200ATTN_OK;
+}
+
 int pick(const Geometry& g, int v, int max_seq_len, int num_sms) {
   if (v == B200ATTN_VARIANT_SIMT) return simt_pick_splits(g, max_seq_len, num_sms);
   if (v == B200ATTN_VARIANT_UMMA2) return umma2_pick_ctas(g, max_seq_len, num_sms);
@@ -227,7 +244,6 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
                num_splits, workspace, workspace_bytes, out, status, gate, 0, 0, 0, {}};
   if (fused) {
     if (v != B200ATTN_VARIANT_UMMA2 && v != B200ATTN_VARIANT_MMA) return B200ATTN_ERR_VARIANT;
-    if (fused->barrier_flags && v != B200ATTN_VARIANT_UMMA2) return B200ATTN_ERR_VARIANT;
     a.k_new = fused->k_new;
     a.v_new = fused->v_new;
     a.seq_pos = fused->seq_pos;
@@ -243,16 +259,16 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
   }
   if (peers) {
     if (v == B200ATTN_VARIANT_SIMT) return B200ATTN_ERR_VARIANT;
-    if (peers->n_peers < 1 || peers->n_peers > 8 || peers->rank < 0 || peers->rank >= peers->n_peers) return B200ATTN_ERR_SHAPE;
-    if (peers->h_q_total != g.h_q * peers->n_peers) return B200ATTN_ERR_SHAPE;
     a.n_out = peers->n_peers;
     a.out_hq_total = peers->h_q_total;
     a.out_head_base = peers->rank * g.h_q;
+    rc = check_peers(peers, g);
+    if (rc) return rc;
     for (int r = 0; r < peers->n_peers; ++r) {
-      if (!peers->out[r]) return B200ATTN_ERR_NULL;
-      if (!aligned16(peers->out[r])) return B200ATTN_ERR_ALIGN;
       a.out_peer[r] = peers->out[r];
+      a.out_peer_alt[r] = peers->n_buffers == 2 ? peers->out_alt[r] : peers->out[r];
     }
+    a.epoch = peers->n_buffers == 2 ? peers->epoch : nullptr;
   }
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
                                              : v == B200ATTN_VARIANT_UMMA2 ? launch_decode_umma2(g, a, (cudaStream_t)stream)
@@ -305,12 +321,8 @@ static int step_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, c
   if (rc) return rc;
   if (!q || (!out && !peers) || !seq_pos || !status) return B200ATTN_ERR_NULL;
   if (peers) {
-    if (peers->n_peers < 1 || peers->n_peers > 8 || peers->rank < 0 || peers->rank >= peers->n_peers) return B200ATTN_ERR_SHAPE;
-    if (peers->h_q_total != g.h_q * peers->n_peers) return B200ATTN_ERR_SHAPE;
-    for (int r = 0; r < peers->n_peers; ++r) {
-      if (!peers->out[r]) return B200ATTN_ERR_NULL;
-      if (!aligned16(peers->out[r])) return B200ATTN_ERR_ALIGN;
-    }
+    rc = check_peers(peers, g);
+    if (rc) return rc;
   }
   const int v = resolve_variant(variant, g);
   if (v < 0) return v;
@@ -325,16 +337,13 @@ static int step_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, c
   if (!aligned16(q) || !aligned16(out) || !aligned16(workspace)) return B200ATTN_ERR_ALIGN;
   if ((v == B200ATTN_VARIANT_UMMA2 || v == B200ATTN_VARIANT_MMA) && g.scale_mode == B200ATTN_SCALE_PER_HEAD) {
     // one launch: the attention kernel appends the new rows and advances the positions itself
-    // (per-token scales are computed by the append kernel: three launches below); the in-launch
-    // cross-GPU barrier exists in the all-tcgen05 kernel only: the barrier kernel follows otherwise
+    // (per-token scales are computed by the append kernel: three launches below), and ends with the
+    // cross-GPU barrier when one is asked for
     if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale) return B200ATTN_ERR_NULL;
     if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return B200ATTN_ERR_ALIGN;
-    const bool barrier_inside = v == B200ATTN_VARIANT_UMMA2;
-    const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr, barrier_inside ? barrier_flags : nullptr};
-    rc = decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
-                     workspace, workspace_bytes, out, status, stream, &fused);
-    if (rc || barrier_inside || !barrier_flags) return rc;
-    return b200attn_peer_barrier(barrier_flags, peers->rank, peers->n_peers, status, stream);
+    const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr, barrier_flags};
+    return decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_pos, 1, softmax_scale, v, num_splits,
+                       workspace, workspace_bytes, out, status, stream, &fused);
   }
   if (peers && v == B200ATTN_VARIANT_SIMT) return B200ATTN_ERR_VARIANT;
   rc = b200attn_kv_quant_append_bulk(shape, 1, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 0,

@@ -113,6 +113,8 @@ struct DecodeArgs {
   int n_out;          // peer mode (tensor-core variants only): number of rank buffers, 0 = local output
   int out_hq_total, out_head_base;
   void* out_peer[8];
+  void* out_peer_alt[8] = {};    // double-buffered gathered output: the second tensor of every rank
+  const int* epoch = nullptr;    // and the step counter whose parity picks the tensor (null = out_peer always)
   // fused step (all-tcgen05 variant only): the new token of every pair is quantised into the cache by
   // the CTA that owns the pair's last tile, and the last CTA to finish advances the positions
   const void* k_new = nullptr;   // bf16 [n_layers][batch][h_kv][1][head_dim]; null = attention only

@@ -165,7 +165,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         for (int i = tid; i < g.h_q * D; i += kThreads) {
           if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
           else
-            for (int pr = 0; pr < p.n_out; ++pr) p.out_peer[pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
+            for (int pr = 0; pr < p.n_out; ++pr)
+              (peer_buffer_is_alt(p) ? p.out_peer_alt[pr] : p.out_peer[pr])[(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
         }
     }
   }
@@ -444,18 +445,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       while (!mbar_try_wait(qfull0 + 8u * qb, (last_seg >> 1) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
     }
   }
-  if (p.seq_pos && tid == 0) {
-    // Fused step: every CTA read the positions before it got here; the last one to arrive advances them.
-    int arrived;
-    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.exit_count) : "memory");
-    if (arrived == (int)gridDim.x - 1) {
-      for (int b = 0; b < g.batch; ++b) {
-        const int pos = p.seq_pos[b];
-        if (pos >= 0 && pos + 1 <= g.capacity) p.seq_pos[b] = pos + 1;
-      }
-      *p.exit_count = 0;   // ready for the next launch
-    }
-  }
+  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(p, lane);
 }
 
 int stages_for(const Geometry& g) { return 3; }
@@ -514,6 +504,8 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.out_hq_total = a.n_out ? a.out_hq_total : g.h_q;
   p.out_head_base = a.n_out ? a.out_head_base : 0;
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
+  for (int r = 0; r < 8; ++r) p.out_peer_alt[r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
+  p.epoch = a.n_out ? a.epoch : nullptr;
   p.status = a.status;
   p.stages = stages_for(g);
   p.k_new = (const uint16_t*)a.k_new;
@@ -522,6 +514,9 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.v_cache_w = (uint8_t*)a.v_cache;
   p.seq_pos = a.seq_pos;
   p.exit_count = p.tickets + (size_t)g.n_layers * g.batch * g.h_kv;
+  for (int r = 0; r < 8; ++r) p.bar_flags[r] = r < a.bar_world ? a.bar_flags[r] : nullptr;
+  p.bar_rank = a.bar_rank;
+  p.bar_world = a.bar_world;
   const size_t smem = smem_bytes_for(g, p.stages);
   auto launch = [&](auto kernel) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -254,7 +254,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         for (int i = tid; i < g.h_q * D; i += kThreads2) {
           if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
           else
-            for (int pr = 0; pr < p.n_out; ++pr) p.out_peer[pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
+            for (int pr = 0; pr < p.n_out; ++pr)
+              (peer_buffer_is_alt(p) ? p.out_peer_alt[pr] : p.out_peer[pr])[(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
         }
     }
   }
@@ -690,42 +691,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if ((p.seq_pos || p.bar_world) && tid == 0) {
-    // Every CTA read the positions and stored its outputs before it got here; the last one to arrive
-    // advances the positions and, in a tensor-parallel step, does the cross-GPU arrive-and-wait.
-    int arrived;
-    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.exit_count) : "memory");
-    if (arrived == (int)gridDim.x - 1) {
-      if (p.seq_pos)
-        for (int b = 0; b < g.batch; ++b) {
-          const int pos = p.seq_pos[b];
-          if (pos >= 0 && pos + 1 <= g.capacity) p.seq_pos[b] = pos + 1;
-        }
-      *p.exit_count = 0;   // ready for the next launch
-      if (p.bar_world) {
-        // Same protocol as the stand-alone barrier kernel: bump the own epoch, publish it to every rank
-        // (all peer stores of this launch are ordered before it through the exit counter and the fence), wait
-        // (bounded, 1 s) until every rank's epoch has reached it.
-        int* mine = p.bar_flags[p.bar_rank];
-        const int e = mine[p.bar_world] + 1;
-        // one system-scope fence orders every peer store of the launch before the flags; the flag stores
-        // themselves are then relaxed and go out back to back (a release per flag costs a round trip each)
-        __threadfence_system();
-        for (int r = 0; r < p.bar_world; ++r)
-          asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.bar_flags[r] + p.bar_rank), "r"(e) : "memory");
-        const unsigned long long t0 = global_timer_ns();
-        for (int r = 0; r < p.bar_world; ++r) {
-          for (;;) {
-            int v;
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + r) : "memory");
-            if (v - e >= 0) break;
-            if (global_timer_ns() - t0 > 1000000000ull) { atomicOr(p.status, B200ATTN_STATUS_WAIT_TIMEOUT); r = p.bar_world; break; }
-          }
-        }
-        mine[p.bar_world] = e;
-      }
-    }
-  }
+  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(p, lane);
 }
 
 // Ring depths: all of the shared memory that the fixed part leaves, at most 4 K and 8 V tiles.
@@ -783,6 +749,8 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   p.out_hq_total = a.n_out ? a.out_hq_total : g.h_q;
   p.out_head_base = a.n_out ? a.out_head_base : 0;
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
+  for (int r = 0; r < 8; ++r) p.out_peer_alt[r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
+  p.epoch = a.n_out ? a.epoch : nullptr;
   p.status = a.status;
   p.k_new = (const uint16_t*)a.k_new;
   p.v_new = (const uint16_t*)a.v_new;

@@ -33,6 +33,9 @@ struct MmaParams {
   // peer mode (tensor-parallel by KV head): every result is stored into the output buffer of all
   // n_out ranks, laid out [n_layers][batch][out_hq_total][D], at head offset out_head_base
   uint16_t* out_peer[8];
+  uint16_t* out_peer_alt[8];   // second gathered tensor of every rank (double buffering), used when `epoch` is set
+  const int* epoch;            // this rank's step counter (the barrier's own-epoch word): the launch that finds e there
+                               // writes out_peer when e + 1 is even, out_peer_alt when it is odd; null = out_peer always
   int n_out;             // 0 = local output only
   int out_hq_total, out_head_base;
   const uint16_t* gate;  // optional bf16 [n_layers][batch][h_q][D]: out *= sigmoid(gate), see store_out
@@ -258,11 +261,16 @@ __device__ __forceinline__ void cta_range(long long total, int grid, int cta, in
 // consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
 __device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
 
+// Which of the two gathered tensors this launch writes (see MmaParams::epoch).
+__device__ __forceinline__ bool peer_buffer_is_alt(const MmaParams& p) {
+  return p.epoch != nullptr && ((*reinterpret_cast<const volatile int*>(p.epoch) + 1) & 1) != 0;
+}
+
 // Two adjacent outputs -> bf16.  With a gate, the consumer-side fusion of the reference's attention
 // block, attn_output * sigmoid(gate), with its two separate bf16 roundings
 // (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150): s = bf16(sigmoid(gate)), then
 // bf16(bf16(attn) * s).
-__device__ __forceinline__ void store_out(const MmaParams& p, long long idx, long long peer_idx, float x, float y) {
+__device__ __forceinline__ void store_out(const MmaParams& p, bool alt, long long idx, long long peer_idx, float x, float y) {
   uint16_t* out = p.out;
   const uint16_t* gate = p.gate;
   __nv_bfloat162 ob = __floats2bfloat162_rn(x, y);
@@ -279,7 +287,7 @@ __device__ __forceinline__ void store_out(const MmaParams& p, long long idx, lon
     // the output all-gather, fused: plain stores into every rank's buffer (own one included) over NVLink
 #pragma unroll
     for (int r = 0; r < 8; ++r)
-      if (r < p.n_out) *reinterpret_cast<uint32_t*>(p.out_peer[r] + peer_idx) = bits;
+      if (r < p.n_out) *reinterpret_cast<uint32_t*>((alt ? p.out_peer_alt[r] : p.out_peer[r]) + peer_idx) = bits;
   }
 }
 
@@ -301,6 +309,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
   const Geometry& g = p.g;
   const int G = g.group;
   const int dump_warp_floats = G * DP;
+  const bool alt = peer_buffer_is_alt(p);
 {
   Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
   long long cur = r0;
@@ -344,7 +353,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           const float inv = ll > 0.f ? vs / ll : 0.f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            store_out(p, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
+            store_out(p, alt, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
           }
         } else {
 #pragma unroll
@@ -415,7 +424,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
             const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
 #pragma unroll
             for (int r = 0; r < UR; ++r) {
-              store_out(p, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
+              store_out(p, alt, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
             }
           }
         }
@@ -426,7 +435,65 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     cur = seg_end;
     if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
   }
+  // Peer mode: every lane's stores into the other GPUs' buffers are made visible system-wide here, by the warp
+  // that issued them, so that the fence of the CTA that finishes the launch finds nothing of them outstanding.
+  if (p.n_out) __threadfence_system();
 }
+}
+
+// Layout of a barrier flag buffer (int32 words, peer-writable): [0, world) arrival epochs written by the ranks,
+// [world] the owner's epoch counter, [16..19] two 64-bit %globaltimer stamps of the owner's latest
+// arrive-and-wait (when it arrived, when the wait ended).
+constexpr int kFlagStampWord = 16;
+constexpr unsigned long long kBarrierBudgetNs = 1000000000ull;   // 1 s
+
+// Cross-GPU arrive-and-wait by one warp: bump the own epoch, publish it into every rank's flag buffer, wait
+// (bounded) until every rank's epoch has reached it.  Lane r talks to rank r, so the flag stores go out
+// together and the polls run side by side.  The caller has made the launch's peer stores happen-before this
+// warp (exit counter + warp shuffle); each publishing lane's system-scope fence orders them before its flag.
+__device__ __forceinline__ void warp_peer_barrier(int* const* flags, int rank, int world, int lane, int* status) {
+  int* mine = flags[rank];
+  const int e = *reinterpret_cast<volatile int*>(mine + world) + 1;
+  const unsigned long long t0 = global_timer_ns();
+  if (lane < world) {
+    __threadfence_system();
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(flags[lane] + rank), "r"(e) : "memory");
+    for (;;) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + lane) : "memory");
+      if (v - e >= 0) break;
+      if (global_timer_ns() - t0 > kBarrierBudgetNs) { atomicOr(status, B200ATTN_STATUS_WAIT_TIMEOUT); break; }
+    }
+  }
+  __syncwarp();
+  if (lane == 0) {
+    unsigned long long* stamp = reinterpret_cast<unsigned long long*>(mine + kFlagStampWord);
+    stamp[0] = t0;
+    stamp[1] = global_timer_ns();
+    *reinterpret_cast<volatile int*>(mine + world) = e;
+  }
+}
+
+// Last act of a launch that is a whole decode step, called by warp 0 of every CTA after the CTA's final
+// __syncthreads (all of the CTA's reads of the positions and all its output stores are done): the warp of the
+// last CTA to arrive advances the positions and, tensor-parallel, does the cross-GPU arrive-and-wait.
+// Out of line: it runs once per CTA and must not cost the tile loops registers.
+__device__ __noinline__ void finish_step(const MmaParams& p, int lane) {
+  int last = 0;
+  if (lane == 0) {
+    int arrived;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.exit_count) : "memory");
+    last = arrived == (int)gridDim.x - 1;
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (!last) return;
+  if (p.seq_pos)
+    for (int b = lane; b < p.g.batch; b += 32) {
+      const int pos = p.seq_pos[b];
+      if (pos >= 0 && pos + 1 <= p.g.capacity) p.seq_pos[b] = pos + 1;
+    }
+  if (lane == 0) *p.exit_count = 0;   // ready for the next launch
+  if (p.bar_world) warp_peer_barrier(p.bar_flags, p.bar_rank, p.bar_world, lane, p.status);
 }
 
 // ---------------------------------------------------------------------------------------------

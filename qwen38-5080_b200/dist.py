@@ -59,11 +59,14 @@ class HeadGather:
 
 
 class PeerOutput:
-    """Gathered output [n_layers, batch, h_q_total, D] in symmetric memory, one per rank, plus the
-    flag buffers of the cross-GPU barrier.  The attention kernel of every rank stores its heads
-    straight into all of these buffers (peer stores over NVLink): the all-gather is fused into the
-    kernel, and `ops.peer_barrier` afterwards is all that is left of the collective.
-    Allocate once, before any graph capture."""
+    """Gathered outputs [n_layers, batch, h_q_total, D] in symmetric memory — two per rank, used in turn —
+    plus the flag buffer of the cross-GPU barrier.  The attention kernel of every rank stores its heads
+    straight into all ranks' buffers (peer stores over NVLink): the all-gather is fused into the kernel,
+    and the arrive-and-wait (``ops.peer_barrier``, or the end of a fused step) is all that is left of the
+    collective.  Two buffers because a fast rank may start its next step while a slow rank's consumer
+    still reads this step's tensor; which one a step writes follows, on the device, from the parity of the
+    step counter the barrier keeps, so a replayed graph alternates by itself.
+    Allocate once, before any graph capture; every step must be followed by exactly one barrier."""
 
     def __init__(self, local_like: torch.Tensor, world: int, rank: int, group=None):
         import ctypes
@@ -74,17 +77,37 @@ class PeerOutput:
         n, b, hq, d = local_like.shape
         dev = local_like.device
         self.world, self.rank = world, rank
-        self.full = symm_mem.empty((n, b, world * hq, d), dtype=local_like.dtype, device=dev)
-        self.full.zero_()
-        self._out_hdl = symm_mem.rendezvous(self.full, group)
+        self.buffers = symm_mem.empty((2, n, b, world * hq, d), dtype=local_like.dtype, device=dev)
+        self.buffers.zero_()
+        self._out_hdl = symm_mem.rendezvous(self.buffers, group)
         self.flags = symm_mem.empty((64,), dtype=torch.int32, device=dev)
         self.flags.zero_()
         self._flag_hdl = symm_mem.rendezvous(self.flags, group)
         torch.cuda.synchronize()
         dist.barrier(group)
-        ptrs = (ctypes.c_void_p * 8)(*[int(p) for p in self._out_hdl.buffer_ptrs])
-        self.c_peers = B200AttnPeerOut(world, rank, world * hq, 0, ptrs)
-        self.c_flags = (ctypes.c_void_p * 8)(*[int(p) for p in self._flag_hdl.buffer_ptrs])
+        half = self.buffers[0].numel() * self.buffers.element_size()
+        bases = [int(p) for p in self._out_hdl.buffer_ptrs]
+        flag_ptrs = [int(p) for p in self._flag_hdl.buffer_ptrs]
+        self.c_peers = B200AttnPeerOut(world, rank, world * hq, 2, (ctypes.c_void_p * 8)(*bases),
+                                       (ctypes.c_void_p * 8)(*[p + half for p in bases]), flag_ptrs[rank] + 4 * world)
+        self.c_flags = (ctypes.c_void_p * 8)(*flag_ptrs)
+
+    def steps_done(self) -> int:
+        """The barrier's step counter (synchronises: not for use inside a captured step)."""
+        return int(self.flags[self.world].item())
+
+    def current(self) -> torch.Tensor:
+        """The gathered tensor of the latest completed step (synchronises)."""
+        return self.buffers[self.steps_done() & 1]
+
+    def poison_next(self) -> None:
+        """Fill the tensor the next step is going to write with NaN (for tests: a step must overwrite all of it)."""
+        self.buffers[(self.steps_done() + 1) & 1].fill_(float("nan"))
+
+    def last_wait_us(self) -> float:
+        """How long this rank's latest arrive-and-wait took, from the two device time stamps the barrier leaves."""
+        t = self.flags[16:20].view(torch.int64).cpu().tolist()
+        return (t[1] - t[0]) / 1e3
 
 
 def gather_sequences(local: torch.Tensor, plan: list[list[int]], batch: int, group=None) -> torch.Tensor:

@@ -138,7 +138,9 @@ def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspac
                      softmax_scale: float | None = None, seq_len_offset: int = 0, out: torch.Tensor | None = None,
                      variant: str | None = None, gate: torch.Tensor | None = None, peer_out=None) -> torch.Tensor:
     """Split-K GQA decode attention over the FP8 cache; returns bf16 with q's shape.
-    With `gate` (bf16, q's shape) the result is bf16(bf16(attention) * bf16(sigmoid(gate)))."""
+    With `gate` (bf16, q's shape) the result is bf16(bf16(attention) * bf16(sigmoid(gate))).
+    With `peer_out` (tensor parallel) the results go into every rank's gathered buffer and nothing is returned:
+    after the barrier, `peer_out.current()` is the gathered tensor."""
     _need_cuda(q, k_scale, v_scale, seq_len)
     if q.dtype != torch.bfloat16:
         raise ValueError("q must be bf16")
@@ -155,7 +157,7 @@ def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspac
             _ptr(v_scale), _ptr(seq_len), seq_len_offset, scale, VARIANTS[variant or workspace.variant],
             workspace.num_splits, _ptr(workspace.buf), workspace.nbytes, _ptr(workspace.status), _stream())
         check(rc, "b200attn_decode_peers")
-        return peer_out.full
+        return None     # after the barrier: peer_out.current()
     if out is None:
         out = torch.empty_like(q)
     if gate is not None:
@@ -198,7 +200,7 @@ def append_decode(q, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 
             workspace.num_splits, _ptr(workspace.buf), workspace.nbytes, peer_out.c_flags if barrier else None,
             _ptr(workspace.status), _stream())
         check(rc, "b200attn_append_decode_peers")
-        return peer_out.full
+        return None     # after the barrier: peer_out.current()
     if out is None:
         out = torch.empty_like(q)
     scale = d ** -0.5 if softmax_scale is None else softmax_scale

@@ -61,6 +61,21 @@ def test_length_sweep_against_oracle(pkg, oracle, cuda_device, variant):
 
 
 @pytest.mark.parametrize("variant", VARIANTS)
+def test_one_short_of_and_exactly_a_full_8192_cache(pkg, oracle, cuda_device, variant):
+    """Depth 8191 and 8192 in capacity 8192 (the reference's check list names 8191): the last tile is
+    one token short of full, then full; NaN bytes in the one free slot."""
+    for L in (8191, 8192):
+        case = build_case(oracle, 1, 1, 40, 8, 128, [L], 8192, seed=400 + L, fill_byte=0xFF)
+        out, status = run_decode(pkg, case, cuda_device, variant)
+        clean_k, clean_v = case["k_cache"].clone(), case["v_cache"].clone()
+        clean_k[:, :, :, L:] = 0
+        clean_v[:, :, :, L:] = 0
+        ref = oracle.decode_step_reference(case["q"], clean_k, clean_v, case["k_scale"], case["v_scale"], [L], 8192)
+        assert status == 0
+        assert_parity(oracle, out, ref, f"{variant}:L={L}")
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
 def test_single_token_is_exactly_the_value_row(pkg, oracle, cuda_device, variant):
     """L=1: softmax weight is 1, so out == bf16(dequantised V row) for every query head."""
     case = build_case(oracle, 1, 1, 40, 8, 128, [1], 64, seed=9)
@@ -417,7 +432,8 @@ def test_full_size_properties(pkg, oracle, cuda_device):
     for layer in (0, 63):
         ref = oracle.decode_step_reference(q[layer:layer + 1].cpu(), kc[layer:layer + 1].cpu(), vc[layer:layer + 1].cpu(),
                                            ks[layer:layer + 1].cpu(), vs[layer:layer + 1].cpu(), [cap], cap)
-        assert_parity(oracle, outs["mma"][layer:layer + 1].cpu(), ref, f"layer {layer}")
+        for variant in ("mma", "umma2"):      # umma2 is what the default kernel choice runs at this size
+            assert_parity(oracle, outs[variant][layer:layer + 1].cpu(), ref, f"{variant} layer {layer}")
     const = torch.arange(h_kv, device=cuda_device).view(1, 1, h_kv, 1, 1).expand_as(vc)
     vconst = (0x30 + const).to(torch.uint8).contiguous()            # e4m3 0x30.. = 0.5, 0.5625, ...
     want = (vconst[0, 0, :, 0, 0].cpu().view(torch.float8_e4m3fn).float() * (4.5 / 448)).repeat_interleave(5)
@@ -425,6 +441,131 @@ def test_full_size_properties(pkg, oracle, cuda_device):
         ws = pkg.Workspace(shape, cuda_device, variant=variant)
         out = pkg.decode_attention(q, kc, vconst, ks, vs, seq, workspace=ws).cpu().float()
         assert (out - want.view(1, 1, h_q, 1)).abs().max().item() <= 2.0 ** -8 * want.max().item(), variant
+
+
+def _random_cache_bytes(shape, gen, device, sigma_over_max=4.5):
+    """e4m3 bytes of N(0,1) values quantised with scale sigma_over_max/448, made on the device."""
+    x = torch.randn(shape, generator=gen, device=device, dtype=torch.bfloat16)
+    return (x.float() / (sigma_over_max / 448)).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+
+
+def test_long_context_size_against_the_oracle(pkg, oracle, cuda_device):
+    """The long-context configuration at its own size: 64 layers, depth 32768 in capacity 33024, the
+    kernel the default choice picks; layers 0 and 63 against the oracle, then one fused decode step
+    (depth 32769) whose appended bytes must be the oracle's, layer 63 against the oracle again."""
+    n_layers, h_q, h_kv, d, depth, cap = 64, 40, 8, 128, 32768, 33024
+    g = torch.Generator(device=cuda_device).manual_seed(3)
+    cache = pkg.FP8StaticCache(n_layers, 1, h_q, h_kv, d, cap, device=cuda_device)
+    assert cache.workspace.resolved == "umma2"
+    for layer in range(n_layers):      # layer by layer: the bf16 staging stays small
+        cache.k_cache[layer, :, :, :depth] = _random_cache_bytes((1, h_kv, depth, d), g, cuda_device)
+        cache.v_cache[layer, :, :, :depth] = _random_cache_bytes((1, h_kv, depth, d), g, cuda_device)
+    cache.k_cache[:, :, :, depth:] = 0xFF          # NaN patterns in the free slots
+    cache.v_cache[:, :, :, depth:] = 0xFF
+    cache.k_scale.fill_(4.5 / 448)
+    cache.v_scale.fill_(4.5 / 448)
+    cache.seq_pos.fill_(depth)
+    cache.host_len = [depth]
+    q = torch.randn(n_layers, 1, h_q, d, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    kn = torch.randn(n_layers, 1, h_kv, d, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    vn = torch.randn(n_layers, 1, h_kv, d, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    out = cache.attend(q)
+    torch.cuda.synchronize()
+    assert cache.workspace.read_status() == 0
+    ks, vs = cache.k_scale.cpu(), cache.v_scale.cpu()
+
+    def check(result, layer, length, what):
+        kb, vb = cache.k_cache[layer:layer + 1].cpu(), cache.v_cache[layer:layer + 1].cpu()
+        kb[:, :, :, length:] = 0
+        vb[:, :, :, length:] = 0
+        ref = oracle.decode_step_reference(q[layer:layer + 1].cpu(), kb, vb, ks[layer:layer + 1], vs[layer:layer + 1], [length], cap)
+        assert_parity(oracle, result[layer:layer + 1].cpu(), ref, what)
+
+    for layer in (0, 63):
+        check(out, layer, depth, f"depth {depth} layer {layer}")
+    out2 = cache.step(q, kn, vn)
+    torch.cuda.synchronize()
+    assert cache.workspace.read_status() == 0 and cache.seq_pos.cpu().tolist() == [depth + 1]
+    want_k = oracle.quantize_e4m3(kn.cpu(), ks.view(n_layers, 1, h_kv, 1))
+    want_v = oracle.quantize_e4m3(vn.cpu(), vs.view(n_layers, 1, h_kv, 1))
+    assert torch.equal(cache.k_cache[:, :, :, depth].cpu(), want_k) and torch.equal(cache.v_cache[:, :, :, depth].cpu(), want_v)
+    check(out2, 63, depth + 1, f"fused step at depth {depth + 1} layer 63")
+
+
+def test_batched_ragged_size_against_the_oracle(pkg, oracle, cuda_device):
+    """The batched configuration at its own depths: bs = 16, depths randint(1024, 16385) with seed 0,
+    capacity 16640 (2.1 M token rows per layer), 4 layers, the default kernel choice.  One fused decode
+    step: every sequence of two layers against the oracle, appended bytes bit-exact for all layers."""
+    n_layers, batch, h_q, h_kv, d, cap = 4, 16, 40, 8, 128, 16640
+    depths = torch.randint(1024, 16384 + 1, (batch,), generator=torch.Generator().manual_seed(0)).tolist()
+    g = torch.Generator(device=cuda_device).manual_seed(4)
+    cache = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device)
+    assert cache.workspace.resolved == "umma2"
+    cache.k_cache.fill_(0xFF)                     # NaN patterns beyond every sequence's depth
+    cache.v_cache.fill_(0xFF)
+    for layer in range(n_layers):
+        for b, L in enumerate(depths):
+            cache.k_cache[layer, b, :, :L] = _random_cache_bytes((h_kv, L, d), g, cuda_device)
+            cache.v_cache[layer, b, :, :L] = _random_cache_bytes((h_kv, L, d), g, cuda_device)
+    cache.k_scale.fill_(4.5 / 448)
+    cache.v_scale.fill_(4.5 / 448)
+    cache.seq_pos.copy_(torch.tensor(depths, dtype=torch.int32))
+    cache.host_len = list(depths)
+    q = torch.randn(n_layers, batch, h_q, d, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    kn = torch.randn(n_layers, batch, h_kv, d, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    vn = torch.randn(n_layers, batch, h_kv, d, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    out = cache.step(q, kn, vn)
+    torch.cuda.synchronize()
+    assert cache.workspace.read_status() == 0
+    assert cache.seq_pos.cpu().tolist() == [x + 1 for x in depths]
+    ks, vs = cache.k_scale.cpu(), cache.v_scale.cpu()
+    want_k = oracle.quantize_e4m3(kn.cpu(), ks.view(n_layers, 1, h_kv, 1))
+    want_v = oracle.quantize_e4m3(vn.cpu(), vs.view(n_layers, 1, h_kv, 1))
+    for b, L in enumerate(depths):
+        assert torch.equal(cache.k_cache[:, b, :, L].cpu(), want_k[:, b]), f"appended K bytes of sequence {b}"
+        assert torch.equal(cache.v_cache[:, b, :, L].cpu(), want_v[:, b]), f"appended V bytes of sequence {b}"
+    for layer in (0, n_layers - 1):
+        kb, vb = cache.k_cache[layer:layer + 1].cpu(), cache.v_cache[layer:layer + 1].cpu()
+        for b, L in enumerate(depths):
+            kb[:, b, :, L + 1:] = 0
+            vb[:, b, :, L + 1:] = 0
+        ref = oracle.decode_step_reference(q[layer:layer + 1].cpu(), kb, vb, ks[layer:layer + 1], vs[layer:layer + 1],
+                                           [x + 1 for x in depths], cap)
+        for b in range(batch):
+            assert_parity(oracle, out[layer:layer + 1, b:b + 1].cpu(), ref[:, b:b + 1], f"layer {layer} sequence {b} depth {depths[b] + 1}")
+
+
+def test_all_zero_head_stays_finite(pkg, oracle, cuda_device):
+    """A KV head that is zero everywhere: calibration gives it scale 1 (not 0), its appended bytes are
+    0, the attention output of its query heads is exactly 0 and nothing turns into NaN; a zero scale
+    handed in by the caller gives zero bytes too, in the append kernel and in the fused step."""
+    n_layers, h_q, h_kv, d, cap, depth = 2, 40, 8, 128, 256, 130
+    g = torch.Generator().manual_seed(12)
+    k0 = torch.randn(n_layers, 1, h_kv, depth, d, generator=g).to(torch.bfloat16)
+    v0 = torch.randn(n_layers, 1, h_kv, depth, d, generator=g).to(torch.bfloat16)
+    k0[:, :, 3] = 0
+    v0[:, :, 3] = 0
+    q = torch.randn(n_layers, 1, h_q, d, generator=g).to(torch.bfloat16).to(cuda_device)
+    kn = torch.randn(n_layers, 1, h_kv, d, generator=g).to(torch.bfloat16)
+    vn = torch.randn(n_layers, 1, h_kv, d, generator=g).to(torch.bfloat16)
+    kn[:, :, 3] = 0
+    vn[:, :, 3] = 0
+    for variant in VARIANTS:
+        c = pkg.FP8StaticCache(n_layers, 1, h_q, h_kv, d, cap, device=cuda_device, variant=variant)
+        c.prefill(k0.to(cuda_device), v0.to(cuda_device), calibrate=True)
+        assert c.k_scale[:, 3].cpu().tolist() == [1.0, 1.0] and c.v_scale[:, 3].cpu().tolist() == [1.0, 1.0]
+        assert torch.equal(c.k_scale.cpu()[0], oracle.head_scales(k0[0]))
+        out = c.step(q, kn.to(cuda_device), vn.to(cuda_device)).cpu()
+        torch.cuda.synchronize()
+        assert int(c.k_cache[:, :, 3].max()) == 0 and int(c.v_cache[:, :, 3].max()) == 0
+        assert bool(torch.isfinite(out.float()).all()) and bool((out[:, :, 15:20] == 0).all()), variant
+        ref = oracle.decode_step_reference(q.cpu(), c.k_cache.cpu(), c.v_cache.cpu(), c.k_scale.cpu(), c.v_scale.cpu(), [depth + 1], cap)
+        assert_parity(oracle, out, ref, f"{variant}: zero head")
+        # a zero scale from the caller: zero bytes, not NaN bytes
+        c.k_scale[:, 5] = 0
+        c.step(q, kn.to(cuda_device), vn.to(cuda_device))
+        torch.cuda.synchronize()
+        assert int(c.k_cache[:, :, 5, depth + 1].max()) == 0, variant
 
 
 def test_fused_step_equals_separate_launches(pkg, oracle, cuda_device):
