@@ -166,7 +166,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
           if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
           else
             for (int pr = 0; pr < p.n_out; ++pr)
-              (peer_buffer_is_alt(p) ? p.out_peer_alt[pr] : p.out_peer[pr])[(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
+              p.out_peer[peer_buffer_base(p) + pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
         }
     }
   }
@@ -445,7 +445,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       while (!mbar_try_wait(qfull0 + 8u * qb, (last_seg >> 1) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
     }
   }
-  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(p, lane);
+  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(step_end_of(p), lane);
 }
 
 int stages_for(const Geometry& g) { return 3; }
@@ -504,7 +504,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.out_hq_total = a.n_out ? a.out_hq_total : g.h_q;
   p.out_head_base = a.n_out ? a.out_head_base : 0;
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
-  for (int r = 0; r < 8; ++r) p.out_peer_alt[r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
+  for (int r = 0; r < 8; ++r) p.out_peer[8 + r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
   p.epoch = a.n_out ? a.epoch : nullptr;
   p.status = a.status;
   p.stages = stages_for(g);

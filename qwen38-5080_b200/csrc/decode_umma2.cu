@@ -255,7 +255,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
           else
             for (int pr = 0; pr < p.n_out; ++pr)
-              (peer_buffer_is_alt(p) ? p.out_peer_alt[pr] : p.out_peer[pr])[(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
+              p.out_peer[peer_buffer_base(p) + pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
         }
     }
   }
@@ -691,7 +691,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(p, lane);
+  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(step_end_of(p), lane);
 }
 
 // Ring depths: all of the shared memory that the fixed part leaves, at most 4 K and 8 V tiles.
@@ -749,7 +749,7 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   p.out_hq_total = a.n_out ? a.out_hq_total : g.h_q;
   p.out_head_base = a.n_out ? a.out_head_base : 0;
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
-  for (int r = 0; r < 8; ++r) p.out_peer_alt[r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
+  for (int r = 0; r < 8; ++r) p.out_peer[8 + r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
   p.epoch = a.n_out ? a.epoch : nullptr;
   p.status = a.status;
   p.k_new = (const uint16_t*)a.k_new;

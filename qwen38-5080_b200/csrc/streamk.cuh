@@ -32,10 +32,9 @@ struct MmaParams {
   uint16_t* out;         // local output [n_layers][batch][h_q][D] (peer mode: unused)
   // peer mode (tensor-parallel by KV head): every result is stored into the output buffer of all
   // n_out ranks, laid out [n_layers][batch][out_hq_total][D], at head offset out_head_base
-  uint16_t* out_peer[8];
-  uint16_t* out_peer_alt[8];   // second gathered tensor of every rank (double buffering), used when `epoch` is set
+  uint16_t* out_peer[16];      // [0..8): every rank's gathered tensor; [8..16): every rank's second one (double buffering)
   const int* epoch;            // this rank's step counter (the barrier's own-epoch word): the launch that finds e there
-                               // writes out_peer when e + 1 is even, out_peer_alt when it is odd; null = out_peer always
+                               // writes tensors [0..8) when e + 1 is even, [8..16) when it is odd; null = [0..8) always
   int n_out;             // 0 = local output only
   int out_hq_total, out_head_base;
   const uint16_t* gate;  // optional bf16 [n_layers][batch][h_q][D]: out *= sigmoid(gate), see store_out
@@ -261,16 +260,16 @@ __device__ __forceinline__ void cta_range(long long total, int grid, int cta, in
 // consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
 __device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
 
-// Which of the two gathered tensors this launch writes (see MmaParams::epoch).
-__device__ __forceinline__ bool peer_buffer_is_alt(const MmaParams& p) {
-  return p.epoch != nullptr && ((*reinterpret_cast<const volatile int*>(p.epoch) + 1) & 1) != 0;
+// Which of the two gathered tensors this launch writes (see MmaParams::epoch): first index into out_peer.
+__device__ __forceinline__ int peer_buffer_base(const MmaParams& p) {
+  return p.epoch != nullptr && ((*reinterpret_cast<const volatile int*>(p.epoch) + 1) & 1) != 0 ? 8 : 0;
 }
 
 // Two adjacent outputs -> bf16.  With a gate, the consumer-side fusion of the reference's attention
 // block, attn_output * sigmoid(gate), with its two separate bf16 roundings
 // (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150): s = bf16(sigmoid(gate)), then
 // bf16(bf16(attn) * s).
-__device__ __forceinline__ void store_out(const MmaParams& p, bool alt, long long idx, long long peer_idx, float x, float y) {
+__device__ __forceinline__ void store_out(const MmaParams& p, int peer_base, long long idx, long long peer_idx, float x, float y) {
   uint16_t* out = p.out;
   const uint16_t* gate = p.gate;
   __nv_bfloat162 ob = __floats2bfloat162_rn(x, y);
@@ -284,10 +283,10 @@ __device__ __forceinline__ void store_out(const MmaParams& p, bool alt, long lon
   if (p.n_out == 0) {
     *reinterpret_cast<uint32_t*>(out + idx) = bits;
   } else {
-    // the output all-gather, fused: plain stores into every rank's buffer (own one included) over NVLink
-#pragma unroll
-    for (int r = 0; r < 8; ++r)
-      if (r < p.n_out) *reinterpret_cast<uint32_t*>((alt ? p.out_peer_alt[r] : p.out_peer[r]) + peer_idx) = bits;
+    // the output all-gather, fused: plain stores into every rank's buffer (own one included) over NVLink; a rolled
+    // loop: this code is inlined at many places of the epilogue, and the kernels are sensitive to their code size
+#pragma unroll 1
+    for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint32_t*>(p.out_peer[peer_base + r] + peer_idx) = bits;
   }
 }
 
@@ -309,7 +308,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
   const Geometry& g = p.g;
   const int G = g.group;
   const int dump_warp_floats = G * DP;
-  const bool alt = peer_buffer_is_alt(p);
+  const int peer_base = peer_buffer_base(p);
 {
   Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
   long long cur = r0;
@@ -353,7 +352,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           const float inv = ll > 0.f ? vs / ll : 0.f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            store_out(p, alt, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
+            store_out(p, peer_base, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
           }
         } else {
 #pragma unroll
@@ -424,7 +423,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
             const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
 #pragma unroll
             for (int r = 0; r < UR; ++r) {
-              store_out(p, alt, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
+              store_out(p, peer_base, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
             }
           }
         }
@@ -477,23 +476,38 @@ __device__ __forceinline__ void warp_peer_barrier(int* const* flags, int rank, i
 // Last act of a launch that is a whole decode step, called by warp 0 of every CTA after the CTA's final
 // __syncthreads (all of the CTA's reads of the positions and all its output stores are done): the warp of the
 // last CTA to arrive advances the positions and, tensor-parallel, does the cross-GPU arrive-and-wait.
-// Out of line: it runs once per CTA and must not cost the tile loops registers.
-__device__ __noinline__ void finish_step(const MmaParams& p, int lane) {
+// Out of line: it runs once per CTA and must not cost the tile loops registers.  Its arguments travel by value:
+// handing the kernel's parameter block to an out-of-line function by reference takes that block's address, and
+// the tile loops then read their parameters through memory instead of as constant operands (measured: +6 % on
+// the long-cache kernel, +30 % at depth 512).
+struct StepEnd {
+  int* seq_pos;
+  int* exit_count;
+  int* status;
+  int batch, capacity, bar_rank, bar_world;
+  int* flags[8];
+};
+__device__ __forceinline__ StepEnd step_end_of(const MmaParams& p) {
+  return StepEnd{p.seq_pos, p.exit_count, p.status, p.g.batch, p.g.capacity, p.bar_rank, p.bar_world,
+                 {p.bar_flags[0], p.bar_flags[1], p.bar_flags[2], p.bar_flags[3], p.bar_flags[4], p.bar_flags[5], p.bar_flags[6],
+                  p.bar_flags[7]}};
+}
+__device__ __noinline__ void finish_step(StepEnd s, int lane) {
   int last = 0;
   if (lane == 0) {
     int arrived;
-    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.exit_count) : "memory");
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(s.exit_count) : "memory");
     last = arrived == (int)gridDim.x - 1;
   }
   last = __shfl_sync(0xffffffffu, last, 0);
   if (!last) return;
-  if (p.seq_pos)
-    for (int b = lane; b < p.g.batch; b += 32) {
-      const int pos = p.seq_pos[b];
-      if (pos >= 0 && pos + 1 <= p.g.capacity) p.seq_pos[b] = pos + 1;
+  if (s.seq_pos)
+    for (int b = lane; b < s.batch; b += 32) {
+      const int pos = s.seq_pos[b];
+      if (pos >= 0 && pos + 1 <= s.capacity) s.seq_pos[b] = pos + 1;
     }
-  if (lane == 0) *p.exit_count = 0;   // ready for the next launch
-  if (p.bar_world) warp_peer_barrier(p.bar_flags, p.bar_rank, p.bar_world, lane, p.status);
+  if (lane == 0) *s.exit_count = 0;   // ready for the next launch
+  if (s.bar_world) warp_peer_barrier(s.flags, s.bar_rank, s.bar_world, lane, s.status);
 }
 
 // ---------------------------------------------------------------------------------------------
