@@ -80,7 +80,7 @@ DTYPES = {"umma2": "fp8-e4m3 KV fed to tcgen05 as stored; query as two e4m3 term
 def kernel_name(variant: str, per_token: bool = False) -> str:
     """Name of the dominant kernel as a profiler lists it, for the head shape of this run."""
     group = H_Q // H_KV
-    return {"simt": f"attn_splitk_simt_kernel<{D},{group}>", "mma": f"attn_streamk_mma_kernel<{D}>",
+    return {"simt": f"attn_splitk_simt_kernel<{D},{group}>", "mma": f"attn_streamk_mma_kernel<{D}, *>",
             "umma2": f"attn_streamk_umma2_kernel<{D}, {'true' if per_token else 'false'}, {5 if group <= 5 else 8}>"}[variant]
 
 
@@ -123,7 +123,7 @@ def make_config(key: str, world: int) -> dict:
           f"{L2_FREE_COPIES} cache copies is reported beside it where measured")
     return {"workload": workload_name(key), "sharding": sharding, "l2": l2,
             "execution": "one CUDA-graph replay per step: quantize-append + split-K attention + combine"
-                         + (" + output all-gather and cross-GPU barrier" if world > 1 and key != "cfg4" else "")}
+                         + (" + output all-gather over NVLink, in the same launch" if world > 1 and key != "cfg4" else "")}
 
 
 class ClockSampler:
@@ -239,7 +239,7 @@ class StepRunner:
     rank's sequences, all heads, no exchange."""
 
     def __init__(self, pkg, torch, device, depths, cap, advance, h_q, h_kv, seed, dist=None, world=1, variant="auto",
-                 num_splits=0, gather="peer", scale_mode="per_head", tensor_parallel=True):
+                 num_splits=0, gather="packets", scale_mode="per_head", tensor_parallel=True):
         self.pkg, self.torch, self.device, self.depths, self.advance = pkg, torch, device, list(depths), advance
         self.h_q, self.h_kv, self.dist, self.world, self.cap = h_q, h_kv, dist, world, cap
         batch = len(self.depths)
@@ -264,8 +264,8 @@ class StepRunner:
         distmod = importlib.import_module("qwen38-5080_b200.dist")
         self.peer = None
         self.gatherer = None
-        if world > 1 and tensor_parallel and gather == "peer":
-            self.peer = distmod.PeerOutput(self.out, world, dist.get_rank())
+        if world > 1 and tensor_parallel and gather in ("packets", "stores"):
+            self.peer = distmod.PeerOutput(self.out, world, dist.get_rank(), mode=gather)
         elif world > 1 and tensor_parallel:
             self.gatherer = distmod.HeadGather(self.out, world)
         self.graph = None
@@ -274,7 +274,8 @@ class StepRunner:
     def launch_step(self):
         c = self.cache
         if self.peer is not None:
-            # one launch: append + attention storing into every rank's gathered buffer + position bump + cross-GPU barrier
+            # one launch: append + attention sending its results to every rank's gathered tensor + position bump
+            # (+ cross-GPU barrier in the stores mode; the packet mode needs none)
             self.pkg.append_decode(self.q, self.k_new, self.v_new, c.k_cache, c.v_cache, c.k_scale, c.v_scale, c.seq_pos,
                                    workspace=c.workspace, advance=self.advance, peer_out=self.peer, barrier=True)
             return
@@ -337,7 +338,7 @@ class StepRunner:
             return 1                         # the fused step: append, attention, combine, position bump (and barrier) in one launch
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump
         n += 1 if self.cache.workspace.resolved == "simt" and self.cache.workspace.num_splits > 1 else 0
-        return n + (1 if self.peer is not None else 0)
+        return n + (1 if self.peer is not None and self.peer.needs_barrier else 0)
 
 
 def barrier(dist, world):
@@ -440,11 +441,12 @@ def timed_e2e(torch, dist, world, runner, steps, warmup) -> tuple[float, int, in
     from its gathered buffer (together the ranks read the whole result once; the gathered tensor itself
     stays on the device, where its consumer is).  The copies and the step are captured into one CUDA
     graph (memcpy nodes + the library's launch), as a host that replays its decode step would do; two
-    steps per graph, because the tensor-parallel step alternates between two gathered buffers."""
+    steps per graph, because the stores mode of the tensor-parallel step alternates between two gathered buffers."""
     hq, hk, hv = (t.cpu().pin_memory() for t in (runner.q, runner.k_new, runner.v_new))
     if runner.peer is not None:
-        rank, hq_loc = runner.peer.rank, runner.h_q
-        sources = [runner.peer.buffers[(runner.peer.steps_done() + 1 + i) & 1][:, :, rank * hq_loc:(rank + 1) * hq_loc] for i in range(2)]
+        rank, hq_loc, peer = runner.peer.rank, runner.h_q, runner.peer
+        tensors = [peer.full, peer.full] if peer.mode == "packets" else [peer.buffers[(peer.steps_done() + 1 + i) & 1] for i in range(2)]
+        sources = [t[:, :, rank * hq_loc:(rank + 1) * hq_loc] for t in tensors]
     else:
         sources = [runner.result()] * 2
     hout = torch.empty(sources[0].shape, dtype=sources[0].dtype).pin_memory()
@@ -658,7 +660,7 @@ def run_ours(args) -> int:
         if runner.cache.workspace.read_status():
             raise SystemExit(f"device status {runner.cache.workspace.read_status()} after {key}")
         waits = None
-        if runner.peer is not None:     # how long each rank's last arrive-and-wait took (device time stamps)
+        if runner.peer is not None and runner.peer.mode == "stores":     # how long each rank's last arrive-and-wait took (device time stamps)
             w = torch.tensor([runner.peer.last_wait_us()], device=device, dtype=torch.float64)
             allw = [torch.empty_like(w) for _ in range(world)]
             dist.all_gather(allw, w)
@@ -766,8 +768,9 @@ def main() -> int:
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cfg4"], default="cfg2")
     ap.add_argument("--only", action="store_true", help="measure only the headline workload")
     ap.add_argument("--variant", choices=["auto", "mma", "umma2", "simt"], default="auto", help="attention kernel variant")
-    ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
-                    help="N > 1: fused peer-store all-gather (default) or NCCL all-gather + reorder copy")
+    ap.add_argument("--gather", choices=["packets", "stores", "nccl"], default="packets",
+                    help="N > 1: all-gather fused into the kernel as 8-byte value+step packets (default), as plain peer stores "
+                         "followed by a cross-GPU barrier, or NCCL all-gather + reorder copy after the kernel")
     ap.add_argument("--scales", choices=["per_head", "per_token"], default="per_head",
                     help="scale granularity of the FP8 cache (per_token = the reference's frozen [capacity, kv_heads] layout)")
     ap.add_argument("--heads", default="", help="H_q,H_kv,head_dim instead of the metric's 40,8,128 (e.g. 24,4,256: the "

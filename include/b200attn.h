@@ -86,30 +86,48 @@ typedef struct B200AttnShape {
 
 /*
  * Output placement for KV-head tensor parallelism (no counterpart in the reference, which is
- * single-GPU): rank `rank` of `n_peers` computes h_q of the h_q_total query heads; instead of a
- * local output followed by an all-gather, the attention kernel stores every result directly into
- * the gathered tensor bf16 [n_layers][batch][h_q_total][head_dim] of ALL ranks (plain peer stores
- * over NVLink into symmetric / peer-mapped memory), at head offset rank*h_q.  out[r] is rank r's
- * buffer as addressable from this GPU.  b200attn_peer_barrier then makes the stores visible.
+ * single-GPU): rank `rank` of `n_peers` computes h_q of the h_q_total query heads, and the
+ * all-gather of the per-head outputs into bf16 [n_layers][batch][h_q_total][head_dim] on every rank
+ * is done by the attention kernel itself, over NVLink peer memory (symmetric / peer-mapped buffers;
+ * plain stores and loads only).  Three ways, `mode`:
  *
- * Double buffering (n_buffers = 2): a fast rank may begin its next step while a slow rank's consumer
- * still reads the gathered tensor of this one, so every rank holds two gathered tensors and the steps
- * use them in turn.  Which one a launch writes is decided on the device, from the step counter that
- * the cross-GPU barrier keeps (word [n_peers] of this rank's flag buffer, see b200attn_peer_barrier):
- * the launch that finds e there writes out[] when e + 1 is even and out_alt[] when it is odd, and the
- * barrier that follows makes the counter e + 1.  A replayed CUDA graph therefore alternates by
- * itself, a consumer on the device reads the same word, and the host finds the tensor of the latest
- * completed step at parity (counter & 1).  Every step must be followed by exactly one barrier.
+ * B200ATTN_GATHER_PACKETS — the fast one.  Every result leaves as an 8-byte packet {two bf16 values,
+ *   step number} stored into the receiving rank's staging buffer, and at its end every CTA of a launch
+ *   copies a share of the packets that arrived for this rank into this rank's own gathered tensor
+ *   out[rank], waiting for each packet's step number.  Value and number travel in one store, so there
+ *   is no fence, no flag and no barrier: when the launch is complete the gathered tensor is, and a
+ *   rank that is a step ahead only ever writes staging, never a tensor a consumer may still be
+ *   reading.  staging[r] is rank r's staging buffer as addressable from this GPU
+ *   (b200attn_peer_staging_bytes() bytes each, zero-initialised); `step` is one int32 of this rank's
+ *   device memory, zero at the start, advanced by every launch (all ranks must make the same calls in
+ *   the same order).  The waits are bounded (1 s, B200ATTN_STATUS_WAIT_TIMEOUT).
+ * B200ATTN_GATHER_STORES — every result is stored directly into every rank's gathered tensor out[r]
+ *   at head offset rank*h_q; b200attn_peer_barrier (or the barrier_flags of
+ *   b200attn_append_decode_peers) then makes the stores visible.  A tensor must not be rewritten by a
+ *   later step while a slower rank still reads it.
+ * B200ATTN_GATHER_STORES_2BUF — the same with two gathered tensors per rank used in turn, so that a
+ *   fast rank's next step cannot touch what a slow rank's consumer still reads.  Which one a launch
+ *   writes is decided on the device from the step counter the cross-GPU barrier keeps (`step` = word
+ *   [n_peers] of this rank's flag buffer, see b200attn_peer_barrier): the launch that finds e there
+ *   writes out[] when e + 1 is even and out_alt[] when it is odd, and the barrier that follows makes
+ *   the counter e + 1.  Every step must be followed by exactly one barrier.
  */
+#define B200ATTN_GATHER_STORES       1   /* 0 means the same */
+#define B200ATTN_GATHER_STORES_2BUF  2
+#define B200ATTN_GATHER_PACKETS      3
 typedef struct B200AttnPeerOut {
   int n_peers;       /* 1..8 */
   int rank;          /* this rank */
   int h_q_total;     /* = n_peers * shape->h_q */
-  int n_buffers;     /* 0 or 1: out[] only; 2: out[] and out_alt[] in turn */
-  void* out[8];
-  void* out_alt[8];  /* n_buffers == 2: every rank's second gathered tensor */
-  const int* epoch;  /* n_buffers == 2: this rank's step counter, flags[rank] + n_peers (device memory) */
+  int mode;          /* B200ATTN_GATHER_* */
+  void* out[8];      /* gathered tensors; PACKETS reads out[rank] only */
+  void* out_alt[8];  /* STORES_2BUF: every rank's second gathered tensor */
+  void* staging[8];  /* PACKETS: every rank's staging buffer */
+  int* step;         /* STORES_2BUF, PACKETS: this rank's step counter (device memory) */
 } B200AttnPeerOut;
+
+/* Bytes of one rank's staging buffer for B200ATTN_GATHER_PACKETS (shape = the per-rank shape). */
+size_t b200attn_peer_staging_bytes(const B200AttnShape* shape, int n_peers);
 
 /* Library version (B200ATTN_VERSION of the build). */
 int b200attn_version(void);
@@ -235,9 +253,9 @@ int b200attn_decode_gated(const B200AttnShape* shape,
 
 /*
  * b200attn_decode whose output all-gather is fused into the kernel (see B200AttnPeerOut).
- * Tensor-core variants only.  Follow it, on the same stream, with b200attn_peer_barrier before
- * anything reads the gathered tensor; a buffer must not be rewritten by a later step while a
- * slower rank may still be reading it (alternate two buffers, or add a second barrier).
+ * Tensor-core variants only.  In packet mode the gathered tensor is complete when the call is; in
+ * the stores modes follow it, on the same stream, with b200attn_peer_barrier before anything reads
+ * the gathered tensor.
  */
 int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* peers,
                           const void* q_bf16,
@@ -253,11 +271,12 @@ int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* pee
  * The decode step of b200attn_append_decode with the gathered output of b200attn_decode_peers:
  * append this rank's new K/V rows, attend seq_pos[b]+1 tokens, store the results into every
  * rank's gathered buffer, advance seq_pos if advance_pos.  One launch with the stream-K
- * kernels, three otherwise.  With barrier_flags == NULL, follow it with
- * b200attn_peer_barrier as for b200attn_decode_peers.  With barrier_flags (the flag buffers
+ * kernels, three otherwise.  Packet mode: barrier_flags must be NULL, the launch itself waits for
+ * the other ranks' packets.  Stores modes: with barrier_flags == NULL, follow it with
+ * b200attn_peer_barrier as for b200attn_decode_peers; with barrier_flags (the flag buffers
  * b200attn_peer_barrier takes) the cross-GPU arrive-and-wait is part of the call: done by the
  * last CTA of the attention launch with the stream-K kernels, by the barrier kernel launched
- * behind the attention otherwise; same bounded wait and status bit.  (Both stream-K kernels do it inside the launch.)
+ * behind the attention otherwise; same bounded wait and status bit.
  * (The reference has no multi-GPU path: no counterpart there.)
  */
 int b200attn_append_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* peers,

@@ -21,6 +21,7 @@ STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEG
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA2 = 0, 1, 2, 4
 VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma2": VARIANT_UMMA2}
 SCALE_PER_HEAD, SCALE_PER_TOKEN = 0, 1
+GATHER_STORES, GATHER_STORES_2BUF, GATHER_PACKETS = 1, 2, 3
 
 
 class B200AttnShape(ctypes.Structure):
@@ -32,8 +33,8 @@ class B200AttnShape(ctypes.Structure):
 
 
 class B200AttnPeerOut(ctypes.Structure):
-    _fields_ = [("n_peers", c_int), ("rank", c_int), ("h_q_total", c_int), ("n_buffers", c_int),
-                ("out", c_void_p * 8), ("out_alt", c_void_p * 8), ("epoch", c_void_p)]
+    _fields_ = [("n_peers", c_int), ("rank", c_int), ("h_q_total", c_int), ("mode", c_int),
+                ("out", c_void_p * 8), ("out_alt", c_void_p * 8), ("staging", c_void_p * 8), ("step", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/b200attn.h declares
@@ -59,6 +60,7 @@ PROTOTYPES = {
     "b200attn_decode_peers": (c_int, [ctypes.POINTER(B200AttnShape), ctypes.POINTER(B200AttnPeerOut), c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p,
                                       c_size_t, c_void_p, c_void_p]),
+    "b200attn_peer_staging_bytes": (c_size_t, [ctypes.POINTER(B200AttnShape), c_int]),
     "b200attn_peer_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),
     "b200attn_decode_static": (c_int, [ctypes.POINTER(B200AttnShape), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),

@@ -12,19 +12,6 @@ thread_local int g_last_cuda_error = 0;
 
 int cuda_fail(cudaError_t e) { return b200attn::record_cuda_error(e); }
 
-// SMs of the current device (cached per device); 148, a B200, when no device can be asked (the
-// pure host helpers also run where there is no GPU).
-int device_sms() {
-  static std::atomic<int> cache[64];
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return 148; }
-  int n = cache[dev].load(std::memory_order_relaxed);
-  if (n > 0) return n;
-  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) { (void)cudaGetLastError(); return 148; }
-  cache[dev].store(n, std::memory_order_relaxed);
-  return n;
-}
-
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Validate the shape and resolve strides.  Returns 0 or a B200ATTN_ERR_* code.
@@ -76,18 +63,29 @@ int resolve_variant(int variant, const Geometry& g) {
 int check_peers(const B200AttnPeerOut* peers, const Geometry& g) {
   if (peers->n_peers < 1 || peers->n_peers > 8 || peers->rank < 0 || peers->rank >= peers->n_peers) return B200ATTN_ERR_SHAPE;
   if (peers->h_q_total != g.h_q * peers->n_peers) return B200ATTN_ERR_SHAPE;
-  if (peers->n_buffers < 0 || peers->n_buffers > 2) return B200ATTN_ERR_SHAPE;
+  if (peers->mode < 0 || peers->mode > B200ATTN_GATHER_PACKETS) return B200ATTN_ERR_SHAPE;
+  if (peers->mode == B200ATTN_GATHER_PACKETS) {
+    if (!peers->out[peers->rank] || !peers->step) return B200ATTN_ERR_NULL;
+    if (!aligned16(peers->out[peers->rank])) return B200ATTN_ERR_ALIGN;
+    for (int r = 0; r < peers->n_peers; ++r) {
+      if (!peers->staging[r]) return B200ATTN_ERR_NULL;
+      if (!aligned16(peers->staging[r])) return B200ATTN_ERR_ALIGN;
+    }
+    return B200ATTN_OK;
+  }
   for (int r = 0; r < peers->n_peers; ++r) {
     if (!peers->out[r]) return B200ATTN_ERR_NULL;
     if (!aligned16(peers->out[r])) return B200ATTN_ERR_ALIGN;
-    if (peers->n_buffers == 2) {
+    if (peers->mode == B200ATTN_GATHER_STORES_2BUF) {
       if (!peers->out_alt[r]) return B200ATTN_ERR_NULL;
       if (!aligned16(peers->out_alt[r])) return B200ATTN_ERR_ALIGN;
     }
   }
-  if (peers->n_buffers == 2 && !peers->epoch) return B200ATTN_ERR_NULL;
+  if (peers->mode == B200ATTN_GATHER_STORES_2BUF && !peers->step) return B200ATTN_ERR_NULL;
   return B200ATTN_OK;
 }
+
+size_t staging_slot_bytes(const Geometry& g) { return (size_t)g.n_layers * g.batch * g.h_q * g.head_dim / 2 * 8; }
 
 int pick(const Geometry& g, int v, int max_seq_len, int num_sms) {
   if (v == B200ATTN_VARIANT_SIMT) return simt_pick_splits(g, max_seq_len, num_sms);
@@ -96,6 +94,19 @@ int pick(const Geometry& g, int v, int max_seq_len, int num_sms) {
 }
 
 }  // namespace
+
+// SMs of the current device (cached per device); 148, a B200, when no device can be asked (the
+// pure host helpers also run where there is no GPU).
+int b200attn::device_sms() {
+  static std::atomic<int> cache[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return 148; }
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) { (void)cudaGetLastError(); return 148; }
+  cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
 
 namespace b200attn {
 int record_cuda_error(cudaError_t e) {
@@ -264,11 +275,26 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
     a.out_head_base = peers->rank * g.h_q;
     rc = check_peers(peers, g);
     if (rc) return rc;
-    for (int r = 0; r < peers->n_peers; ++r) {
-      a.out_peer[r] = peers->out[r];
-      a.out_peer_alt[r] = peers->n_buffers == 2 ? peers->out_alt[r] : peers->out[r];
+    if (peers->mode == B200ATTN_GATHER_PACKETS) {
+      // this rank's slots in the other ranks' staging buffers ([2 parities][n_peers slots][slot]), its own staging
+      // buffer to unpack from, its own gathered tensor
+      if (fused && fused->barrier_flags) return B200ATTN_ERR_SHAPE;   // packets need no barrier and must not be mixed with one
+      const size_t slot = staging_slot_bytes(g);
+      for (int r = 0; r < peers->n_peers; ++r) {
+        char* base = r == peers->rank ? nullptr : (char*)peers->staging[r] + (size_t)peers->rank * slot;
+        a.out_peer[r] = base;
+        a.out_peer_alt[r] = base ? base + (size_t)peers->n_peers * slot : nullptr;
+      }
+      a.pkt_src = peers->staging[peers->rank];
+      a.out = peers->out[peers->rank];
+      a.epoch = peers->step;
+    } else {
+      for (int r = 0; r < peers->n_peers; ++r) {
+        a.out_peer[r] = peers->out[r];
+        a.out_peer_alt[r] = peers->mode == B200ATTN_GATHER_STORES_2BUF ? peers->out_alt[r] : peers->out[r];
+      }
+      a.epoch = peers->mode == B200ATTN_GATHER_STORES_2BUF ? peers->step : nullptr;
     }
-    a.epoch = peers->n_buffers == 2 ? peers->epoch : nullptr;
   }
   cudaError_t e = v == B200ATTN_VARIANT_SIMT ? launch_decode_simt(g, a, (cudaStream_t)stream)
                                              : v == B200ATTN_VARIANT_UMMA2 ? launch_decode_umma2(g, a, (cudaStream_t)stream)
@@ -300,6 +326,12 @@ int b200attn_decode_peers(const B200AttnShape* shape, const B200AttnPeerOut* pee
   if (!peers) return B200ATTN_ERR_NULL;
   return decode_impl(shape, peers, q, nullptr, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                      variant, num_splits, workspace, workspace_bytes, nullptr, status, stream);
+}
+
+size_t b200attn_peer_staging_bytes(const B200AttnShape* shape, int n_peers) {
+  Geometry g;
+  if (resolve(shape, &g) || n_peers < 1 || n_peers > 8) return 0;
+  return 2 * (size_t)n_peers * staging_slot_bytes(g);
 }
 
 int b200attn_peer_barrier(void* const* flags, int rank, int world, int* status, void* stream) {

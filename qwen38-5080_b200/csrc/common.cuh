@@ -66,6 +66,9 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
   return __uint_as_float(bits16 << 16);
 }
 
+// SMs of the current device (cached per device); 148, a B200, when no device can be asked.
+int device_sms();
+
 // Remember a failed CUDA call for b200attn_last_cuda_error() on this thread; returns B200ATTN_ERR_CUDA.
 int record_cuda_error(cudaError_t e);
 
@@ -114,7 +117,9 @@ struct DecodeArgs {
   int out_hq_total, out_head_base;
   void* out_peer[8];
   void* out_peer_alt[8] = {};    // double-buffered gathered output: the second tensor of every rank
-  const int* epoch = nullptr;    // and the step counter whose parity picks the tensor (null = out_peer always)
+  int* epoch = nullptr;          // and the step counter whose parity picks the tensor (null = out_peer always)
+  const void* pkt_src = nullptr; // packet mode: this rank's staging buffer; out_peer / out_peer_alt are then this rank's slots
+                                 // in the other ranks' staging buffers for even / odd steps, `out` its own gathered tensor
   // fused step (all-tcgen05 variant only): the new token of every pair is quantised into the cache by
   // the CTA that owns the pair's last tile, and the last CTA to finish advances the positions
   const void* k_new = nullptr;   // bf16 [n_layers][batch][h_kv][1][head_dim]; null = attention only

@@ -87,8 +87,11 @@ __device__ __noinline__ void append_rows_by_warp(int batch, int h_kv, int capaci
   __syncwarp();
 }
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, D == 128 ? kCtasPerSm : 1)
+// MINB: CTAs per SM the instance is compiled for.  Three (96 registers, ~100 B of spills in the consumer loop) is
+// the long-cache configuration; the instance for two has 168 registers to work with and serves the small grids of
+// short caches, where nothing is gained from a third CTA per SM and the consumer chain's latency is what counts.
+template <int D, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
 attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                         const MmaParams p) {
   constexpr int DH = D / 128;              // 128-byte column blocks per row
@@ -162,12 +165,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
-        for (int i = tid; i < g.h_q * D; i += kThreads) {
-          if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
-          else
-            for (int pr = 0; pr < p.n_out; ++pr)
-              p.out_peer[peer_buffer_base(p) + pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
-        }
+        for (int i = 2 * tid; i < g.h_q * D; i += 2 * kThreads)
+          emit_bits(p, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
     }
   }
 
@@ -445,10 +444,11 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       while (!mbar_try_wait(qfull0 + 8u * qb, (last_seg >> 1) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
     }
   }
-  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(step_end_of(p), lane);
+  end_of_launch(p, tid, kThreads);
 }
 
-int stages_for(const Geometry& g) { return 3; }
+constexpr int kStages = 3;   // ring depth.  A deeper ring where a small grid leaves shared memory unused (short caches, up to
+                             // 12 stages at one CTA per SM) changed nothing: there the consumer chain is the limit, not the copies
 
 size_t smem_bytes_for(const Geometry& g, int stages) {
   size_t b = 1024;                                            // alignment slack
@@ -472,13 +472,24 @@ size_t mma_workspace_bytes(const Geometry& g, int num_ctas) {
   return (b + 255) & ~(size_t)255;
 }
 
+// The persistent grid: every CTA slot of the device.  Exception, short caches (at most kAlignMaxTiles tiles per
+// pair at the given length): the kernel gives every CTA whole pairs (cta_range), and CTAs beyond the ones that
+// get work only cost launch time (depth 512, 512 pairs: 444 CTAs 21.6 us, 256 CTAs 20.0 us; splitting the pairs
+// of a small shard over more CTAs is slower than one pair per CTA: 128 pairs on 128 / 256 / 384 CTAs 11.8 / 15.4 /
+// 17.0 us): the grid is the smallest one that gives every CTA the same number of pairs.
 int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
-  (void)max_seq_len;
-  const size_t smem = smem_bytes_for(g, stages_for(g));
+  const size_t smem = smem_bytes_for(g, kStages);
   int per_sm = (int)((227 * 1024) / (smem + 1024));   // + per-CTA reservation
   if (per_sm < 1) per_sm = 1;
   if (per_sm > kCtasPerSm) per_sm = kCtasPerSm;
-  return num_sms * per_sm;
+  const int full = num_sms * per_sm;
+  const long long pairs = (long long)g.n_layers * g.batch * g.h_kv;
+  const int tiles = (max_seq_len + kTileT - 1) / kTileT;
+  if (tiles >= 1 && tiles <= kAlignMaxTiles) {
+    const long long k = (pairs + full - 1) / full;
+    return (int)((pairs + k - 1) / k);
+  }
+  return full;
 }
 
 cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream_t stream) {
@@ -506,8 +517,11 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
   for (int r = 0; r < 8; ++r) p.out_peer[8 + r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
   p.epoch = a.n_out ? a.epoch : nullptr;
+  p.pkt = a.n_out && a.pkt_src ? 1 : 0;
+  p.pkt_src = (const unsigned long long*)a.pkt_src;
+  p.pkt_slot_words = (long long)g.n_layers * g.batch * g.h_q * g.head_dim / 2;
   p.status = a.status;
-  p.stages = stages_for(g);
+  p.stages = kStages;
   p.k_new = (const uint16_t*)a.k_new;
   p.v_new = (const uint16_t*)a.v_new;
   p.k_cache_w = (uint8_t*)a.k_cache;
@@ -521,10 +535,17 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   auto launch = [&](auto kernel) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
+    if (p.pkt) {   // may every CTA wait for remote packets?  only if the whole grid is resident at once
+      int per_sm = 0;
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem);
+      if (e != cudaSuccess) return e;
+      p.pkt_resident = (long long)per_sm * device_sms() >= n ? 1 : 0;
+    }
     kernel<<<n, kThreads, smem, stream>>>(kmap, vmap, p);
     return cudaGetLastError();
   };
-  return g.head_dim == 128 ? launch(attn_streamk_mma_kernel<128>) : launch(attn_streamk_mma_kernel<256>);
+  if (g.head_dim != 128) return launch(attn_streamk_mma_kernel<256, 1>);
+  return n <= 2 * device_sms() ? launch(attn_streamk_mma_kernel<128, 2>) : launch(attn_streamk_mma_kernel<128, kCtasPerSm>);
 }
 
 }  // namespace b200attn

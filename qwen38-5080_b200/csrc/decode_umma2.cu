@@ -251,12 +251,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
-        for (int i = tid; i < g.h_q * D; i += kThreads2) {
-          if (p.n_out == 0) p.out[r * g.h_q * D + i] = 0;
-          else
-            for (int pr = 0; pr < p.n_out; ++pr)
-              p.out_peer[peer_buffer_base(p) + pr][(r * p.out_hq_total + p.out_head_base) * D + i] = 0;
-        }
+        for (int i = 2 * tid; i < g.h_q * D; i += 2 * kThreads2)
+          emit_bits(p, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
     }
   }
 
@@ -691,7 +687,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if ((p.seq_pos || p.bar_world) && warp == 0) finish_step(step_end_of(p), lane);
+  end_of_launch(p, tid, kThreads2);
 }
 
 // Ring depths: all of the shared memory that the fixed part leaves, at most 4 K and 8 V tiles.
@@ -751,6 +747,9 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   for (int r = 0; r < 8; ++r) p.out_peer[r] = r < a.n_out ? (uint16_t*)a.out_peer[r] : nullptr;
   for (int r = 0; r < 8; ++r) p.out_peer[8 + r] = r < a.n_out ? (uint16_t*)a.out_peer_alt[r] : nullptr;
   p.epoch = a.n_out ? a.epoch : nullptr;
+  p.pkt = a.n_out && a.pkt_src ? 1 : 0;
+  p.pkt_src = (const unsigned long long*)a.pkt_src;
+  p.pkt_slot_words = (long long)g.n_layers * g.batch * g.h_q * g.head_dim / 2;
   p.status = a.status;
   p.k_new = (const uint16_t*)a.k_new;
   p.v_new = (const uint16_t*)a.v_new;
@@ -767,6 +766,12 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   auto launch = [&](auto kernel) -> cudaError_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.bytes);
     if (e != cudaSuccess) return e;
+    if (p.pkt) {   // may every CTA wait for remote packets?  only if the whole grid is resident at once
+      int per_sm = 0;
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads2, pl.bytes);
+      if (e != cudaSuccess) return e;
+      p.pkt_resident = (long long)per_sm * device_sms() >= n ? 1 : 0;
+    }
     kernel<<<n, kThreads2, pl.bytes, stream>>>(kmap, vmap, p);
     return cudaGetLastError();
   };

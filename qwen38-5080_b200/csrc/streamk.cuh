@@ -33,10 +33,20 @@ struct MmaParams {
   // peer mode (tensor-parallel by KV head): every result is stored into the output buffer of all
   // n_out ranks, laid out [n_layers][batch][out_hq_total][D], at head offset out_head_base
   uint16_t* out_peer[16];      // [0..8): every rank's gathered tensor; [8..16): every rank's second one (double buffering)
-  const int* epoch;            // this rank's step counter (the barrier's own-epoch word): the launch that finds e there
-                               // writes tensors [0..8) when e + 1 is even, [8..16) when it is odd; null = [0..8) always
+  int* epoch;                  // this rank's step counter: the launch that finds e there is step e + 1 and uses table entries
+                               // [0..8) when e + 1 is even, [8..16) when it is odd; null = [0..8) always.  (Stores mode: the
+                               // barrier's own-epoch word, advanced by the barrier.  Packet mode: advanced by the launch.)
   int n_out;             // 0 = local output only
   int out_hq_total, out_head_base;
+  // packet mode (pkt != 0): results travel to the other ranks as 8-byte packets {two bf16 values, step number} into
+  // their staging buffers: out_peer[r] / out_peer[8 + r] are this rank's slots there for even / odd steps (null for
+  // the own rank), `out` is this rank's own gathered tensor; at its end every CTA unpacks a share of what the other
+  // ranks sent here (pkt_src: own staging, [2 parities][n_out slots][pkt_slot_words]), waiting for each packet's step
+  // number — that wait is all the cross-GPU synchronisation there is: no fence, no flag, no barrier
+  int pkt;
+  int pkt_resident;            // the whole grid is resident at once: every CTA may wait for remote packets (see unpack_packets)
+  const unsigned long long* pkt_src;
+  long long pkt_slot_words;
   const uint16_t* gate;  // optional bf16 [n_layers][batch][h_q][D]: out *= sigmoid(gate), see store_out
   int* status;
   int stages;            // ring depth (the V ring where K and V have their own)
@@ -232,23 +242,34 @@ __device__ __forceinline__ int owner_of(long long x, long long total, int n) {
 
 // Tile range [r0, r1) of CTA `cta`.  Default: the even stream-K split of `total` tiles over n_eff
 // CTAs.  Short sequences are the exception: when every pair has the same small number of tiles
-// (`pair_tiles` <= kAlignMaxTiles, i.e. depth <= 1024 with 64-token tiles) and there are enough pairs
-// to occupy at least half the grid, boundaries are rounded to whole pairs.  A split pair costs its
-// two owners a partial write, an arrival ticket and a combine (~4 us on the epilogue warp), more than
-// the few tiles of imbalance it saves; with whole pairs no partial ever exists.
+// (`pair_tiles` <= kAlignMaxTiles, i.e. depth <= 1024 with 64-token tiles), a split pair costs its
+// owners a partial write, an arrival ticket and a combine (~4 us on the epilogue warp), more than the
+// few tiles of imbalance it saves.  So
+//   * with more than half as many pairs as CTAs, every CTA takes whole pairs, and only as many CTAs work as
+//     it takes to give each the same number k = ceil(pairs / grid) of them (512 pairs on a grid of 444:
+//     256 CTAs with two pairs each, 20.0 us, against 444 CTAs of which 68 have two, 21.6 us);
+//   * with fewer pairs (few KV heads per GPU), every pair is cut into the same number of equal pieces, one
+//     piece per CTA, as many as the grid has room for: n_eff = pairs * pieces, so the even split below puts
+//     its boundaries on the pairs by itself.  The host chooses the grid for that (mma_pick_ctas).
 constexpr int kAlignMaxTiles = 16;
 __device__ __forceinline__ void cta_range(long long total, int grid, int cta, int pair_tiles,
                                           int& n_eff, long long& r0, long long& r1) {
   n_eff = (int)(total < (long long)grid ? total : (long long)grid);
   r0 = r1 = 0;
-  if (pair_tiles > 0 && pair_tiles <= kAlignMaxTiles && total / pair_tiles >= (long long)(grid / 2)) {
+  if (pair_tiles > 0 && pair_tiles <= kAlignMaxTiles) {
     const long long pairs = total / pair_tiles;
-    n_eff = (int)(pairs < (long long)grid ? pairs : (long long)grid);
-    if (cta < n_eff) {
-      r0 = ((long long)cta * pairs / n_eff) * pair_tiles;
-      r1 = (((long long)cta + 1) * pairs / n_eff) * pair_tiles;
+    if (2 * pairs > (long long)grid) {
+      const long long k = (pairs + grid - 1) / grid;
+      n_eff = (int)((pairs + k - 1) / k);
+      if (cta < n_eff) {
+        r0 = ((long long)cta * pairs / n_eff) * pair_tiles;
+        r1 = (((long long)cta + 1) * pairs / n_eff) * pair_tiles;
+      }
+      return;
     }
-    return;
+    long long pieces = (long long)grid / pairs;
+    if (pieces > pair_tiles) pieces = pair_tiles;
+    n_eff = (int)(pairs * pieces);
   }
   if (cta < n_eff) {
     r0 = (long long)cta * total / n_eff;
@@ -260,17 +281,41 @@ __device__ __forceinline__ void cta_range(long long total, int grid, int cta, in
 // consumer fragments (dims 16*gq + 2*j per lane) over all banks; it permutes within groups of 8.
 __device__ __forceinline__ int dump_pos(int u) { return (u & ~7) | ((u & 7) ^ ((u >> 3) & 7)); }
 
-// Which of the two gathered tensors this launch writes (see MmaParams::epoch): first index into out_peer.
-__device__ __forceinline__ int peer_buffer_base(const MmaParams& p) {
-  return p.epoch != nullptr && ((*reinterpret_cast<const volatile int*>(p.epoch) + 1) & 1) != 0 ? 8 : 0;
+// The number of the step this launch is (see MmaParams::epoch), and the half of out_peer it uses.
+__device__ __forceinline__ int peer_step(const MmaParams& p) {
+  return p.epoch != nullptr ? *reinterpret_cast<const volatile int*>(p.epoch) + 1 : 0;
+}
+__device__ __forceinline__ int peer_buffer_base(int step) { return (step & 1) ? 8 : 0; }
+
+// One pair of adjacent bf16 outputs on its way: `idx` is its element index in this rank's [n_layers][batch][h_q][D]
+// layout, `peer_idx` in the gathered [n_layers][batch][out_hq_total][D] layout.
+__device__ __forceinline__ void emit_bits(const MmaParams& p, int step, long long idx, long long peer_idx, uint32_t bits) {
+  if (p.n_out == 0) {
+    *reinterpret_cast<uint32_t*>(p.out + idx) = bits;
+  } else if (p.pkt) {
+    *reinterpret_cast<uint32_t*>(p.out + peer_idx) = bits;   // this rank's rows of its own gathered tensor
+    const unsigned long long w = (unsigned long long)bits | ((unsigned long long)(uint32_t)step << 32);
+    const int base = peer_buffer_base(step);
+    // one 8-byte store per rank: value and step number arrive together or not at all (rolled loops: this code is
+    // inlined at many places of the epilogue, and the kernels are sensitive to their code size)
+#pragma unroll 1
+    for (int r = 0; r < p.n_out; ++r) {
+      unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.out_peer[base + r]);
+      if (dst) asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst + (idx >> 1)), "l"(w) : "memory");
+    }
+  } else {
+    // the output all-gather as plain stores into every rank's gathered tensor (own one included) over NVLink
+    const int base = peer_buffer_base(step);
+#pragma unroll 1
+    for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint32_t*>(p.out_peer[base + r] + peer_idx) = bits;
+  }
 }
 
 // Two adjacent outputs -> bf16.  With a gate, the consumer-side fusion of the reference's attention
 // block, attn_output * sigmoid(gate), with its two separate bf16 roundings
 // (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150): s = bf16(sigmoid(gate)), then
 // bf16(bf16(attn) * s).
-__device__ __forceinline__ void store_out(const MmaParams& p, int peer_base, long long idx, long long peer_idx, float x, float y) {
-  uint16_t* out = p.out;
+__device__ __forceinline__ void store_out(const MmaParams& p, int step, long long idx, long long peer_idx, float x, float y) {
   const uint16_t* gate = p.gate;
   __nv_bfloat162 ob = __floats2bfloat162_rn(x, y);
   if (gate) {
@@ -279,15 +324,7 @@ __device__ __forceinline__ void store_out(const MmaParams& p, int peer_base, lon
     const __nv_bfloat162 s = __floats2bfloat162_rn(__fdiv_rn(1.f, 1.f + expf(-g0)), __fdiv_rn(1.f, 1.f + expf(-g1)));
     ob = __floats2bfloat162_rn(__low2float(ob) * __low2float(s), __high2float(ob) * __high2float(s));
   }
-  const uint32_t bits = *reinterpret_cast<uint32_t*>(&ob);
-  if (p.n_out == 0) {
-    *reinterpret_cast<uint32_t*>(out + idx) = bits;
-  } else {
-    // the output all-gather, fused: plain stores into every rank's buffer (own one included) over NVLink; a rolled
-    // loop: this code is inlined at many places of the epilogue, and the kernels are sensitive to their code size
-#pragma unroll 1
-    for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint32_t*>(p.out_peer[peer_base + r] + peer_idx) = bits;
-  }
+  emit_bits(p, step, idx, peer_idx, *reinterpret_cast<uint32_t*>(&ob));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -308,7 +345,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
   const Geometry& g = p.g;
   const int G = g.group;
   const int dump_warp_floats = G * DP;
-  const int peer_base = peer_buffer_base(p);
+  const int step = peer_step(p);
 {
   Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
   long long cur = r0;
@@ -352,7 +389,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           const float inv = ll > 0.f ? vs / ll : 0.f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            store_out(p, peer_base, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
+            store_out(p, step, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
           }
         } else {
 #pragma unroll
@@ -423,7 +460,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
             const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
 #pragma unroll
             for (int r = 0; r < UR; ++r) {
-              store_out(p, peer_base, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
+              store_out(p, step, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
             }
           }
         }
@@ -434,9 +471,9 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     cur = seg_end;
     if (cur < r1) next_pair(c, sCum, sLen, g.batch, g.h_kv);
   }
-  // Peer mode: every lane's stores into the other GPUs' buffers are made visible system-wide here, by the warp
+  // Stores mode: every lane's stores into the other GPUs' tensors are made visible system-wide here, by the warp
   // that issued them, so that the fence of the CTA that finishes the launch finds nothing of them outstanding.
-  if (p.n_out) __threadfence_system();
+  if (p.n_out && !p.pkt) __threadfence_system();
 }
 }
 
@@ -486,13 +523,60 @@ struct StepEnd {
   int* status;
   int batch, capacity, bar_rank, bar_world;
   int* flags[8];
+  int* step_counter;   // packet mode: the counter the last CTA advances (null otherwise)
+  int step;
 };
-__device__ __forceinline__ StepEnd step_end_of(const MmaParams& p) {
+__device__ __forceinline__ StepEnd step_end_of(const MmaParams& p, int step) {
   return StepEnd{p.seq_pos, p.exit_count, p.status, p.g.batch, p.g.capacity, p.bar_rank, p.bar_world,
                  {p.bar_flags[0], p.bar_flags[1], p.bar_flags[2], p.bar_flags[3], p.bar_flags[4], p.bar_flags[5], p.bar_flags[6],
-                  p.bar_flags[7]}};
+                  p.bar_flags[7]}, p.pkt ? p.epoch : nullptr, step};
 }
-__device__ __noinline__ void finish_step(StepEnd s, int lane) {
+
+// Packet mode, receiving side.  The other ranks' results arrive in this rank's staging buffer as 8-byte packets
+// {two bf16 values, step number}, slot s = sender s, in the sender's own [n_layers][batch][h_q][D] order.  Share
+// `part` of `parts` of the (n_out - 1) * slot_words packets is copied into this rank's gathered tensor, each packet
+// as soon as its step number is this step's (bounded wait: after kBarrierBudgetNs the status bit is set and the rest
+// is skipped).  Every CTA calls it after its own work (part = its index), so the copy is spread over the grid and
+// runs while slower CTAs and slower ranks are still computing.  That needs the whole grid resident: a CTA waiting
+// here for a rank whose progress depends, through that rank's own waiting CTAs, on CTAs of this grid that have not
+// started yet would wait for ever; a grid larger than the device holds at once is unpacked by the last CTA instead.
+struct Unpack {
+  const unsigned long long* src;   // this rank's staging, already at this step's parity
+  uint16_t* out;                   // this rank's gathered tensor
+  int* status;
+  long long slot_words;
+  int row_words;                   // packets per (layer, sequence) row of one sender: h_q * D / 2
+  long long out_row;               // elements per (layer, sequence) row of the gathered tensor: out_hq_total * D
+  int n_out, rank, step;
+};
+__device__ __forceinline__ Unpack unpack_of(const MmaParams& p, int step) {
+  return Unpack{p.pkt_src + (long long)(step & 1) * p.n_out * p.pkt_slot_words, p.out, p.status, p.pkt_slot_words,
+                p.g.h_q * p.g.head_dim / 2, (long long)p.out_hq_total * p.g.head_dim, p.n_out, p.out_head_base / p.g.h_q, step};
+}
+__device__ __noinline__ void unpack_packets(Unpack u, int part, int parts, int tid, int nthreads) {
+  const long long total = (long long)(u.n_out - 1) * u.slot_words;
+  const long long t0 = (long long)part * total / parts, t1 = ((long long)part + 1) * total / parts;
+  const unsigned long long start = global_timer_ns();
+  for (long long t = t0 + tid; t < t1; t += nthreads) {
+    const int si = (int)(t / u.slot_words);
+    const int s = si < u.rank ? si : si + 1;
+    const long long w = t - (long long)si * u.slot_words;
+    const unsigned long long* src = u.src + (long long)s * u.slot_words + w;
+    unsigned long long v;
+    bool ok = false;
+    for (int tries = 0;; ++tries) {
+      asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(src) : "memory");
+      if ((int)(v >> 32) == u.step) { ok = true; break; }
+      if ((tries & 63) == 63 && global_timer_ns() - start > kBarrierBudgetNs) break;
+    }
+    if (!ok) { atomicOr(u.status, B200ATTN_STATUS_WAIT_TIMEOUT); return; }
+    const long long row = w / u.row_words;
+    const long long rem = w - row * u.row_words;
+    *reinterpret_cast<uint32_t*>(u.out + row * u.out_row + (long long)s * u.row_words * 2 + rem * 2) = (uint32_t)v;
+  }
+}
+
+__device__ __noinline__ void finish_step(StepEnd s, Unpack u, int unpack_all, int lane) {
   int last = 0;
   if (lane == 0) {
     int arrived;
@@ -501,13 +585,32 @@ __device__ __noinline__ void finish_step(StepEnd s, int lane) {
   }
   last = __shfl_sync(0xffffffffu, last, 0);
   if (!last) return;
+  if (unpack_all) {   // a grid that is not resident all at once: everything this rank sent is out, one warp waits for the rest
+    unpack_packets(u, 0, 1, lane, 32);
+    __syncwarp();
+  }
   if (s.seq_pos)
     for (int b = lane; b < s.batch; b += 32) {
       const int pos = s.seq_pos[b];
       if (pos >= 0 && pos + 1 <= s.capacity) s.seq_pos[b] = pos + 1;
     }
-  if (lane == 0) *s.exit_count = 0;   // ready for the next launch
+  if (lane == 0) {
+    *s.exit_count = 0;   // ready for the next launch
+    if (s.step_counter) *s.step_counter = s.step;
+  }
   if (s.bar_world) warp_peer_barrier(s.flags, s.bar_rank, s.bar_world, lane, s.status);
+}
+
+// What every CTA does after its final __syncthreads when the launch is a whole step and / or sends packets.
+__device__ __forceinline__ void end_of_launch(const MmaParams& p, int tid, int nthreads) {
+  if (!(p.seq_pos || p.bar_world || p.pkt)) return;
+  const int step = peer_step(p);   // read before this CTA arrives at the exit counter: the last arrival advances it
+  const bool receive = p.pkt && p.n_out > 1;
+  if (receive && p.pkt_resident) {
+    unpack_packets(unpack_of(p, step), (int)blockIdx.x, (int)gridDim.x, tid, nthreads);
+    __syncthreads();   // this CTA's copies are done before it counts as finished
+  }
+  if (tid < 32) finish_step(step_end_of(p, step), unpack_of(p, step), receive && !p.pkt_resident, tid);
 }
 
 // ---------------------------------------------------------------------------------------------

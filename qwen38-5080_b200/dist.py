@@ -59,24 +59,51 @@ class HeadGather:
 
 
 class PeerOutput:
-    """Gathered outputs [n_layers, batch, h_q_total, D] in symmetric memory — two per rank, used in turn —
-    plus the flag buffer of the cross-GPU barrier.  The attention kernel of every rank stores its heads
-    straight into all ranks' buffers (peer stores over NVLink): the all-gather is fused into the kernel,
-    and the arrive-and-wait (``ops.peer_barrier``, or the end of a fused step) is all that is left of the
-    collective.  Two buffers because a fast rank may start its next step while a slow rank's consumer
-    still reads this step's tensor; which one a step writes follows, on the device, from the parity of the
-    step counter the barrier keeps, so a replayed graph alternates by itself.
-    Allocate once, before any graph capture; every step must be followed by exactly one barrier."""
+    """The gathered output [n_layers, batch, h_q_total, D] of a tensor-parallel step and what the fused
+    all-gather needs around it.  The attention kernel of every rank sends its heads to all ranks over
+    NVLink peer memory (symmetric memory); the all-gather is part of the kernel.
 
-    def __init__(self, local_like: torch.Tensor, world: int, rank: int, group=None):
+    mode "packets" (default): results travel as 8-byte packets {two bf16 values, step number} into the
+    receivers' staging buffers and every launch copies what arrived for it into its own gathered tensor;
+    no fence, no flag, no barrier, one gathered tensor per rank (``current()``), complete when the launch is.
+    mode "stores": results are stored directly into every rank's gathered tensors — two per rank, used in
+    turn, because a fast rank may start its next step while a slow rank's consumer still reads this one's —
+    and a cross-GPU arrive-and-wait follows (``ops.peer_barrier`` or ``barrier=True`` on the step); which
+    tensor a step writes follows, on the device, from the parity of the step counter the barrier keeps.
+
+    Allocate once, before any graph capture; all ranks make the same calls in the same order."""
+
+    def __init__(self, local_like: torch.Tensor, world: int, rank: int, group=None, mode: str = "packets"):
         import ctypes
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
-        from ._lib import B200AttnPeerOut
+        from . import _lib
         group = group if group is not None else dist.group.WORLD
         n, b, hq, d = local_like.shape
         dev = local_like.device
-        self.world, self.rank = world, rank
+        self.world, self.rank, self.mode = world, rank, mode
+        zeros8 = (ctypes.c_void_p * 8)()
+        if mode == "packets":
+            shape = _lib.B200AttnShape(n, b, hq, hq, d, 1, 0, 0, 0, 0)     # only layers, batch, query heads and head_dim count
+            nbytes = _lib.lib().b200attn_peer_staging_bytes(ctypes.byref(shape), world)
+            if nbytes == 0:
+                raise ValueError("unsupported shape for the packet staging buffer")
+            self.full = torch.zeros(n, b, world * hq, d, dtype=local_like.dtype, device=dev)
+            self.staging = symm_mem.empty((nbytes // 8,), dtype=torch.int64, device=dev)
+            self.staging.zero_()
+            self._stage_hdl = symm_mem.rendezvous(self.staging, group)
+            self.step = torch.zeros(1, dtype=torch.int32, device=dev)
+            torch.cuda.synchronize()
+            dist.barrier(group)
+            out = (ctypes.c_void_p * 8)()
+            out[rank] = self.full.data_ptr()
+            self.c_peers = _lib.B200AttnPeerOut(world, rank, world * hq, _lib.GATHER_PACKETS, out, zeros8,
+                                                (ctypes.c_void_p * 8)(*[int(p) for p in self._stage_hdl.buffer_ptrs]),
+                                                self.step.data_ptr())
+            self.c_flags = None
+            return
+        if mode != "stores":
+            raise ValueError("mode must be 'packets' or 'stores'")
         self.buffers = symm_mem.empty((2, n, b, world * hq, d), dtype=local_like.dtype, device=dev)
         self.buffers.zero_()
         self._out_hdl = symm_mem.rendezvous(self.buffers, group)
@@ -88,24 +115,30 @@ class PeerOutput:
         half = self.buffers[0].numel() * self.buffers.element_size()
         bases = [int(p) for p in self._out_hdl.buffer_ptrs]
         flag_ptrs = [int(p) for p in self._flag_hdl.buffer_ptrs]
-        self.c_peers = B200AttnPeerOut(world, rank, world * hq, 2, (ctypes.c_void_p * 8)(*bases),
-                                       (ctypes.c_void_p * 8)(*[p + half for p in bases]), flag_ptrs[rank] + 4 * world)
+        self.c_peers = _lib.B200AttnPeerOut(world, rank, world * hq, _lib.GATHER_STORES_2BUF, (ctypes.c_void_p * 8)(*bases),
+                                            (ctypes.c_void_p * 8)(*[p + half for p in bases]), zeros8, flag_ptrs[rank] + 4 * world)
         self.c_flags = (ctypes.c_void_p * 8)(*flag_ptrs)
 
+    @property
+    def needs_barrier(self) -> bool:
+        return self.mode == "stores"
+
     def steps_done(self) -> int:
-        """The barrier's step counter (synchronises: not for use inside a captured step)."""
-        return int(self.flags[self.world].item())
+        """The step counter (synchronises: not for use inside a captured step)."""
+        return int(self.step.item()) if self.mode == "packets" else int(self.flags[self.world].item())
 
     def current(self) -> torch.Tensor:
-        """The gathered tensor of the latest completed step (synchronises)."""
-        return self.buffers[self.steps_done() & 1]
+        """The gathered tensor of the latest completed step (stores mode: synchronises)."""
+        return self.full if self.mode == "packets" else self.buffers[self.steps_done() & 1]
 
     def poison_next(self) -> None:
         """Fill the tensor the next step is going to write with NaN (for tests: a step must overwrite all of it)."""
-        self.buffers[(self.steps_done() + 1) & 1].fill_(float("nan"))
+        (self.full if self.mode == "packets" else self.buffers[(self.steps_done() + 1) & 1]).fill_(float("nan"))
 
-    def last_wait_us(self) -> float:
-        """How long this rank's latest arrive-and-wait took, from the two device time stamps the barrier leaves."""
+    def last_wait_us(self) -> float | None:
+        """Stores mode: how long this rank's latest arrive-and-wait took, from the two device time stamps the barrier leaves."""
+        if self.mode == "packets":
+            return None
         t = self.flags[16:20].view(torch.int64).cpu().tolist()
         return (t[1] - t[0]) / 1e3
 

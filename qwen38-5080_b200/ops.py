@@ -178,7 +178,9 @@ def decode_attention(q, k_cache, v_cache, k_scale, v_scale, seq_len, *, workspac
 
 
 def peer_barrier(peer_out, status: torch.Tensor) -> None:
-    """Cross-GPU arrive-and-wait after `decode_attention(..., peer_out=...)` (same stream)."""
+    """Cross-GPU arrive-and-wait after `decode_attention(..., peer_out=...)` (same stream); nothing to do in packet mode."""
+    if not peer_out.needs_barrier:
+        return
     check(_lib.lib().b200attn_peer_barrier(peer_out.c_flags, peer_out.rank, peer_out.world, _ptr(status), _stream()),
           "b200attn_peer_barrier")
 
@@ -187,8 +189,9 @@ def append_decode(q, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 
                   softmax_scale: float | None = None, advance: bool = True, out: torch.Tensor | None = None,
                   variant: str | None = None, peer_out=None, barrier: bool = False) -> torch.Tensor:
     """One decode step: append this token's K/V at seq_pos, attend seq_pos+1 tokens, bump seq_pos.
-    With `peer_out` (tensor parallel) the results go into every rank's gathered buffer; either pass
-    `barrier=True` (the cross-GPU arrive-and-wait becomes part of the step) or follow with `peer_barrier`."""
+    With `peer_out` (tensor parallel) the results go into every rank's gathered tensor (`peer_out.current()`); in its
+    stores mode either pass `barrier=True` (the cross-GPU arrive-and-wait becomes part of the step) or follow with
+    `peer_barrier`; in packet mode the step is complete by itself."""
     _need_cuda(q, k_new, v_new, k_scale, v_scale, seq_pos)
     h_q, d = q.shape[-2], q.shape[-1]
     shape = make_shape(h_q, k_cache, v_cache, k_scale)
@@ -197,7 +200,7 @@ def append_decode(q, k_new, v_new, k_cache, v_cache, k_scale, v_scale, seq_pos, 
             ctypes.byref(shape), ctypes.byref(peer_out.c_peers), _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache),
             _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(seq_pos), int(advance),
             d ** -0.5 if softmax_scale is None else softmax_scale, VARIANTS[variant or workspace.variant],
-            workspace.num_splits, _ptr(workspace.buf), workspace.nbytes, peer_out.c_flags if barrier else None,
+            workspace.num_splits, _ptr(workspace.buf), workspace.nbytes, peer_out.c_flags if barrier and peer_out.needs_barrier else None,
             _ptr(workspace.status), _stream())
         check(rc, "b200attn_append_decode_peers")
         return None     # after the barrier: peer_out.current()

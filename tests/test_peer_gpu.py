@@ -1,8 +1,9 @@
 """The two multi-GPU shardings on real GPUs, one process per GPU (skipped with fewer than 2 GPUs; runs
 on min(GPUs, 8) ranks, a divisor of the 8 KV heads).
 
-* KV-head tensor parallel with the output all-gather fused into the attention kernel (peer stores into
-  every rank's gathered buffer): a small case where sharded == single-GPU bit for bit, and a case big
+* KV-head tensor parallel with the output all-gather fused into the attention kernel (value+step packets
+  into the other ranks' staging, or plain stores into every rank's gathered tensors followed by a
+  barrier): a small ragged case against the single-GPU result (bit for bit where the split points coincide), and a case big
   enough that the default kernel choice is the all-tcgen05 kernel with (layer, sequence, head) pairs
   split over several CTAs, checked against the single-GPU result and the CPU oracle.
 * sequence sharding of a ragged batch: every rank steps its own sequences; the gathered result is the
@@ -31,8 +32,19 @@ def _setup(rank, world, port):
     return dist, dev, importlib.import_module("qwen38-5080_b200")
 
 
-def _finish(dist, ret, rank, ok):
-    ret[rank] = ok
+class _Checks:
+    """Collects the labels of failed checks, so that a failing rank says what failed."""
+
+    def __init__(self):
+        self.failed = []
+
+    def __call__(self, label, cond):
+        if not cond:
+            self.failed.append(label)
+
+
+def _finish(dist, ret, rank, chk):
+    ret[rank] = chk.failed if isinstance(chk, _Checks) else ([] if chk else ["failed"])
     torch.cuda.synchronize(); dist.barrier()
     os._exit(0)
 
@@ -49,17 +61,28 @@ def _small_worker(rank, world, port, ret):
            "vs": case["v_scale"][:, kv].contiguous().to(dev)}
     shape = pkg.make_shape(h_q // world, loc["k"], loc["v"], loc["ks"])
     seq = torch.tensor(lens, dtype=torch.int32, device=dev)
-    peer = pkg.dist.PeerOutput(loc["q"], world, rank)
+    peers = {mode: pkg.dist.PeerOutput(loc["q"], world, rank, mode=mode) for mode in ("packets", "stores")}
     ref_case = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
     shape1 = pkg.make_shape(h_q, ref_case["k_cache"], ref_case["v_cache"], ref_case["k_scale"])
     g = torch.Generator().manual_seed(5)
     k_new = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16)
     v_new = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16)
-    ok = True
-    for variant in ("mma", "umma2"):
+    chk = _Checks()
+    done = {"packets": 0, "stores": 0}
+
+    def same(got, want, variant):
+        # The all-tcgen05 kernel cuts this small case into one tile per CTA on one GPU and on a shard alike, so the
+        # partials and their merge order are the same: bit-identical.  The mma.sync kernel sizes its grid by the number
+        # of pairs, the shard's split points fall elsewhere inside the pairs of this ragged batch: last-bit differences.
+        if variant == "umma2":
+            return torch.equal(got.view(torch.int16), want.view(torch.int16))
+        m = oracle.error_metrics(got.cpu(), want.cpu())
+        return m["max_abs"] <= 2.0 ** -7 and m["cosine"] >= 0.99999
+    for variant, mode in (("mma", "packets"), ("umma2", "packets"), ("mma", "stores"), ("umma2", "stores")):
+        peer = peers[mode]
         ws = pkg.Workspace(shape, dev, variant=variant)
         ws1 = pkg.Workspace(shape1, dev, variant=variant)
-        for step in range(3):      # repeated steps: the barrier's epoch advances on the device
+        for step in range(3):      # repeated steps: the step counter advances on the device
             peer.poison_next()
             torch.cuda.synchronize(); dist.barrier()
             pkg.decode_attention(loc["q"], loc["k"], loc["v"], loc["ks"], loc["vs"], seq, workspace=ws, peer_out=peer)
@@ -69,8 +92,10 @@ def _small_worker(rank, world, port, ret):
             want = pkg.decode_attention(ref_case["q"], ref_case["k_cache"], ref_case["v_cache"], ref_case["k_scale"],
                                         ref_case["v_scale"], seq, workspace=ws1)
             torch.cuda.synchronize()
-            ok = ok and torch.equal(peer.current().view(torch.int16), want.view(torch.int16)) and ws.read_status() == 0
-            ok = ok and peer.steps_done() == step + 1 + (0 if variant == "mma" else 5)
+            done[mode] += 1
+            chk(f"{variant} {mode} attention {step}: result", same(peer.current(), want, variant))
+            chk(f"{variant} {mode} attention {step}: status", ws.read_status() == 0)
+            chk(f"{variant} {mode} attention {step}: counter {peer.steps_done()} != {done[mode]}", peer.steps_done() == done[mode])
             dist.barrier()
         # the whole decode step (append + attend + advance) with the gathered output, against one GPU
         kc, vc = loc["k"].clone(), loc["v"].clone()
@@ -86,11 +111,14 @@ def _small_worker(rank, world, port, ret):
             want = pkg.append_decode(ref_case["q"], k_new.to(dev), v_new.to(dev), kc1, vc1, ref_case["k_scale"],
                                      ref_case["v_scale"], pos1, workspace=ws1)
             torch.cuda.synchronize()
-            ok = ok and torch.equal(peer.current().view(torch.int16), want.view(torch.int16)) and ws.read_status() == 0
-            ok = ok and torch.equal(kc, kc1[:, :, kv]) and torch.equal(vc, vc1[:, :, kv]) and torch.equal(pos, pos1)
-            ok = ok and pos.cpu().tolist() == [x + step + 1 for x in lens]
+            done[mode] += 1
+            chk(f"{variant} {mode} step {step}: result", same(peer.current(), want, variant))
+            chk(f"{variant} {mode} step {step}: status", ws.read_status() == 0)
+            chk(f"{variant} {mode} step {step}: cache", torch.equal(kc, kc1[:, :, kv]) and torch.equal(vc, vc1[:, :, kv]) and torch.equal(pos, pos1))
+            chk(f"{variant} {mode} step {step}: positions", pos.cpu().tolist() == [x + step + 1 for x in lens])
+            chk(f"{variant} {mode} step {step}: counter {peer.steps_done()} != {done[mode]}", peer.steps_done() == done[mode])
             dist.barrier()
-    _finish(dist, ret, rank, bool(ok))
+    _finish(dist, ret, rank, chk)
 
 
 def _random_bytes(shape, gen, dev):
@@ -241,7 +269,7 @@ def _run(worker, port_base, timeout=300):
         for p in alive:
             p.kill()
         assert not alive, "a rank did not finish"
-        assert dict(ret) == {r: True for r in range(world)}
+        assert dict(ret) == {r: [] for r in range(world)}
 
 
 def test_fused_all_gather_matches_single_gpu():
