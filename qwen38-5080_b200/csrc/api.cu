@@ -280,6 +280,7 @@ static int decode_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers,
       // buffer to unpack from, its own gathered tensor
       if (fused && fused->barrier_flags) return B200ATTN_ERR_SHAPE;   // packets need no barrier and must not be mixed with one
       const size_t slot = staging_slot_bytes(g);
+      if ((unsigned long long)peers->n_peers * (slot / 8) >= 0x7fffffffull) return B200ATTN_ERR_SHAPE;   // 32-bit packet indices
       for (int r = 0; r < peers->n_peers; ++r) {
         char* base = r == peers->rank ? nullptr : (char*)peers->staging[r] + (size_t)peers->rank * slot;
         a.out_peer[r] = base;

@@ -115,7 +115,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   float* sDump = reinterpret_cast<float*>(sQ + 2 * q_bytes);                          // [2][4][G][DP]
   float* sML = sDump + kDumpBufs * kConsumerWarps * dump_warp_floats;                         // [2][4][16]: m[8], l[8]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sML + kDumpBufs * kConsumerWarps * 16);
-  int* sFlags = reinterpret_cast<int*>(bars + 2 * stages + 9);                        // [0] timed_out [2] any_empty [3] copies
+  unsigned long long* sPeer = reinterpret_cast<unsigned long long*>(bars + 2 * stages + 9);   // [8], see fill_peer_table
+  int* sFlags = reinterpret_cast<int*>(sPeer + 8);                                    // [0] timed_out [2] any_empty [3] copies
   int* sLen = sFlags + 4;                                                             // [batch]
   int* sCum = sLen + g.batch;                                                         // [batch+1]
   volatile int* timed_out = sFlags;
@@ -162,11 +163,15 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 
   // sequences of length 0 have no tiles: their outputs are zero, written by whoever gets there
   if (sFlags[2] & 1) {
+    if (p.n_out) {   // tensor parallel: the destinations are needed here already (the epilogue warp writes them again later)
+      if (tid < 8) fill_peer_table(p, sPeer, tid);
+      __syncthreads();
+    }
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
         for (int i = 2 * tid; i < g.h_q * D; i += 2 * kThreads)
-          emit_bits(p, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
+          emit_bits(p, sPeer, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
     }
   }
 
@@ -228,7 +233,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       if (lane == 0) mbar_arrive(appended0);
     }
     if (has_work)
-      epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+      epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer);
   } else if (has_work) {
     // ================================ consumer warps ================================
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
@@ -457,6 +462,7 @@ size_t smem_bytes_for(const Geometry& g, int stages) {
   b += (size_t)kDumpBufs * kConsumerWarps * g.group * (g.head_dim + 4) * 4;   // dumped warp states
   b += (size_t)kDumpBufs * kConsumerWarps * 16 * 4;                   // their m, l
   b += (size_t)(2 * stages + 9) * 8;                          // barriers
+  b += 64;                                                    // destinations of the tensor-parallel output
   b += 16;                                                    // flags
   b += (size_t)(2 * g.batch + 1) * 4;                         // sLen, sCum
   return (b + 15) & ~(size_t)15;

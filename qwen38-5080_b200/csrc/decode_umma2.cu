@@ -106,6 +106,7 @@ __host__ __device__ inline size_t umma2_fixed_bytes(int group, int head_dim, int
   b += (size_t)kGroups2 * group * (head_dim + 4) * 4;                // dumped states
   b += (size_t)kGroups2 * 16 * 4;                                    // their m, l
   b += (size_t)(4 + 2 * kQRing2 + 4 * kGroups2 + 3) * 8;             // fixed barriers
+  b += 64;                                                           // destinations of the tensor-parallel output
   b += 32;                                                           // flags
   b += (size_t)(2 * batch + 1) * 4;
   return b;
@@ -199,7 +200,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   const uint32_t pfull0 = sempty0 + 8u * NG, pvdone0 = pfull0 + 8u * NG;
   const uint32_t dfull0 = pvdone0 + 8u * NG, dempty0 = dfull0 + 8u, appended0 = dempty0 + 8u;
   constexpr int kFixedBars = 4 + 2 * kQRing2 + 4 * NG + 3;
-  int* sFlags = reinterpret_cast<int*>(bars + kFixedBars + 2 * kstages + 2 * vstages);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
+  unsigned long long* sPeer = reinterpret_cast<unsigned long long*>(bars + kFixedBars + 2 * kstages + 2 * vstages);   // [8], see fill_peer_table
+  int* sFlags = reinterpret_cast<int*>(sPeer + 8);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
   int* sLen = sFlags + 8;
   int* sCum = sLen + g.batch;
   volatile int* timed_out = sFlags;
@@ -247,12 +249,16 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)sFlags[1];
 
-  if (sFlags[2] & 1) {   // sequences of length 0 have no tiles: their outputs are zero
+  if (sFlags[2] & 1) {
+    if (p.n_out) {   // tensor parallel: the destinations are needed here already (the epilogue warp writes them again later)
+      if (tid < 8) fill_peer_table(p, sPeer, tid);
+      __syncthreads();
+    }
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
         for (int i = 2 * tid; i < g.h_q * D; i += 2 * kThreads2)
-          emit_bits(p, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
+          emit_bits(p, sPeer, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
     }
   }
 
@@ -318,7 +324,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     }
   } else if (warp == kEpilogue2) {
     if (has_work)
-      epilogue_warp<D, 1, NG, true, PT>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out);
+      epilogue_warp<D, 1, NG, true, PT>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer);
   } else if (warp == kIssuerS2) {
     // ===================== S issuer warp: query operand, S = K q^T =====================
     if (has_work) {

@@ -287,35 +287,62 @@ __device__ __forceinline__ int peer_step(const MmaParams& p) {
 }
 __device__ __forceinline__ int peer_buffer_base(int step) { return (step & 1) ? 8 : 0; }
 
-// One pair of adjacent bf16 outputs on its way: `idx` is its element index in this rank's [n_layers][batch][h_q][D]
-// layout, `peer_idx` in the gathered [n_layers][batch][out_hq_total][D] layout.
-__device__ __forceinline__ void emit_bits(const MmaParams& p, int step, long long idx, long long peer_idx, uint32_t bits) {
-  if (p.n_out == 0) {
-    *reinterpret_cast<uint32_t*>(p.out + idx) = bits;
-  } else if (p.pkt) {
-    *reinterpret_cast<uint32_t*>(p.out + peer_idx) = bits;   // this rank's rows of its own gathered tensor
+// Tensor-parallel output: where this launch's results go on the other GPUs.  The epilogue warp of a CTA writes the
+// (up to 8) destinations of this step into shared memory once (fill_peer_table), and the results of a pair then go
+// out together through one out-of-line function that reads them from there (send_pair).  All of it is about code
+// size and latency: the kernels' tile loops are sensitive to the size of the code around them (destination loops
+// inlined at the twenty places of the epilogue that produce output cost the long-cache kernel 3 % of its time),
+// kernel parameters can only be read by the kernel function itself, a lookup in the parameter block per destination
+// and value costs ~150 cycles, and so does an out-of-line call per value (both ~2 us per pair).
+//   packet mode: entry r = this rank's slot in rank r's staging buffer for this step's parity (0 for the own rank)
+//   stores mode: entry r = rank r's gathered tensor of this step's parity (0 beyond n_out)
+__device__ __forceinline__ void fill_peer_table(const MmaParams& p, unsigned long long* tab, int r) {   // entry r < 8
+  const int step = peer_step(p);
+  unsigned long long v = 0;
+  if (p.pkt) {
+    if (p.out_peer[r]) v = (unsigned long long)p.out_peer[r] + (unsigned long long)(step & 1) * p.n_out * p.pkt_slot_words * 8ull;
+  } else if (r < p.n_out) {
+    v = (unsigned long long)p.out_peer[peer_buffer_base(step) + r];
+  }
+  tab[r] = v;
+}
+// Packet mode: one 8-byte store per rank, value and step number arrive together or not at all.  Stores mode: the
+// output all-gather as plain stores into every rank's gathered tensor (own one included) over NVLink.
+__device__ __noinline__ void emit_peer(const unsigned long long* tab, int pkt, int step, long long idx, long long peer_idx, uint32_t bits) {
+  if (pkt) {
     const unsigned long long w = (unsigned long long)bits | ((unsigned long long)(uint32_t)step << 32);
-    const int base = peer_buffer_base(step);
-    // one 8-byte store per rank: value and step number arrive together or not at all (rolled loops: this code is
-    // inlined at many places of the epilogue, and the kernels are sensitive to their code size)
-#pragma unroll 1
-    for (int r = 0; r < p.n_out; ++r) {
-      unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.out_peer[base + r]);
-      if (dst) asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst + (idx >> 1)), "l"(w) : "memory");
+    const unsigned long long off = (unsigned long long)(idx >> 1) * 8ull;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const unsigned long long dst = tab[r];
+      if (dst) asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst + off), "l"(w) : "memory");
     }
   } else {
-    // the output all-gather as plain stores into every rank's gathered tensor (own one included) over NVLink
-    const int base = peer_buffer_base(step);
-#pragma unroll 1
-    for (int r = 0; r < p.n_out; ++r) *reinterpret_cast<uint32_t*>(p.out_peer[base + r] + peer_idx) = bits;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const unsigned long long dst = tab[r];
+      if (dst) *reinterpret_cast<uint32_t*>(dst + (unsigned long long)peer_idx * 2ull) = bits;
+    }
   }
 }
 
-// Two adjacent outputs -> bf16.  With a gate, the consumer-side fusion of the reference's attention
+// One pair of adjacent bf16 outputs on its way: `idx` is its element index in this rank's [n_layers][batch][h_q][D]
+// layout, `peer_idx` in the gathered [n_layers][batch][out_hq_total][D] layout.
+__device__ __forceinline__ void emit_bits(const MmaParams& p, const unsigned long long* peer_tab, int step, long long idx,
+                                          long long peer_idx, uint32_t bits) {
+  if (p.n_out == 0) {
+    *reinterpret_cast<uint32_t*>(p.out + idx) = bits;
+  } else {
+    if (p.pkt) *reinterpret_cast<uint32_t*>(p.out + peer_idx) = bits;   // this rank's rows of its own gathered tensor
+    emit_peer(peer_tab, p.pkt, step, idx, peer_idx, bits);
+  }
+}
+
+// Two adjacent outputs -> bf16 bits.  With a gate, the consumer-side fusion of the reference's attention
 // block, attn_output * sigmoid(gate), with its two separate bf16 roundings
 // (docs/journal/2026-10-23-phase2-r3-coordinator.md:147-150): s = bf16(sigmoid(gate)), then
-// bf16(bf16(attn) * s).
-__device__ __forceinline__ void store_out(const MmaParams& p, int step, long long idx, long long peer_idx, float x, float y) {
+// bf16(bf16(attn) * s).  `idx`: element index in this rank's [n_layers][batch][h_q][D] layout.
+__device__ __forceinline__ uint32_t out_bits(const MmaParams& p, long long idx, float x, float y) {
   const uint16_t* gate = p.gate;
   __nv_bfloat162 ob = __floats2bfloat162_rn(x, y);
   if (gate) {
@@ -324,7 +351,41 @@ __device__ __forceinline__ void store_out(const MmaParams& p, int step, long lon
     const __nv_bfloat162 s = __floats2bfloat162_rn(__fdiv_rn(1.f, 1.f + expf(-g0)), __fdiv_rn(1.f, 1.f + expf(-g1)));
     ob = __floats2bfloat162_rn(__low2float(ob) * __low2float(s), __high2float(ob) * __high2float(s));
   }
-  emit_bits(p, step, idx, peer_idx, *reinterpret_cast<uint32_t*>(&ob));
+  return *reinterpret_cast<uint32_t*>(&ob);
+}
+
+// The finished rows of one (layer, sequence, kv head) pair, G heads x D dims, on their way to the other GPUs: lane
+// `lane` of the epilogue warp holds words[h * (D / 64) + r] = dims 2 * (lane + 32 r), + 1 of head h.  `orow`: the
+// pair's first element in this rank's [n_layers][batch][h_q][D] layout, `prow` in the gathered layout.
+template <int D>
+__device__ __noinline__ void send_pair(const unsigned long long* tab, int pkt, int step, const uint32_t* words, int G,
+                                       long long orow, long long prow, uint16_t* own, int lane) {
+  constexpr int UR = D / 64;
+  if (pkt) {   // this rank's rows of its own gathered tensor
+    for (int h = 0; h < G; ++h)
+#pragma unroll
+      for (int r = 0; r < UR; ++r) *reinterpret_cast<uint32_t*>(own + prow + h * D + 2 * (lane + 32 * r)) = words[h * UR + r];
+  }
+  const unsigned long long tag = (unsigned long long)(uint32_t)step << 32;
+#pragma unroll 1
+  for (int d = 0; d < 8; ++d) {
+    const unsigned long long dst = tab[d];
+    if (!dst) continue;
+    if (pkt) {   // one 8-byte store per value pair: value and step number arrive together or not at all
+      const unsigned long long base = dst + (unsigned long long)((orow >> 1) + lane) * 8ull;
+      for (int h = 0; h < G; ++h)
+#pragma unroll
+        for (int r = 0; r < UR; ++r)
+          asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(base + (unsigned long long)(h * (D / 2) + 32 * r) * 8ull),
+                       "l"((unsigned long long)words[h * UR + r] | tag) : "memory");
+    } else {     // plain stores into rank d's gathered tensor
+      const unsigned long long base = dst + (unsigned long long)(prow + 2 * lane) * 2ull;
+      for (int h = 0; h < G; ++h)
+#pragma unroll
+        for (int r = 0; r < UR; ++r)
+          *reinterpret_cast<uint32_t*>(base + (unsigned long long)(h * D + 64 * r) * 2ull) = words[h * UR + r];
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -339,13 +400,18 @@ template <int D, int NDUMP, int NW = kConsumerWarps, bool PLAIN = false, bool UN
 __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long long r0, long long r1,
                                               long long total, int n_eff, const int* sCum, const int* sLen,
                                               const float* sDump, const float* sML, uint32_t dfull0,
-                                              uint32_t dempty0, volatile int* timed_out) {
+                                              uint32_t dempty0, volatile int* timed_out, const unsigned long long* peer_tab) {
   constexpr int DP = D + 4;                // padded head row of a dumped state, in floats
   constexpr int UR = D / 64;               // dim pairs per epilogue lane
   const Geometry& g = p.g;
   const int G = g.group;
   const int dump_warp_floats = G * DP;
   const int step = peer_step(p);
+  uint32_t obuf[kMaxGroup * UR];   // peer mode: the bf16 rows of the pair being finished, sent together (send_pair)
+  if (p.n_out) {
+    if (lane < 8) fill_peer_table(p, const_cast<unsigned long long*>(peer_tab), lane);
+    __syncwarp();
+  }
 {
   Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
   long long cur = r0;
@@ -389,7 +455,10 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           const float inv = ll > 0.f ? vs / ll : 0.f;
 #pragma unroll
           for (int r = 0; r < UR; ++r) {
-            store_out(p, step, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[r] * inv, ay[r] * inv);
+            const long long idx = orow + h * D + 2 * (lane + 32 * r);
+            const uint32_t bits = out_bits(p, idx, ax[r] * inv, ay[r] * inv);
+            if (p.n_out == 0) *reinterpret_cast<uint32_t*>(p.out + idx) = bits;
+            else obuf[h * UR + r] = bits;
           }
         } else {
 #pragma unroll
@@ -398,6 +467,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           if (lane == 0) { pml[h] = M; pml[8 + h] = ll; }
         }
       }
+      if (complete && p.n_out) send_pair<D>(peer_tab, p.pkt, step, obuf, G, orow, prow, p.out, lane);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(dempty0 + 8u * db);   // the dump buffer may be overwritten
@@ -460,10 +530,14 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
             const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
 #pragma unroll
             for (int r = 0; r < UR; ++r) {
-              store_out(p, step, orow + h * D + 2 * (lane + 32 * r), prow + h * D + 2 * (lane + 32 * r), ax[h][r] * inv, ay[h][r] * inv);
+              const long long idx = orow + h * D + 2 * (lane + 32 * r);
+              const uint32_t bits = out_bits(p, idx, ax[h][r] * inv, ay[h][r] * inv);
+              if (p.n_out == 0) *reinterpret_cast<uint32_t*>(p.out + idx) = bits;
+              else obuf[h * UR + r] = bits;
             }
           }
         }
+        if (p.n_out) send_pair<D>(peer_tab, p.pkt, step, obuf, G, orow, prow, p.out, lane);
         if (lane == 0) p.tickets[pair] = 0;   // ready for the next launch
       }
     }
@@ -554,14 +628,14 @@ __device__ __forceinline__ Unpack unpack_of(const MmaParams& p, int step) {
                 p.g.h_q * p.g.head_dim / 2, (long long)p.out_hq_total * p.g.head_dim, p.n_out, p.out_head_base / p.g.h_q, step};
 }
 __device__ __noinline__ void unpack_packets(Unpack u, int part, int parts, int tid, int nthreads) {
-  const long long total = (long long)(u.n_out - 1) * u.slot_words;
-  const long long t0 = (long long)part * total / parts, t1 = ((long long)part + 1) * total / parts;
+  // 32-bit index arithmetic: the host refuses staging buffers of 2^31 packets or more
+  const uint32_t slot = (uint32_t)u.slot_words, total = (uint32_t)(u.n_out - 1) * slot;
+  const uint32_t t0 = (uint32_t)((unsigned long long)part * total / parts), t1 = (uint32_t)(((unsigned long long)part + 1) * total / parts);
   const unsigned long long start = global_timer_ns();
-  for (long long t = t0 + tid; t < t1; t += nthreads) {
-    const int si = (int)(t / u.slot_words);
-    const int s = si < u.rank ? si : si + 1;
-    const long long w = t - (long long)si * u.slot_words;
-    const unsigned long long* src = u.src + (long long)s * u.slot_words + w;
+  for (uint32_t t = t0 + tid; t < t1; t += nthreads) {
+    const uint32_t si = t / slot, w = t - si * slot;
+    const uint32_t s = si < (uint32_t)u.rank ? si : si + 1;
+    const unsigned long long* src = u.src + (size_t)s * slot + w;
     unsigned long long v;
     bool ok = false;
     for (int tries = 0;; ++tries) {
@@ -570,17 +644,23 @@ __device__ __noinline__ void unpack_packets(Unpack u, int part, int parts, int t
       if ((tries & 63) == 63 && global_timer_ns() - start > kBarrierBudgetNs) break;
     }
     if (!ok) { atomicOr(u.status, B200ATTN_STATUS_WAIT_TIMEOUT); return; }
-    const long long row = w / u.row_words;
-    const long long rem = w - row * u.row_words;
-    *reinterpret_cast<uint32_t*>(u.out + row * u.out_row + (long long)s * u.row_words * 2 + rem * 2) = (uint32_t)v;
+    const uint32_t row = w / (uint32_t)u.row_words, rem = w - row * (uint32_t)u.row_words;
+    *reinterpret_cast<uint32_t*>(u.out + (long long)row * u.out_row + (size_t)s * u.row_words * 2 + rem * 2) = (uint32_t)v;
   }
 }
 
 __device__ __noinline__ void finish_step(StepEnd s, Unpack u, int unpack_all, int lane) {
+  // the positions of the first 32 sequences are fetched while the counter's round trip is under way: whoever turns
+  // out to be last has them at hand (nobody writes them before that)
+  int pos0 = 0;
+  if (s.seq_pos && lane < s.batch) pos0 = s.seq_pos[lane];
   int last = 0;
   if (lane == 0) {
     int arrived;
-    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(s.exit_count) : "memory");
+    if (s.bar_world)   // stores mode: the counter also carries this CTA's peer stores to the CTA that publishes the flags
+      asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(s.exit_count) : "memory");
+    else               // otherwise it only counts: the CTA's reads of the positions are long complete
+      asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(s.exit_count) : "memory");
     last = arrived == (int)gridDim.x - 1;
   }
   last = __shfl_sync(0xffffffffu, last, 0);
@@ -591,7 +671,7 @@ __device__ __noinline__ void finish_step(StepEnd s, Unpack u, int unpack_all, in
   }
   if (s.seq_pos)
     for (int b = lane; b < s.batch; b += 32) {
-      const int pos = s.seq_pos[b];
+      const int pos = b < 32 ? pos0 : s.seq_pos[b];
       if (pos >= 0 && pos + 1 <= s.capacity) s.seq_pos[b] = pos + 1;
     }
   if (lane == 0) {
