@@ -333,7 +333,7 @@ class StepRunner:
             self.gather()
 
     def kernels_per_step(self) -> int:
-        fused = self.cache.workspace.resolved in ("umma2", "mma") and not self.cache.per_token
+        fused = self.cache.workspace.resolved == "umma2" or (self.cache.workspace.resolved == "mma" and not self.cache.per_token)
         if fused:
             return 1                         # the fused step: append, attention, combine, position bump (and barrier) in one launch
         n = 3 if self.advance else 2         # append, attention (+ fused combine), position bump

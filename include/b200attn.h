@@ -361,12 +361,12 @@ int b200attn_qk_norm_rope_append(const B200AttnShape* shape,
 /*
  * Fused convenience for one decode step: A (append at seq_pos) then B+C attending
  * seq_pos[b]+1 tokens, then seq_pos[b] += 1 if advance_pos.  Same stream, no host sync.
- * With the stream-K kernels (B200ATTN_VARIANT_UMMA2, B200ATTN_VARIANT_MMA, i.e. whatever AUTO
- * resolves to for per-head scales) the step is ONE launch: the CTA that owns the tile holding a
- * pair's new token quantises that row first, and the last CTA to finish advances the
- * positions; the other variants, and the per-token scale layout, launch append, attention and
- * the position kernel one after the other.  Cache bytes, positions and status bits are the same
- * either way.
+ * With the stream-K kernels (B200ATTN_VARIANT_UMMA2 for both scale layouts, B200ATTN_VARIANT_MMA
+ * for per-head scales, i.e. whatever AUTO resolves to where a tensor-core kernel applies) the step
+ * is ONE launch: the CTA that owns the tile holding a pair's new token quantises that row first
+ * (per-token layout: after computing and storing its scale), and the last CTA to finish advances
+ * the positions; the CUDA-core variant launches append, attention and the position kernel one
+ * after the other.  Cache bytes, scales, positions and status bits are the same either way.
  */
 int b200attn_append_decode(const B200AttnShape* shape,
                            const void* q_bf16,

@@ -368,10 +368,9 @@ static int step_impl(const B200AttnShape* shape, const B200AttnPeerOut* peers, c
     if (workspace_bytes < need) return B200ATTN_ERR_WORKSPACE;
   }
   if (!aligned16(q) || !aligned16(out) || !aligned16(workspace)) return B200ATTN_ERR_ALIGN;
-  if ((v == B200ATTN_VARIANT_UMMA2 || v == B200ATTN_VARIANT_MMA) && g.scale_mode == B200ATTN_SCALE_PER_HEAD) {
-    // one launch: the attention kernel appends the new rows and advances the positions itself
-    // (per-token scales are computed by the append kernel: three launches below), and ends with the
-    // cross-GPU barrier when one is asked for
+  if (v == B200ATTN_VARIANT_UMMA2 || (v == B200ATTN_VARIANT_MMA && g.scale_mode == B200ATTN_SCALE_PER_HEAD)) {
+    // one launch: the attention kernel appends the new rows (per-token layout: and computes their scales) and
+    // advances the positions itself, and ends with the cross-GPU barrier when one is asked for
     if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale) return B200ATTN_ERR_NULL;
     if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache)) return B200ATTN_ERR_ALIGN;
     const FusedStep fused{k_new, v_new, advance_pos ? seq_pos : nullptr, barrier_flags};

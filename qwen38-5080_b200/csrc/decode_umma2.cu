@@ -113,17 +113,18 @@ __host__ __device__ inline size_t umma2_fixed_bytes(int group, int head_dim, int
 }
 
 // Fused step: quantise the new token of every pair whose last tile the CTA owns (the tile that holds it),
-// exactly as the append kernel does.  Called by the softmax warps; threads work in teams of D/2, 4 values
-// of the K or V row each.  Kept out of line: it runs once per launch and must not disturb the tile loop.
-template <int D>
-__device__ __noinline__ void append_new_rows(int n_layers, int batch, int h_kv, int capacity, long long k_layer_stride,
+// exactly as the append kernel does.  Called by the softmax warps: one warp per K or V row at a time, D / 32 values
+// per lane.  Per-token scale layout: the row's scale amax / 448 is computed here (a warp reduction) and written to
+// [layer][sequence][slot][kv head] before the bytes.  Kept out of line: it runs once per launch and must not
+// disturb the tile loop.
+template <int D, bool PT>
+__device__ __noinline__ void append_new_rows(int batch, int h_kv, int capacity, long long k_layer_stride,
                                              long long v_layer_stride, const uint16_t* k_new, const uint16_t* v_new,
-                                             uint8_t* k_cache, uint8_t* v_cache, const float* k_scale, const float* v_scale,
+                                             uint8_t* k_cache, uint8_t* v_cache, float* k_scale, float* v_scale,
                                              const int* seq_pos, int tid, long long r0, long long r1,
                                              const int* sCum, const int* sLen) {
-  (void)n_layers;
-  constexpr int TEAM = D / 2, TEAMS = kSoftmaxWarps2 * 32 / TEAM;
-  const int team = tid / TEAM, e = tid % TEAM, which = e >= D / 4 ? 1 : 0, el = (e % (D / 4)) * 4;
+  constexpr int VPL = D / 32;   // values per lane: 4 or 8
+  const int wid = tid >> 5, lane = tid & 31;
   Cursor a = locate(r0, sCum, sLen, batch, h_kv);
   long long cur = r0;
   int n = 0;
@@ -131,19 +132,39 @@ __device__ __noinline__ void append_new_rows(int n_layers, int batch, int h_kv, 
     const long long pair_end = cur - a.tile + a.tiles_b;
     if (pair_end <= r1) {
       const int pos = seq_pos[a.b];
-      if (n % TEAMS == team && pos >= 0 && pos < capacity) {
-        const long long rowi = ((long long)a.layer * batch + a.b) * h_kv + a.h;
-        const uint2 raw = *reinterpret_cast<const uint2*>((which ? v_new : k_new) + rowi * D + el);
-        const float sc = (which ? v_scale : k_scale)[a.layer * h_kv + a.h];
-        const uint32_t bytes = (uint32_t)quantize_e4m3(bf16_bits_to_float(raw.x & 0xFFFFu), sc) |
-                               ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.x >> 16), sc) << 8) |
-                               ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.y & 0xFFFFu), sc) << 16) |
-                               ((uint32_t)quantize_e4m3(bf16_bits_to_float(raw.y >> 16), sc) << 24);
-        uint8_t* dst = (which ? v_cache : k_cache) + (long long)a.layer * (which ? v_layer_stride : k_layer_stride) +
-                       (((long long)a.b * h_kv + a.h) * capacity + pos) * D + el;
-        *reinterpret_cast<uint32_t*>(dst) = bytes;
+      if (pos >= 0 && pos < capacity) {
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which, ++n) {
+          if (n % kSoftmaxWarps2 != wid) continue;
+          const long long rowi = ((long long)a.layer * batch + a.b) * h_kv + a.h;
+          const uint16_t* src = (which ? v_new : k_new) + rowi * D + lane * VPL;
+          float x[VPL];
+#pragma unroll
+          for (int i = 0; i < VPL / 4; ++i) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(src + 4 * i);
+            x[4 * i] = bf16_bits_to_float(raw.x & 0xFFFFu); x[4 * i + 1] = bf16_bits_to_float(raw.x >> 16);
+            x[4 * i + 2] = bf16_bits_to_float(raw.y & 0xFFFFu); x[4 * i + 3] = bf16_bits_to_float(raw.y >> 16);
+          }
+          float sc;
+          if (PT) {
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) amax = fmaxf(amax, fabsf(x[i]));
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            sc = __fdiv_rn(amax, kE4m3Max);
+            if (lane == 0) (which ? v_scale : k_scale)[(((long long)a.layer * batch + a.b) * capacity + pos) * h_kv + a.h] = sc;
+          } else {
+            sc = (which ? v_scale : k_scale)[a.layer * h_kv + a.h];
+          }
+          uint8_t* dst = (which ? v_cache : k_cache) + (long long)a.layer * (which ? v_layer_stride : k_layer_stride) +
+                         (((long long)a.b * h_kv + a.h) * capacity + pos) * D + lane * VPL;
+#pragma unroll
+          for (int i = 0; i < VPL / 4; ++i)
+            *reinterpret_cast<uint32_t*>(dst + 4 * i) = (uint32_t)quantize_e4m3(x[4 * i], sc) | ((uint32_t)quantize_e4m3(x[4 * i + 1], sc) << 8) |
+                                                        ((uint32_t)quantize_e4m3(x[4 * i + 2], sc) << 16) | ((uint32_t)quantize_e4m3(x[4 * i + 3], sc) << 24);
+        }
       }
-      ++n;
     }
     cur = pair_end < r1 ? pair_end : r1;
     if (cur < r1) next_pair(a, sCum, sLen, batch, h_kv);
@@ -458,11 +479,14 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   } else if (has_work) {
     // ===== softmax warps: groups of four; group = tile index mod NG; one thread = one token / one output dim =====
     if (p.k_new) {
-      append_new_rows<D>(g.n_layers, g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new,
-                         p.k_cache_w, p.v_cache_w, p.k_scale, p.v_scale, p.seq_len, tid, r0, r1, sCum, sLen);
+      append_new_rows<D, PT>(g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new,
+                             p.k_cache_w, p.v_cache_w, const_cast<float*>(p.k_scale), const_cast<float*>(p.v_scale), p.seq_len, tid,
+                             r0, r1, sCum, sLen);
       asm volatile("fence.proxy.async.global;" ::: "memory");   // the rows -> visible to the TMA loads of this CTA
       __syncwarp();
       if (lane == 0) mbar_arrive(appended0);
+      // per-token layout: the new token's scales, written by one softmax warp, are read by another (its token's owner)
+      if (PT) asm volatile("bar.sync 5, %0;" ::"n"(kSoftmaxWarps2 * 32) : "memory");
     }
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
     long long cur = r0;
@@ -507,8 +531,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       float kst_next = 1.f, vst_next = 1.f;
       if (per_token && jfirst < it0 + ntiles && (c.tile + (jfirst - it0)) * kTile2 + tok_in_tile < c.len_b) {
         const long long si = (((long long)c.layer * g.batch + c.b) * g.capacity + (c.tile + (jfirst - it0)) * kTile2 + tok_in_tile) * g.h_kv + c.h;
-        kst_next = __ldg(p.k_scale + si);
-        vst_next = __ldg(p.v_scale + si);
+        kst_next = __ldcg(p.k_scale + si);
+        vst_next = __ldcg(p.v_scale + si);
       }
       for (int j = jfirst; j < it0 + ntiles; j += NG) {
         jlast = j;
@@ -519,8 +543,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         const float kst = kst_next, vst = vst_next * kPScale;
         if (per_token && j + NG < it0 + ntiles && tile_tok0 + NG * kTile2 + tok_in_tile < c.len_b) {
           const long long si = (((long long)c.layer * g.batch + c.b) * g.capacity + tile_tok0 + NG * kTile2 + tok_in_tile) * g.h_kv + c.h;
-          kst_next = __ldg(p.k_scale + si);
-          vst_next = __ldg(p.v_scale + si);
+          kst_next = __ldcg(p.k_scale + si);
+          vst_next = __ldcg(p.v_scale + si);
         }
         const bool sok = mbar_wait_lean(sfull, ph, timed_out, p.status);
         uint32_t r[16];

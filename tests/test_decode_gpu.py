@@ -285,7 +285,9 @@ def test_per_token_scale_mode_decode(pkg, oracle, cuda_device):
 def test_per_token_scales_on_the_tensor_cores(pkg, oracle, cuda_device):
     """The per-token scale layout through the all-tcgen05 kernel (each softmax thread applies its
     token's K and V scales): parity with the oracle on a ragged batch, agreement with the SIMT
-    kernel, and the decode step (append kernel computes the scales, then attention)."""
+    kernel, and the decode step — one launch with the all-tcgen05 kernel, which computes the new rows'
+    scales itself, against append kernel + attention + position kernel with the SIMT kernel: cache bytes,
+    scales and positions identical, over several steps (lengths cross a tile boundary)."""
     n_layers, batch, h_q, h_kv, d, cap = 2, 3, 40, 8, 128, 640
     lens = [300, 1, 513]
     q = torch.zeros(n_layers, batch, h_q, d, dtype=torch.bfloat16)
@@ -314,7 +316,7 @@ def test_per_token_scales_on_the_tensor_cores(pkg, oracle, cuda_device):
     assert m["max_abs"] <= 2.0 ** -6 and m["cosine"] >= 0.9999, m
     with pytest.raises(pkg.B200AttnError):        # the mma.sync kernel has no per-token path
         run_decode(pkg, case, cuda_device, "mma")
-    # the decode step with per-token scales: append kernel (scales + bytes), attention, position kernel
+    # the decode step with per-token scales
     caches = {}
     for variant in ("simt", "umma2"):
         c = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant=variant, scale_mode="per_token")
@@ -327,12 +329,25 @@ def test_per_token_scales_on_the_tensor_cores(pkg, oracle, cuda_device):
     g = torch.Generator().manual_seed(77)
     kn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
     vn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)
-    step_out = {v: caches[v].step(q.to(cuda_device), kn, vn, count=False).cpu() for v in caches}
-    torch.cuda.synchronize()
     a, u = caches["simt"], caches["umma2"]
-    assert torch.equal(a.k_cache, u.k_cache) and torch.equal(a.k_scale, u.k_scale) and torch.equal(a.seq_pos, u.seq_pos)
-    ref2 = oracle.decode_step_reference(q, u.k_cache.cpu(), u.v_cache.cpu(), u.k_scale.cpu(), u.v_scale.cpu(), [x + 1 for x in lens], cap)
-    assert_parity(oracle, step_out["umma2"], ref2, "per-token step")
+    for step in range(3):
+        kn_s, vn_s = torch.roll(kn, step, dims=-1), torch.roll(vn, step, dims=-1)
+        if step == 2:
+            kn_s = kn_s.clone()
+            kn_s[:, 1, 3] = 0                  # an all-zero key row: scale 0, zero bytes
+        step_out = {v: caches[v].step(q.to(cuda_device), kn_s, vn_s, count=False).cpu() for v in caches}
+        torch.cuda.synchronize()
+        assert torch.equal(a.k_cache, u.k_cache) and torch.equal(a.v_cache, u.v_cache), f"step {step}: cache bytes"
+        assert torch.equal(a.k_scale, u.k_scale) and torch.equal(a.v_scale, u.v_scale), f"step {step}: scales"
+        assert torch.equal(a.seq_pos, u.seq_pos) and u.seq_pos.cpu().tolist() == [x + step + 1 for x in lens]
+        assert a.workspace.read_status() == 0 and u.workspace.read_status() == 0
+        want_s = oracle.token_scales(kn_s.cpu().transpose(0, 1).reshape(batch, n_layers * h_kv, 1, d))     # [B, 1, n*h]
+        for b, L in enumerate(lens):
+            assert torch.equal(u.k_scale[:, b, L + step].cpu().flatten(), want_s[b, 0]), f"step {step}: scales of sequence {b} vs the oracle"
+        ref2 = oracle.decode_step_reference(q, u.k_cache.cpu(), u.v_cache.cpu(), u.k_scale.cpu(), u.v_scale.cpu(),
+                                            [x + step + 1 for x in lens], cap)
+        assert_parity(oracle, step_out["umma2"], ref2, f"per-token step {step}")
+    assert float(u.k_scale[0, 1, lens[1] + 2, 3]) == 0.0 and int(u.k_cache[0, 1, 3, lens[1] + 2].max()) == 0
 
 
 @pytest.mark.parametrize("variant", VARIANTS)
@@ -748,3 +763,166 @@ def test_in_launch_barrier_wait_is_bounded(pkg, oracle, cuda_device):
         assert_parity(oracle, buf[:, :, :h_q].cpu(), ref, "gathered buffer")
         assert torch.isnan(buf[:, :, h_q:].float()).all()          # the other rank's heads: untouched
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+
+
+def test_packet_wait_is_bounded(pkg, oracle, cuda_device):
+    """Tensor-parallel step in packet mode with a peer that never sends (a staging buffer nobody writes): every CTA's
+    wait for the other rank's packets runs out after its 1 s budget, the status word says so, this rank's own heads are
+    in its gathered tensor and in the 'peer's' staging all the same (as packets carrying step number 1), the cache and
+    the positions are advanced, the step counter is 1 and the context stays usable."""
+    import ctypes
+    import time
+    L = pkg._lib
+    n_layers, batch, h_q, h_kv, d, cap, lens = 2, 1, 20, 4, 128, 256, [130]
+    case = build_case(oracle, n_layers, batch, h_q, h_kv, d, lens, cap, seed=3)
+    dev = cuda_device
+    for variant in ("mma", "umma2"):
+        c = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=dev, variant=variant)
+        c.set_scales(case["k_scale"].to(dev), case["v_scale"].to(dev))
+        c.k_cache.copy_(case["k_cache"])
+        c.v_cache.copy_(case["v_cache"])
+        c.seq_pos.copy_(torch.tensor(lens, dtype=torch.int32))
+        g = torch.Generator().manual_seed(4)
+        kn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(dev)
+        vn = torch.randn(n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(dev)
+        nbytes = L.lib().b200attn_peer_staging_bytes(ctypes.byref(c.shape), 2)
+        assert nbytes == 2 * 2 * n_layers * batch * h_q * d // 2 * 8
+        mine = torch.zeros(nbytes // 8, dtype=torch.int64, device=dev)
+        silent_peer = torch.zeros_like(mine)                         # stands in for a rank that never sends
+        full = torch.full((n_layers, batch, 2 * h_q, d), float("nan"), dtype=torch.bfloat16, device=dev)
+        step = torch.zeros(1, dtype=torch.int32, device=dev)
+        out = (ctypes.c_void_p * 8)()
+        out[0] = full.data_ptr()
+        peers = L.B200AttnPeerOut(2, 0, 2 * h_q, L.GATHER_PACKETS, out, (ctypes.c_void_p * 8)(),
+                                  (ctypes.c_void_p * 8)(mine.data_ptr(), silent_peer.data_ptr()), step.data_ptr())
+        q = case["q"].to(dev)
+        ws = c.workspace
+        t0 = time.perf_counter()
+        rc = L.lib().b200attn_append_decode_peers(
+            ctypes.byref(c.shape), ctypes.byref(peers), q.data_ptr(), kn.data_ptr(), vn.data_ptr(), c.k_cache.data_ptr(),
+            c.v_cache.data_ptr(), c.k_scale.data_ptr(), c.v_scale.data_ptr(), c.seq_pos.data_ptr(), 1, d ** -0.5,
+            L.VARIANTS[variant], ws.num_splits, ws.buf.data_ptr(), ws.nbytes, None, ws.status.data_ptr(),
+            torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert rc == 0
+        assert ws.read_status() == L.STATUS_WAIT_TIMEOUT, variant
+        assert 0.5 < dt < 5.0, dt
+        assert c.seq_pos.cpu().tolist() == [131] and int(step.item()) == 1
+        ref = oracle.decode_step_reference(case["q"], c.k_cache.cpu(), c.v_cache.cpu(), case["k_scale"], case["v_scale"], [131], cap)
+        assert_parity(oracle, full[:, :, :h_q].cpu(), ref, f"{variant}: own heads of the gathered tensor")
+        assert torch.isnan(full[:, :, h_q:].float()).all()            # the other rank's heads: untouched
+        slot = nbytes // 8 // 4                                      # [2 parities][2 senders][slot] packets
+        sent = silent_peer.view(2, 2, slot)[1, 0]                    # step 1 is odd; this rank is sender 0
+        assert bool(((sent >> 32) == 1).all()), "every packet carries the step number"
+        vals = (sent & 0xFFFFFFFF).to(torch.int32).view(torch.bfloat16).view(n_layers, batch, h_q, d)
+        assert torch.equal(vals.view(torch.int16), full[:, :, :h_q].contiguous().view(torch.int16))
+        assert int(silent_peer.view(2, 2, slot)[0].abs().max()) == 0 and int(mine.abs().max()) == 0
+        # barrier flags and packets do not mix
+        flags = (ctypes.c_void_p * 8)(mine.data_ptr(), silent_peer.data_ptr())
+        rc = L.lib().b200attn_append_decode_peers(
+            ctypes.byref(c.shape), ctypes.byref(peers), q.data_ptr(), kn.data_ptr(), vn.data_ptr(), c.k_cache.data_ptr(),
+            c.v_cache.data_ptr(), c.k_scale.data_ptr(), c.v_scale.data_ptr(), c.seq_pos.data_ptr(), 1, d ** -0.5,
+            L.VARIANTS[variant], ws.num_splits, ws.buf.data_ptr(), ws.nbytes, flags, ws.status.data_ptr(),
+            torch.cuda.current_stream().cuda_stream)
+        assert rc == L.ERR_SHAPE
+        assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+
+
+def test_reset_lifecycle_sequences(pkg, oracle, cuda_device):
+    """The reset gates of the reference's check list (scripts/m3_check.py: A -> B -> A and short -> long -> short on one
+    cache object against fresh caches): after an in-place reset a run reproduces, bit for bit, what a fresh cache gives,
+    whatever ran before it; addresses never change; stale bytes of a longer earlier run stay invisible."""
+    n_layers, batch, h_q, h_kv, d, cap = 3, 2, 40, 8, 128, 384
+    g = torch.Generator().manual_seed(31)
+    runs = {}
+    for name, depth, steps in (("A", 100, 5), ("B", 260, 9), ("short", 17, 3), ("long", 300, 40)):
+        runs[name] = {"k0": torch.randn(n_layers, batch, h_kv, depth, d, generator=g).to(torch.bfloat16).to(cuda_device),
+                      "v0": torch.randn(n_layers, batch, h_kv, depth, d, generator=g).to(torch.bfloat16).to(cuda_device),
+                      "q": torch.randn(steps, n_layers, batch, h_q, d, generator=g).to(torch.bfloat16).to(cuda_device),
+                      "kn": torch.randn(steps, n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device),
+                      "vn": torch.randn(steps, n_layers, batch, h_kv, d, generator=g).to(torch.bfloat16).to(cuda_device)}
+
+    def play(cache, run):
+        cache.prefill(run["k0"], run["v0"], calibrate=True)
+        outs = [cache.step(run["q"][i], run["kn"][i], run["vn"][i]).clone() for i in range(run["q"].shape[0])]
+        torch.cuda.synchronize()
+        assert cache.workspace.read_status() == 0
+        return outs
+
+    for variant in ("mma", "umma2"):
+        fresh = {}
+        for name, run in runs.items():
+            fresh[name] = play(pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant=variant), run)
+        one = pkg.FP8StaticCache(n_layers, batch, h_q, h_kv, d, cap, device=cuda_device, variant=variant)
+        ptrs = (one.k_cache.data_ptr(), one.v_cache.data_ptr(), one.seq_pos.data_ptr())
+        for name in ("A", "B", "A", "short", "long", "short"):
+            one.reset()
+            got = play(one, runs[name])
+            assert (one.k_cache.data_ptr(), one.v_cache.data_ptr(), one.seq_pos.data_ptr()) == ptrs
+            for i, (a, b) in enumerate(zip(got, fresh[name])):
+                assert torch.equal(a.view(torch.int16), b.view(torch.int16)), (variant, name, i)
+
+
+def test_canary_words_around_every_buffer_the_kernels_write(pkg, oracle, cuda_device):
+    """Every buffer a launch may write — output, workspace (partials, tickets, exit counter), status word, cache,
+    positions — sits between guard regions filled with a pattern; lengths 1..160 (every position inside and across
+    the 64- and 128-token tiles) x several CTA counts, attention alone and the fused step, both tensor-core kernels:
+    the guards must come back untouched and the results must match the oracle.  (Stand-in for a memory checker.)"""
+    n_layers, h_q, h_kv, d, cap, guard = 2, 40, 8, 128, 192, 4096
+    dev = cuda_device
+
+    class Guarded:
+        def __init__(self, nbytes):
+            self.nbytes = (nbytes + 255) // 256 * 256
+            self.raw = torch.full((self.nbytes + 2 * guard,), 0xA5, dtype=torch.uint8, device=dev)
+            self.body = self.raw[guard:guard + self.nbytes]
+
+        def view(self, dtype, shape):
+            n = int(torch.tensor(shape).prod()) * torch.empty(0, dtype=dtype).element_size()
+            return self.body[:n].view(dtype).view(shape)
+
+        def intact(self, used_bytes):
+            tail = self.raw[guard + used_bytes:]
+            return bool((self.raw[:guard] == 0xA5).all()) and bool((tail == 0xA5).all())
+
+    g = torch.Generator().manual_seed(77)
+    kn = torch.randn(n_layers, 1, h_kv, d, generator=g).to(torch.bfloat16).to(dev)
+    vn = torch.randn(n_layers, 1, h_kv, d, generator=g).to(torch.bfloat16).to(dev)
+    for L in list(range(1, 161, 3)) + [63, 64, 65, 127, 128, 129, 160]:
+        case = build_case(oracle, n_layers, 1, h_q, h_kv, d, [L], cap, seed=500 + L, fill_byte=0xFF)
+        clean_k, clean_v = case["k_cache"].clone(), case["v_cache"].clone()
+        clean_k[:, :, :, L:] = 0
+        clean_v[:, :, :, L:] = 0
+        ref = oracle.decode_step_reference(case["q"], clean_k, clean_v, case["k_scale"], case["v_scale"], [L], cap)
+        for variant, ctas in (("mma", 0), ("mma", 5), ("mma", 37), ("umma2", 0), ("umma2", 3), ("umma2", 148)):
+            cache_bytes = n_layers * h_kv * cap * d
+            gk, gv = Guarded(cache_bytes), Guarded(cache_bytes)
+            kc, vc = gk.view(torch.uint8, (n_layers, 1, h_kv, cap, d)), gv.view(torch.uint8, (n_layers, 1, h_kv, cap, d))
+            kc.copy_(case["k_cache"]); vc.copy_(case["v_cache"])
+            ks, vs = case["k_scale"].to(dev), case["v_scale"].to(dev)
+            shape = pkg.make_shape(h_q, kc, vc, ks)
+            n = ctas or pkg.pick_splits(shape, variant=variant)
+            ws_bytes = pkg.workspace_bytes(shape, n, variant)
+            gw, go, gs, gp = Guarded(ws_bytes), Guarded(n_layers * h_q * d * 2), Guarded(4), Guarded(4)
+            ws = pkg.Workspace(shape, dev, variant=variant, num_splits=n)
+            ws.buf, ws.nbytes = gw.body[:ws_bytes], ws_bytes           # the library's workspace, between guards
+            ws.status = gs.view(torch.int32, (1,))
+            ws.status.zero_()
+            ws.init()
+            out = go.view(torch.bfloat16, (n_layers, 1, h_q, d))
+            pos = gp.view(torch.int32, (1,))
+            pos.fill_(L)
+            q = case["q"].to(dev)
+            pkg.decode_attention(q, kc, vc, ks, vs, pos, workspace=ws, out=out)
+            torch.cuda.synchronize()
+            what = f"L={L} {variant} ctas={n}"
+            assert ws.read_status() == 0, what
+            assert_parity(oracle, out.cpu(), ref, what)
+            if L < cap:
+                pkg.append_decode(q, kn, vn, kc, vc, ks, vs, pos, workspace=ws, out=out)
+                torch.cuda.synchronize()
+                assert ws.read_status() == 0 and int(pos.item()) == L + 1, what
+            for name, gd, used in (("k cache", gk, cache_bytes), ("v cache", gv, cache_bytes), ("workspace", gw, ws_bytes),
+                                   ("output", go, n_layers * h_q * d * 2), ("status", gs, 4), ("positions", gp, 4)):
+                assert gd.intact(used), f"{what}: guard words of the {name} overwritten"
