@@ -629,23 +629,42 @@ __device__ __forceinline__ Unpack unpack_of(const MmaParams& p, int step) {
 }
 __device__ __noinline__ void unpack_packets(Unpack u, int part, int parts, int tid, int nthreads) {
   // 32-bit index arithmetic: the host refuses staging buffers of 2^31 packets or more
+  constexpr int U = 8;   // packets a thread has in flight: one L2 round trip per U packets, not per packet (a small
+                         // shard of a short cache runs on few CTAs, and each of its threads has a dozen packets to wait for)
   const uint32_t slot = (uint32_t)u.slot_words, total = (uint32_t)(u.n_out - 1) * slot;
   const uint32_t t0 = (uint32_t)((unsigned long long)part * total / parts), t1 = (uint32_t)(((unsigned long long)part + 1) * total / parts);
   const unsigned long long start = global_timer_ns();
-  for (uint32_t t = t0 + tid; t < t1; t += nthreads) {
-    const uint32_t si = t / slot, w = t - si * slot;
-    const uint32_t s = si < (uint32_t)u.rank ? si : si + 1;
-    const unsigned long long* src = u.src + (size_t)s * slot + w;
-    unsigned long long v;
-    bool ok = false;
-    for (int tries = 0;; ++tries) {
-      asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(src) : "memory");
-      if ((int)(v >> 32) == u.step) { ok = true; break; }
-      if ((tries & 63) == 63 && global_timer_ns() - start > kBarrierBudgetNs) break;
+  for (uint32_t base = t0 + tid; base < t1; base += (uint32_t)nthreads * U) {
+    uint32_t sender[U], word[U];
+    unsigned long long v[U];
+    uint32_t pending = 0;
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const uint32_t t = base + (uint32_t)i * nthreads;
+      if (t < t1) {
+        const uint32_t si = t / slot;
+        word[i] = t - si * slot;
+        sender[i] = si < (uint32_t)u.rank ? si : si + 1;
+        pending |= 1u << i;
+      }
     }
-    if (!ok) { atomicOr(u.status, B200ATTN_STATUS_WAIT_TIMEOUT); return; }
-    const uint32_t row = w / (uint32_t)u.row_words, rem = w - row * (uint32_t)u.row_words;
-    *reinterpret_cast<uint32_t*>(u.out + (long long)row * u.out_row + (size_t)s * u.row_words * 2 + rem * 2) = (uint32_t)v;
+    for (int tries = 0; pending; ++tries) {
+#pragma unroll
+      for (int i = 0; i < U; ++i)
+        if (pending & (1u << i))
+          asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v[i]) : "l"(u.src + (size_t)sender[i] * slot + word[i]) : "memory");
+#pragma unroll
+      for (int i = 0; i < U; ++i)
+        if ((pending & (1u << i)) && (int)(v[i] >> 32) == u.step) {
+          pending &= ~(1u << i);
+          const uint32_t row = word[i] / (uint32_t)u.row_words, rem = word[i] - row * (uint32_t)u.row_words;
+          *reinterpret_cast<uint32_t*>(u.out + (long long)row * u.out_row + (size_t)sender[i] * u.row_words * 2 + rem * 2) = (uint32_t)v[i];
+        }
+      if (pending && (tries & 63) == 63 && global_timer_ns() - start > kBarrierBudgetNs) {
+        atomicOr(u.status, B200ATTN_STATUS_WAIT_TIMEOUT);
+        return;
+      }
+    }
   }
 }
 
