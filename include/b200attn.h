@@ -45,6 +45,8 @@ extern "C" {
 #define B200ATTN_STATUS_LEN_OVER_CAP     2  /* seq_len[b] > capacity: clamped to capacity */
 #define B200ATTN_STATUS_WAIT_TIMEOUT     4  /* a bounded wait on a copy barrier ran out */
 #define B200ATTN_STATUS_LEN_NEGATIVE     8  /* seq_len[b] < 0: treated as 0 */
+#define B200ATTN_STATUS_BOUNDS          16  /* index-checking build only (-DB200ATTN_BOUNDS=1): a kernel computed an index
+                                               outside its buffer (reported, never trapped) */
 
 /* kernel variants for b200attn_decode */
 #define B200ATTN_VARIANT_AUTO     0   /* the library's default (the fastest validated variant) */
@@ -131,6 +133,9 @@ size_t b200attn_peer_staging_bytes(const B200AttnShape* shape, int n_peers);
 
 /* Library version (B200ATTN_VERSION of the build). */
 int b200attn_version(void);
+
+/* 1 if this is the index-checking build (-DB200ATTN_BOUNDS=1), else 0. */
+int b200attn_bounds_checked(void);
 
 /* Hash of the sources the library was compiled from ("" for a build that did not record one); a
  * loader compares it with the sources beside the library to refuse a stale binary. */

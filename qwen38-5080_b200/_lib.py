@@ -10,14 +10,16 @@ import os
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
-LIB_PATH = PKG_DIR / "libb200attn.so"
+# B200ATTN_BOUNDS=1: the index-checking build of the same sources (build.py --bounds), for chasing a memory error
+BOUNDS = os.environ.get("B200ATTN_BOUNDS") == "1"
+LIB_PATH = PKG_DIR / ("libb200attn_bounds.so" if BOUNDS else "libb200attn.so")
 
 c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_longlong
 
 # host-side error codes / status bits / variants (include/b200attn.h)
 OK = 0
 ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_WORKSPACE, ERR_SPLITS, ERR_CUDA, ERR_CAPACITY, ERR_VARIANT, ERR_TOO_LARGE = range(-1, -10, -1)
-STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEGATIVE = 1, 2, 4, 8
+STATUS_POS_AT_CAPACITY, STATUS_LEN_OVER_CAP, STATUS_WAIT_TIMEOUT, STATUS_LEN_NEGATIVE, STATUS_BOUNDS = 1, 2, 4, 8, 16
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA2 = 0, 1, 2, 4
 VARIANTS = {"auto": VARIANT_AUTO, "simt": VARIANT_SIMT, "mma": VARIANT_MMA, "umma2": VARIANT_UMMA2}
 SCALE_PER_HEAD, SCALE_PER_TOKEN = 0, 1
@@ -40,6 +42,7 @@ class B200AttnPeerOut(ctypes.Structure):
 # name -> (restype, argtypes); every symbol include/b200attn.h declares
 PROTOTYPES = {
     "b200attn_version": (c_int, []),
+    "b200attn_bounds_checked": (c_int, []),
     "b200attn_source_hash": (ctypes.c_char_p, []),
     "b200attn_error_string": (ctypes.c_char_p, [c_int]),
     "b200attn_last_cuda_error": (c_int, []),
@@ -101,8 +104,8 @@ def lib() -> ctypes.CDLL:
         return _lib
     from . import build as _build
     want = _build.source_hash()
-    if _build.needs_build() or os.environ.get("B200ATTN_REBUILD") == "1":
-        _build.build(force=os.environ.get("B200ATTN_REBUILD") == "1")   # raises if nvcc is missing: no fallback
+    if _build.needs_build(BOUNDS) or os.environ.get("B200ATTN_REBUILD") == "1":
+        _build.build(force=os.environ.get("B200ATTN_REBUILD") == "1", bounds=BOUNDS)   # raises if nvcc is missing: no fallback
     if not LIB_PATH.exists():
         raise RuntimeError(f"{LIB_PATH} is missing: build it with `python {PKG_DIR / 'build.py'}`")
     handle = ctypes.CDLL(str(LIB_PATH))

@@ -119,6 +119,14 @@ extern "C" {
 
 int b200attn_version(void) { return B200ATTN_VERSION; }
 
+int b200attn_bounds_checked(void) {
+#ifdef B200ATTN_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 #ifndef B200ATTN_SOURCE_HASH
 #define B200ATTN_SOURCE_HASH ""
 #endif

@@ -11,6 +11,14 @@
 
 namespace b200attn {
 
+// Index checks of the -DB200ATTN_BOUNDS=1 build: a violated condition sets B200ATTN_STATUS_BOUNDS in the status word
+// (nothing traps); the regular build compiles them away.
+#ifdef B200ATTN_BOUNDS
+#define B200ATTN_CHECK(status, cond) do { if (!(cond)) atomicOr((status), B200ATTN_STATUS_BOUNDS); } while (0)
+#else
+#define B200ATTN_CHECK(status, cond) do { } while (0)
+#endif
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kE4m3Max = 448.0f;
 constexpr int kMaxGroup = 8;  // query heads per KV head the kernels support (benchmark shape 40/8: 5, reference model 24/4: 6)

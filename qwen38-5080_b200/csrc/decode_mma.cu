@@ -57,7 +57,8 @@ __device__ __noinline__ void append_rows_by_warp(int batch, int h_kv, int capaci
                                                  long long v_layer_stride, const uint16_t* k_new, const uint16_t* v_new,
                                                  uint8_t* k_cache, uint8_t* v_cache, const float* k_scale, const float* v_scale,
                                                  const int* seq_pos, int lane, long long r0, long long r1,
-                                                 const int* sCum, const int* sLen) {
+                                                 const int* sCum, const int* sLen, int* status) {
+  (void)status;
   Cursor a = locate(r0, sCum, sLen, batch, h_kv);
   long long cur = r0;
   while (cur < r1) {
@@ -66,6 +67,7 @@ __device__ __noinline__ void append_rows_by_warp(int batch, int h_kv, int capaci
       const int pos = seq_pos[a.b];
       if (pos >= 0 && pos < capacity) {
         const long long rowi = ((long long)a.layer * batch + a.b) * h_kv + a.h;
+        B200ATTN_CHECK(status, a.b >= 0 && a.b < batch && a.h >= 0 && a.h < h_kv && a.layer >= 0 && pos / kTileT == a.tiles_b - 1);
         for (int e = lane; e < D / 2; e += 32) {   // 4 values of the K row (e < D/4) or of the V row
           const int which = e >= D / 4 ? 1 : 0, el = (e % (D / 4)) * 4;
           const uint2 raw = *reinterpret_cast<const uint2*>((which ? v_new : k_new) + rowi * D + el);
@@ -209,6 +211,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
         const uint32_t fb = full0 + 8u * s;
         mbar_arrive_expect_tx(fb, 2u * TILE_BYTES);
         const int row = (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTileT;
+        B200ATTN_CHECK(p.status, c.layer >= 0 && c.layer < g.n_layers && c.b >= 0 && c.b < g.batch && c.h >= 0 && c.h < g.h_kv &&
+                                     c.tile >= 0 && c.tile * kTileT < c.len_b && (long long)row < (long long)g.batch * g.h_kv * g.capacity);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf) {
           // K/V lines are used once: an L2 evict-first policy on the copies keeps L2 for what is used again
@@ -229,7 +233,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       // fused step: this warp is idle until the first segment ends; it appends the new rows of the pairs
       // whose last tile this CTA loads while the producer is already streaming the tiles before them
       append_rows_by_warp<D>(g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new, p.k_cache_w,
-                             p.v_cache_w, p.k_scale, p.v_scale, p.seq_len, lane, r0, r1, sCum, sLen);
+                             p.v_cache_w, p.k_scale, p.v_scale, p.seq_len, lane, r0, r1, sCum, sLen, p.status);
       if (lane == 0) mbar_arrive(appended0);
     }
     if (has_work)

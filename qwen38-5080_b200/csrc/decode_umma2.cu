@@ -122,7 +122,8 @@ __device__ __noinline__ void append_new_rows(int batch, int h_kv, int capacity, 
                                              long long v_layer_stride, const uint16_t* k_new, const uint16_t* v_new,
                                              uint8_t* k_cache, uint8_t* v_cache, float* k_scale, float* v_scale,
                                              const int* seq_pos, int tid, long long r0, long long r1,
-                                             const int* sCum, const int* sLen) {
+                                             const int* sCum, const int* sLen, int* status) {
+  (void)status;
   constexpr int VPL = D / 32;   // values per lane: 4 or 8
   const int wid = tid >> 5, lane = tid & 31;
   Cursor a = locate(r0, sCum, sLen, batch, h_kv);
@@ -159,6 +160,7 @@ __device__ __noinline__ void append_new_rows(int batch, int h_kv, int capacity, 
           }
           uint8_t* dst = (which ? v_cache : k_cache) + (long long)a.layer * (which ? v_layer_stride : k_layer_stride) +
                          (((long long)a.b * h_kv + a.h) * capacity + pos) * D + lane * VPL;
+          B200ATTN_CHECK(status, a.b >= 0 && a.b < batch && a.h >= 0 && a.h < h_kv && a.layer >= 0 && pos / kTile2 == a.tiles_b - 1);
 #pragma unroll
           for (int i = 0; i < VPL / 4; ++i)
             *reinterpret_cast<uint32_t*>(dst + 4 * i) = (uint32_t)quantize_e4m3(x[4 * i], sc) | ((uint32_t)quantize_e4m3(x[4 * i + 1], sc) << 8) |
@@ -317,6 +319,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
           need_append = false;
         }
         if (kround && !mbar_wait_lean(kempty0 + 8u * ks, (kround - 1) & 1, timed_out, p.status)) break;
+        B200ATTN_CHECK(p.status, c.layer >= 0 && c.layer < g.n_layers && row >= 0 && (long long)row < (long long)g.batch * g.h_kv * g.capacity &&
+                                     row == (c.b * g.h_kv + c.h) * g.capacity + c.tile * kTile2 && c.tile * kTile2 < c.len_b && ks < kstages && vs < vstages);
         mbar_arrive_expect_tx(kfull0 + 8u * ks, TILE_BYTES);
 #pragma unroll
         for (int hf = 0; hf < DH; ++hf) {
@@ -481,7 +485,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     if (p.k_new) {
       append_new_rows<D, PT>(g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new,
                              p.k_cache_w, p.v_cache_w, const_cast<float*>(p.k_scale), const_cast<float*>(p.v_scale), p.seq_len, tid,
-                             r0, r1, sCum, sLen);
+                             r0, r1, sCum, sLen, p.status);
       asm volatile("fence.proxy.async.global;" ::: "memory");   // the rows -> visible to the TMA loads of this CTA
       __syncwarp();
       if (lane == 0) mbar_arrive(appended0);

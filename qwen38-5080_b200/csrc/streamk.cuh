@@ -432,6 +432,9 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
     const long long orow = (lb * g.h_q + c.h * G) * D;
     const long long prow = (lb * p.out_hq_total + p.out_head_base + c.h * G) * D;   // row in the gathered layout
+    B200ATTN_CHECK(p.status, c.layer >= 0 && c.layer < g.n_layers && c.b >= 0 && c.b < g.batch && c.h >= 0 && c.h < g.h_kv);
+    B200ATTN_CHECK(p.status, orow >= 0 && orow + (long long)G * D <= (long long)g.n_layers * g.batch * g.h_q * D);
+    B200ATTN_CHECK(p.status, seg_end > cur && seg_end <= r1 && c.tile >= 0 && c.tile < c.tiles_b);
     if (ok) {
       for (int h = 0; h < G; ++h) {
         float mw[NW], M = -INFINITY;
@@ -474,6 +477,7 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     if (!complete && ok) {
       // ---- fused combine: the last owner of the pair to arrive merges all partials ----
       const int c_first = owner_of(pair_start, total, n_eff), c_last = owner_of(pair_end - 1, total, n_eff);
+      B200ATTN_CHECK(p.status, c_first >= 0 && c_first <= c_last && c_last < (int)gridDim.x && c_first <= (int)blockIdx.x && (int)blockIdx.x <= c_last);
       int last = 0;
       if (lane == 0) {
         // release: the warp's partial (ordered before this by __syncwarp) is visible to whoever
@@ -658,6 +662,7 @@ __device__ __noinline__ void unpack_packets(Unpack u, int part, int parts, int t
         if ((pending & (1u << i)) && (int)(v[i] >> 32) == u.step) {
           pending &= ~(1u << i);
           const uint32_t row = word[i] / (uint32_t)u.row_words, rem = word[i] - row * (uint32_t)u.row_words;
+          B200ATTN_CHECK(u.status, sender[i] < (uint32_t)u.n_out && sender[i] != (uint32_t)u.rank && row < slot / (uint32_t)u.row_words);
           *reinterpret_cast<uint32_t*>(u.out + (long long)row * u.out_row + (size_t)sender[i] * u.row_words * 2 + rem * 2) = (uint32_t)v[i];
         }
       if (pending && (tries & 63) == 63 && global_timer_ns() - start > kBarrierBudgetNs) {
