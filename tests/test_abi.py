@@ -106,6 +106,15 @@ def test_kernel_choice_is_a_pure_host_function(pkg):
     assert r(_shape(pkg, scale_mode=1)) == L.VARIANT_UMMA2                      # per-token scales, long cache
     assert r(_shape(pkg, scale_mode=1, capacity=512)) == L.VARIANT_SIMT         # per-token scales, short cache
     assert r(_shape(pkg, h_q=8, h_kv=1, batch=16, capacity=16640)) == L.VARIANT_UMMA2   # group 8
+    # KV-head shards of the benchmark shape: a quarter keeps the all-tcgen05 kernel, an eighth (28 tiles per SM) does not,
+    # unless its scales are per token (the mma.sync kernel does not take those); an eighth at depth 32768 keeps it
+    assert r(_shape(pkg, h_q=10, h_kv=2)) == L.VARIANT_UMMA2
+    assert r(_shape(pkg, h_q=5, h_kv=1)) == L.VARIANT_MMA
+    assert r(_shape(pkg, h_q=5, h_kv=1, scale_mode=1)) == L.VARIANT_UMMA2
+    assert r(_shape(pkg, h_q=5, h_kv=1, capacity=32768 + 256)) == L.VARIANT_UMMA2
+    one = _shape(pkg, h_q=5, h_kv=1)
+    assert lib.b200attn_pick_splits(ctypes.byref(one), 8192, 148, 0) == 296     # two CTAs per SM for the small shard
+    assert lib.b200attn_pick_splits(ctypes.byref(_shape(pkg)), 8192, 148, L.VARIANT_MMA) == 444
     for v in (L.VARIANT_SIMT, L.VARIANT_MMA, L.VARIANT_UMMA2):
         assert r(_shape(pkg), v) == v
     assert r(_shape(pkg, h_q=48, h_kv=8), L.VARIANT_UMMA2) == L.VARIANT_UMMA2   # group 6
