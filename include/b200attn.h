@@ -165,14 +165,16 @@ int b200attn_resolve_variant(const B200AttnShape* shape, int variant);
 
 /*
  * Bytes of workspace b200attn_decode needs for `num_splits` (as returned by
- * b200attn_pick_splits, or larger).  The workspace holds split-K partials
- * (m, l, acc[G][D] in fp32) and the arrival tickets of the fused combine.
+ * b200attn_pick_splits, or larger).  The workspace holds the split-K partials (m, l, acc[G][D] in
+ * fp32; the stream-K kernels keep each value in an 8-byte word with a tag that tells the CTA finishing the
+ * pair that it has arrived) and the CTA counter of the one-launch step.
  */
 int b200attn_workspace_bytes(const B200AttnShape* shape, int num_splits, int variant, size_t* bytes);
 
 /*
- * Zero the workspace (tickets must start at zero; the kernels leave them at zero again).
- * Call once after allocation and after any call that reported a status error.
+ * Zero the workspace (the partial words and the counter must start at zero; a launch that ends without a
+ * status error leaves them at zero again).  Call once after allocation and after any call that reported a
+ * status error.
  */
 int b200attn_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
@@ -311,7 +313,7 @@ int b200attn_peer_barrier(void* const* flags, int rank, int world, int* status, 
  * b200attn_decode without a caller workspace (no counterpart in the reference: its fused kernel
  * takes its scratch from torch's allocator).  For hosts that may not allocate device memory where
  * they call the library — memory owned and budgeted by a framework pool, or a step that cannot
- * afford cudaMalloc's device synchronisation.  The split-K partials and tickets of the tensor-core
+ * afford cudaMalloc's device synchronisation.  The split-K partials of the tensor-core
  * stream-K kernel (B200ATTN_VARIANT_MMA) live in a fixed 4 MiB array inside the library image
  * (b200attn_static_scratch_bytes()), held by every GPU that loads the library until exit.
  *   - a request whose workspace would not fit returns B200ATTN_ERR_TOO_LARGE, nothing launched

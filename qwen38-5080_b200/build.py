@@ -4,7 +4,7 @@
 
 --bounds builds libb200attn_bounds.so instead: the same sources with -DB200ATTN_BOUNDS=1, in which
 the kernels check the indices of their global-memory accesses (cache rows, copy coordinates, partial
-slots, tickets, output and packet positions) and report a violation as B200ATTN_STATUS_BOUNDS in the
+slots and their owners, output and packet positions) and report a violation as B200ATTN_STATUS_BOUNDS in the
 status word (never a trap).  Setting B200ATTN_BOUNDS=1 in the environment makes the package load it.
 """
 from __future__ import annotations

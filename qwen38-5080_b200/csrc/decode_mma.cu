@@ -118,7 +118,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   float* sML = sDump + kDumpBufs * kConsumerWarps * dump_warp_floats;                         // [2][4][16]: m[8], l[8]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sML + kDumpBufs * kConsumerWarps * 16);
   unsigned long long* sPeer = reinterpret_cast<unsigned long long*>(bars + 2 * stages + 9);   // [8], see fill_peer_table
-  int* sFlags = reinterpret_cast<int*>(sPeer + 8);                                    // [0] timed_out [2] any_empty [3] copies
+  DeferredCombine* sComb = reinterpret_cast<DeferredCombine*>(sPeer + 8);             // the pair this CTA finishes at its end
+  int* sFlags = reinterpret_cast<int*>(sComb + 1);                                    // [0] timed_out [2] any_empty [3] copies
   int* sLen = sFlags + 4;                                                             // [batch]
   int* sCum = sLen + g.batch;                                                         // [batch+1]
   volatile int* timed_out = sFlags;
@@ -141,6 +142,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     sFlags[0] = 0; sFlags[1] = 0; sFlags[3] = 0;
+    sComb->valid = 0;
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
       int len = p.seq_len[b] + p.seq_len_offset;
@@ -237,7 +239,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       if (lane == 0) mbar_arrive(appended0);
     }
     if (has_work)
-      epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer);
+      epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer, sComb);
   } else if (has_work) {
     // ================================ consumer warps ================================
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
@@ -453,6 +455,9 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       while (!mbar_try_wait(qfull0 + 8u * qb, (last_seg >> 1) & 1) && global_timer_ns() - t0 < kWaitBudgetNs) {}
     }
   }
+  // the pair whose last piece this CTA holds: all warps collect the other pieces (they end when this CTA's range does)
+  if (sComb->valid && !sFlags[0]) combine_deferred<D>(combine_args_of(p, sPeer), *sComb, warp, kThreads / 32, lane);
+  if (p.bar_world) __syncthreads();   // stores mode: every warp's peer stores are fenced before the CTA counts as finished
   end_of_launch(p, tid, kThreads);
 }
 
@@ -467,6 +472,7 @@ size_t smem_bytes_for(const Geometry& g, int stages) {
   b += (size_t)kDumpBufs * kConsumerWarps * 16 * 4;                   // their m, l
   b += (size_t)(2 * stages + 9) * 8;                          // barriers
   b += 64;                                                    // destinations of the tensor-parallel output
+  b += sizeof(DeferredCombine);                               // the pair finished at the CTA's end
   b += 16;                                                    // flags
   b += (size_t)(2 * g.batch + 1) * 4;                         // sLen, sCum
   return (b + 15) & ~(size_t)15;
@@ -475,10 +481,8 @@ size_t smem_bytes_for(const Geometry& g, int stages) {
 }  // namespace
 
 size_t mma_workspace_bytes(const Geometry& g, int num_ctas) {
-  const size_t pairs = (size_t)g.n_layers * g.batch * g.h_kv;
-  size_t b = (size_t)num_ctas * 2 * g.group * g.head_dim * sizeof(float);   // ws_acc
-  b += (size_t)num_ctas * 2 * 16 * sizeof(float);                            // ws_ml
-  b += (pairs + 1) * sizeof(int);                                            // tickets, exit counter of the fused step
+  size_t b = (size_t)num_ctas * 2 * partial_slot_words(g.group, g.head_dim) * 8;   // two tagged partials per CTA
+  b += 16;                                                                            // exit counter of the fused step
   return (b + 255) & ~(size_t)255;
 }
 
@@ -520,9 +524,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.seq_len_offset = a.seq_len_offset;
   p.score_scale = a.softmax_scale * kLog2e;
   const int n = a.num_splits;
-  p.ws_acc = (float*)a.workspace;
-  p.ws_ml = p.ws_acc + (size_t)n * 2 * g.group * g.head_dim;
-  p.tickets = (int*)(p.ws_ml + (size_t)n * 2 * 16);
+  p.ws_pkt = (unsigned long long*)a.workspace;
   p.out = (uint16_t*)a.out;
   p.gate = (const uint16_t*)a.gate;
   p.n_out = a.n_out;
@@ -541,7 +543,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
   p.k_cache_w = (uint8_t*)a.k_cache;
   p.v_cache_w = (uint8_t*)a.v_cache;
   p.seq_pos = a.seq_pos;
-  p.exit_count = p.tickets + (size_t)g.n_layers * g.batch * g.h_kv;
+  p.exit_count = (int*)(p.ws_pkt + (size_t)n * 2 * partial_slot_words(g.group, g.head_dim));
   for (int r = 0; r < 8; ++r) p.bar_flags[r] = r < a.bar_world ? a.bar_flags[r] : nullptr;
   p.bar_rank = a.bar_rank;
   p.bar_world = a.bar_world;

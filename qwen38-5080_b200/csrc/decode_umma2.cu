@@ -107,6 +107,7 @@ __host__ __device__ inline size_t umma2_fixed_bytes(int group, int head_dim, int
   b += (size_t)kGroups2 * 16 * 4;                                    // their m, l
   b += (size_t)(4 + 2 * kQRing2 + 4 * kGroups2 + 3) * 8;             // fixed barriers
   b += 64;                                                           // destinations of the tensor-parallel output
+  b += sizeof(DeferredCombine);                                      // the pair finished at the CTA's end
   b += 32;                                                           // flags
   b += (size_t)(2 * batch + 1) * 4;
   return b;
@@ -224,7 +225,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   const uint32_t dfull0 = pvdone0 + 8u * NG, dempty0 = dfull0 + 8u, appended0 = dempty0 + 8u;
   constexpr int kFixedBars = 4 + 2 * kQRing2 + 4 * NG + 3;
   unsigned long long* sPeer = reinterpret_cast<unsigned long long*>(bars + kFixedBars + 2 * kstages + 2 * vstages);   // [8], see fill_peer_table
-  int* sFlags = reinterpret_cast<int*>(sPeer + 8);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
+  DeferredCombine* sComb = reinterpret_cast<DeferredCombine*>(sPeer + 8);   // the pair this CTA finishes at its end
+  int* sFlags = reinterpret_cast<int*>(sComb + 1);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
   int* sLen = sFlags + 8;
   int* sCum = sLen + g.batch;
   volatile int* timed_out = sFlags;
@@ -246,6 +248,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     sFlags[0] = 0; sFlags[3] = 0; sFlags[4] = 0; sFlags[5] = 0; sFlags[6] = 0; sFlags[7] = 0;
+    sComb->valid = 0;
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
       int len = p.seq_len[b] + p.seq_len_offset;
@@ -349,7 +352,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     }
   } else if (warp == kEpilogue2) {
     if (has_work)
-      epilogue_warp<D, 1, NG, true, PT>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer);
+      epilogue_warp<D, 1, NG, true, PT>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer, sComb);
   } else if (warp == kIssuerS2) {
     // ===================== S issuer warp: query operand, S = K q^T =====================
     if (has_work) {
@@ -721,6 +724,9 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  // the pair whose last piece this CTA holds: all warps collect the other pieces (they end when this CTA's range does)
+  if (sComb->valid && !sFlags[0]) combine_deferred<D>(combine_args_of(p, sPeer), *sComb, warp, kThreads2 / 32, lane);
+  if (p.bar_world) __syncthreads();   // stores mode: every warp's peer stores are fenced before the CTA counts as finished
   end_of_launch(p, tid, kThreads2);
 }
 
@@ -770,9 +776,7 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   p.seq_len_offset = a.seq_len_offset;
   p.score_scale = a.softmax_scale * kLog2e;
   const int n = a.num_splits;
-  p.ws_acc = (float*)a.workspace;
-  p.ws_ml = p.ws_acc + (size_t)n * 2 * g.group * g.head_dim;
-  p.tickets = (int*)(p.ws_ml + (size_t)n * 2 * 16);
+  p.ws_pkt = (unsigned long long*)a.workspace;
   p.out = (uint16_t*)a.out;
   p.gate = (const uint16_t*)a.gate;
   p.n_out = a.n_out;
@@ -790,7 +794,7 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
   p.k_cache_w = (uint8_t*)a.k_cache;
   p.v_cache_w = (uint8_t*)a.v_cache;
   p.seq_pos = a.seq_pos;
-  p.exit_count = p.tickets + (size_t)g.n_layers * g.batch * g.h_kv;
+  p.exit_count = (int*)(p.ws_pkt + (size_t)n * 2 * partial_slot_words(g.group, g.head_dim));
   for (int r = 0; r < 8; ++r) p.bar_flags[r] = r < a.bar_world ? a.bar_flags[r] : nullptr;
   p.bar_rank = a.bar_rank;
   p.bar_world = a.bar_world;

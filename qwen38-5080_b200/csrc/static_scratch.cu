@@ -4,21 +4,21 @@
 // serving loop whose device memory is owned and budgeted by the framework's pool (an extra
 // cudaMalloc would bypass the accounting and can fail under fragmentation), or a latency-critical
 // step where cudaMalloc's implicit device synchronisation is not acceptable.  For them the
-// split-K partials and arrival tickets of the tensor-core stream-K kernel live in a fixed
+// split-K partials of the tensor-core stream-K kernel live in a fixed
 // array inside the library image instead of a caller-provided workspace.
 //
 // The array is per GPU (every device that loads the library holds kStaticScratchBytes until the
 // process exits) and shared by all calls on that GPU: two calls that overlap on the device (two
-// streams, two threads) would race on it — serialise them.  It keeps the previous call's
-// contents; the only part that must start at zero, the ticket area, is cleared on the caller's
-// stream by every call.
+// streams, two threads) would race on it — serialise them.  The kernel needs the part it uses
+// zeroed and leaves it so; every call clears that part on the caller's stream all the same, so
+// that a launch that ended in a time-out cannot leave anything behind for the next one.
 #include <mutex>
 
 #include "common.cuh"
 
 namespace {
 
-constexpr size_t kStaticScratchBytes = 4u << 20;   // 4 MiB: 444 CTAs x 2 partials x (5 x 128 + 16) floats = 2.3 MiB + tickets
+constexpr size_t kStaticScratchBytes = 4u << 20;   // 4 MiB: 296 CTAs x 2 partials x (5 x 128 + 16) tagged 8-byte words = 3.0 MiB
 constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
@@ -65,10 +65,7 @@ extern "C" int b200attn_decode_static(const B200AttnShape* shape, const void* q,
   void* scratch = nullptr;
   cudaError_t e = scratch_address(&scratch);   // first call on a device: looks the address up
   if (e != cudaSuccess) return b200attn::record_cuda_error(e);
-  // tickets sit at the end of the workspace layout: one int per (layer, sequence, kv head)
-  const size_t tickets = (size_t)g.n_layers * g.batch * g.h_kv * sizeof(int);
-  const size_t ticket_off = (size_t)num_splits * 2 * ((size_t)g.group * g.head_dim + 16) * sizeof(float);
-  e = cudaMemsetAsync((char*)scratch + ticket_off, 0, tickets, (cudaStream_t)stream);
+  e = cudaMemsetAsync(scratch, 0, need, (cudaStream_t)stream);
   if (e != cudaSuccess) return b200attn::record_cuda_error(e);
   return b200attn_decode(shape, q, k_cache, v_cache, k_scale, v_scale, seq_len, seq_len_offset, softmax_scale,
                          B200ATTN_VARIANT_MMA, num_splits, scratch, kStaticScratchBytes, out, status, stream);

@@ -26,9 +26,7 @@ struct MmaParams {
   const int* seq_len;
   int seq_len_offset;
   float score_scale;     // softmax_scale * log2(e)
-  float* ws_acc;         // [num_ctas][2][G][D]
-  float* ws_ml;          // [num_ctas][2][2][8]
-  int* tickets;          // [pairs]
+  unsigned long long* ws_pkt;   // split-K partials as tagged words, [num_ctas][2 slots][G * D + 16]: see partial_slot_words
   uint16_t* out;         // local output [n_layers][batch][h_q][D] (peer mode: unused)
   // peer mode (tensor-parallel by KV head): every result is stored into the output buffer of all
   // n_out ranks, laid out [n_layers][batch][out_hq_total][D], at head offset out_head_base
@@ -389,18 +387,167 @@ __device__ __noinline__ void send_pair(const unsigned long long* tab, int pkt, i
 }
 
 // ---------------------------------------------------------------------------------------------
+// Split-K hand-over.  A pair whose tiles are spread over the CTAs c_first .. c_last is finished by c_last, the
+// owner of its final piece.  Every owner (c_last included) leaves its piece's merged state (m, l, acc) in its own
+// workspace slot as 8-byte words {fp32 value, tag = pair + 1}: value and tag become visible together, so the
+// words need no fence, no flag and no arrival counter, and the writer is done when its stores are issued.  c_last
+// holds the pair's FINAL tiles, which are the first of its own range: it notes the pair (DeferredCombine) and
+// goes on; when its whole range is done, all its warps collect the pair's pieces (combine_deferred) — each
+// word is polled until its tag is the pair's (bounded), summed in CTA order (the result is the same from launch to
+// launch) and set back to zero, which is the state every launch must find (the workspace starts zeroed and every
+// launch that ends without a time-out leaves it so).  c_last only ever waits for CTAs of lower index, which the
+// hardware dispatches first: this cannot deadlock on a grid that is not resident all at once.  The other
+// owners reach the end of their pieces when they reach the end of their ranges, i.e. when c_last does: the
+// hand-over costs the pair one trip through L2, where the ticket scheme it replaces cost five in a row under
+// full memory load (partials, release, ticket, two dependent rounds of loads): 7-10 us at the end of a launch.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ long long partial_slot_words(int G, int D) { return (long long)G * D + 16; }   // acc, m[8], l[8]
+
+struct DeferredCombine {   // in shared memory; written by lane 0 of the epilogue warp, read after the CTA's last barrier
+  long long orow, prow;    // the pair's first output element, local and gathered layout
+  int pair, c_first, first_slot, valid;
+  float vs;
+  int pad;
+};
+
+__device__ __forceinline__ void st_tagged(unsigned long long* dst, float v, unsigned long long tag) {
+  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(dst), "l"((unsigned long long)__float_as_uint(v) | tag) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_tagged(const unsigned long long* src) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(src) : "memory");
+  return v;
+}
+
+// What combine_deferred needs of the kernel's parameters, by value (handing the parameter block itself to an
+// out-of-line function by reference would make the tile loops read their parameters through memory).
+struct CombineArgs {
+  unsigned long long* ws_pkt;
+  uint16_t* out;
+  const uint16_t* gate;
+  const unsigned long long* peer_tab;
+  int* status;
+  int G, n_out, pkt, step;
+};
+__device__ __forceinline__ CombineArgs combine_args_of(const MmaParams& p, const unsigned long long* peer_tab) {
+  return CombineArgs{p.ws_pkt, p.out, p.gate, peer_tab, p.status, p.g.group, p.n_out, p.pkt, peer_step(p)};
+}
+
+// All warps of c_last, after the CTA's last barrier.  Warp w takes heads w, w + nwarps, ...; lane j polls owner j's
+// (m, l) and every lane its UR dim pairs of every owner's accumulator, CH owners at a time, all loads of a round in
+// flight together.
+template <int D>
+__device__ __noinline__ void combine_deferred(CombineArgs a, DeferredCombine dc, int warp, int nwarps, int lane) {
+  constexpr int UR = D / 64;               // dim pairs per lane
+  constexpr int CH = 8 / UR;               // owners per round: 16 words in flight per lane
+  const long long SW = partial_slot_words(a.G, D);
+  const int c_last = (int)blockIdx.x, n = c_last - dc.c_first + 1;
+  const uint32_t tag32 = (uint32_t)(dc.pair + 1);
+  const unsigned long long t0 = global_timer_ns();
+  for (int h = warp; h < a.G; h += nwarps) {
+    // the pieces in CTA order, CH at a time, against a running maximum (one round when the pair has at most CH pieces)
+    float M = -INFINITY, ll = 0.f, ax[UR], ay[UR];
+#pragma unroll
+    for (int r = 0; r < UR; ++r) { ax[r] = 0.f; ay[r] = 0.f; }
+    for (int c0 = 0; c0 < n; c0 += CH) {
+      unsigned long long w[CH][2 * UR], wm[CH], wl[CH];
+      uint32_t pending = 0;   // bit per word of the round: CH * (2 * UR + 2) <= 32
+#pragma unroll
+      for (int i = 0; i < CH; ++i)
+        if (c0 + i < n) pending |= ((1u << (2 * UR + 2)) - 1u) << (i * (2 * UR + 2));
+      for (int tries = 0; pending; ++tries) {
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const int cc = dc.c_first + c0 + i;
+          const unsigned long long* slot = a.ws_pkt + ((long long)cc * 2 + (cc == dc.c_first ? dc.first_slot : 0)) * SW;
+          const uint32_t bit0 = i * (2 * UR + 2);
+#pragma unroll
+          for (int r = 0; r < UR; ++r) {
+            if (pending & (1u << (bit0 + 2 * r))) w[i][2 * r] = ld_tagged(slot + h * D + 2 * (lane + 32 * r));
+            if (pending & (1u << (bit0 + 2 * r + 1))) w[i][2 * r + 1] = ld_tagged(slot + h * D + 2 * (lane + 32 * r) + 1);
+          }
+          if (pending & (1u << (bit0 + 2 * UR))) wm[i] = ld_tagged(slot + (long long)a.G * D + h);
+          if (pending & (1u << (bit0 + 2 * UR + 1))) wl[i] = ld_tagged(slot + (long long)a.G * D + 8 + h);
+        }
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const uint32_t bit0 = i * (2 * UR + 2);
+#pragma unroll
+          for (int k = 0; k < 2 * UR; ++k)
+            if ((pending & (1u << (bit0 + k))) && (uint32_t)(w[i][k] >> 32) == tag32) pending &= ~(1u << (bit0 + k));
+          if ((pending & (1u << (bit0 + 2 * UR))) && (uint32_t)(wm[i] >> 32) == tag32) pending &= ~(1u << (bit0 + 2 * UR));
+          if ((pending & (1u << (bit0 + 2 * UR + 1))) && (uint32_t)(wl[i] >> 32) == tag32) pending &= ~(1u << (bit0 + 2 * UR + 1));
+        }
+        if (pending && (tries & 63) == 63 && global_timer_ns() - t0 > kWaitBudgetNs) {
+          atomicOr(a.status, B200ATTN_STATUS_WAIT_TIMEOUT);
+          return;
+        }
+      }
+      float Mn = M;
+#pragma unroll
+      for (int i = 0; i < CH; ++i)
+        if (c0 + i < n) Mn = fmaxf(Mn, __uint_as_float((uint32_t)wm[i]));
+      const float keep = M == -INFINITY ? 0.f : ex2(M - Mn);   // what is summed so far, on the new maximum's scale
+      M = Mn;
+      ll *= keep;
+#pragma unroll
+      for (int r = 0; r < UR; ++r) { ax[r] *= keep; ay[r] *= keep; }
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        if (c0 + i < n) {
+          const int cc = dc.c_first + c0 + i;
+          unsigned long long* slot = a.ws_pkt + ((long long)cc * 2 + (cc == dc.c_first ? dc.first_slot : 0)) * SW;
+          B200ATTN_CHECK(a.status, cc >= 0 && cc <= c_last && cc < (int)gridDim.x);
+          const float mc = __uint_as_float((uint32_t)wm[i]);
+          const float f = mc == -INFINITY ? 0.f : ex2(mc - M);
+          ll += __uint_as_float((uint32_t)wl[i]) * f;
+#pragma unroll
+          for (int r = 0; r < UR; ++r) {
+            ax[r] += __uint_as_float((uint32_t)w[i][2 * r]) * f;
+            ay[r] += __uint_as_float((uint32_t)w[i][2 * r + 1]) * f;
+            // 16 bytes of zeros: the two words are consumed
+            *reinterpret_cast<ulonglong2*>(slot + h * D + 2 * (lane + 32 * r)) = make_ulonglong2(0ull, 0ull);
+          }
+          if (lane == 0) { slot[(long long)a.G * D + h] = 0ull; slot[(long long)a.G * D + 8 + h] = 0ull; }
+        }
+      }
+    }
+    const float inv = ll > 0.f ? dc.vs / ll : 0.f;
+    uint32_t words[UR];
+#pragma unroll
+    for (int r = 0; r < UR; ++r) {
+      const long long idx = dc.orow + h * D + 2 * (lane + 32 * r);
+      __nv_bfloat162 ob = __floats2bfloat162_rn(ax[r] * inv, ay[r] * inv);
+      if (a.gate) {   // as out_bits
+        const uint32_t gw = *reinterpret_cast<const uint32_t*>(a.gate + idx);
+        const float g0 = bf16_bits_to_float(gw & 0xFFFFu), g1 = bf16_bits_to_float(gw >> 16);
+        const __nv_bfloat162 sg = __floats2bfloat162_rn(__fdiv_rn(1.f, 1.f + expf(-g0)), __fdiv_rn(1.f, 1.f + expf(-g1)));
+        ob = __floats2bfloat162_rn(__low2float(ob) * __low2float(sg), __high2float(ob) * __high2float(sg));
+      }
+      words[r] = *reinterpret_cast<uint32_t*>(&ob);
+      if (a.n_out == 0) *reinterpret_cast<uint32_t*>(a.out + idx) = words[r];
+    }
+    if (a.n_out) {
+      send_pair<D>(a.peer_tab, a.pkt, a.step, words, 1, dc.orow + h * D, dc.prow + h * D, a.out, lane);
+      if (!a.pkt) __threadfence_system();   // stores mode: see the end of epilogue_warp
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // epilogue warp: walks the CTA's segments in the consumers' order.  For each it waits for the
 // NW dumped states (m[8], l[8], acc[G][D]; head rows in the xor layout of dump_pos, or in plain
 // dim order when PLAIN), merges them (UNIT_V: the V scales are already in the accumulators: per-token layout),
-// and either writes the normalised bf16 output (pair fully owned by this CTA) or writes an
-// (m, l, acc) partial, takes an arrival ticket and, if it is the last owner to arrive, merges all
-// partials of the pair in CTA order and resets the ticket.
+// and either writes the normalised bf16 output (pair fully owned by this CTA) or leaves the merged state in the
+// CTA's workspace slot as tagged words; if the piece is the pair's last one, it notes the pair in `deferred` for
+// combine_deferred.
 // ---------------------------------------------------------------------------------------------
 template <int D, int NDUMP, int NW = kConsumerWarps, bool PLAIN = false, bool UNIT_V = false>
 __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long long r0, long long r1,
                                               long long total, int n_eff, const int* sCum, const int* sLen,
                                               const float* sDump, const float* sML, uint32_t dfull0,
-                                              uint32_t dempty0, volatile int* timed_out, const unsigned long long* peer_tab) {
+                                              uint32_t dempty0, volatile int* timed_out, const unsigned long long* peer_tab,
+                                              DeferredCombine* deferred) {
   constexpr int DP = D + 4;                // padded head row of a dumped state, in floats
   constexpr int UR = D / 64;               // dim pairs per epilogue lane
   const Geometry& g = p.g;
@@ -428,8 +575,8 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
     const float* dump = sDump + db * NW * dump_warp_floats;
     const float* ml = sML + db * NW * 16;
     const int slot = cur == r0 ? 0 : 1;
-    float* pacc = p.ws_acc + ((long long)blockIdx.x * 2 + slot) * G * D;
-    float* pml = p.ws_ml + ((long long)blockIdx.x * 2 + slot) * 16;
+    unsigned long long* pslot = p.ws_pkt + ((long long)blockIdx.x * 2 + slot) * partial_slot_words(G, D);
+    const unsigned long long tag = (unsigned long long)(uint32_t)(pair + 1) << 32;
     const long long orow = (lb * g.h_q + c.h * G) * D;
     const long long prow = (lb * p.out_hq_total + p.out_head_base + c.h * G) * D;   // row in the gathered layout
     B200ATTN_CHECK(p.status, c.layer >= 0 && c.layer < g.n_layers && c.b >= 0 && c.b < g.batch && c.h >= 0 && c.h < g.h_kv);
@@ -465,84 +612,27 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
           }
         } else {
 #pragma unroll
-          for (int r = 0; r < UR; ++r)
-            *reinterpret_cast<float2*>(pacc + h * D + 2 * (lane + 32 * r)) = make_float2(ax[r], ay[r]);
-          if (lane == 0) { pml[h] = M; pml[8 + h] = ll; }
+          for (int r = 0; r < UR; ++r) {
+            st_tagged(pslot + h * D + 2 * (lane + 32 * r), ax[r], tag);
+            st_tagged(pslot + h * D + 2 * (lane + 32 * r) + 1, ay[r], tag);
+          }
+          if (lane == 0) { st_tagged(pslot + G * D + h, M, tag); st_tagged(pslot + G * D + 8 + h, ll, tag); }
         }
       }
       if (complete && p.n_out) send_pair<D>(peer_tab, p.pkt, step, obuf, G, orow, prow, p.out, lane);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(dempty0 + 8u * db);   // the dump buffer may be overwritten
-    if (!complete && ok) {
-      // ---- fused combine: the last owner of the pair to arrive merges all partials ----
-      const int c_first = owner_of(pair_start, total, n_eff), c_last = owner_of(pair_end - 1, total, n_eff);
-      B200ATTN_CHECK(p.status, c_first >= 0 && c_first <= c_last && c_last < (int)gridDim.x && c_first <= (int)blockIdx.x && (int)blockIdx.x <= c_last);
-      int last = 0;
+    if (!complete && ok && seg_end == pair_end) {
+      // the pair's last piece: this CTA finishes the pair when its own range is done
+      const int c_first = owner_of(pair_start, total, n_eff);
+      B200ATTN_CHECK(p.status, c_first >= 0 && c_first < (int)blockIdx.x && owner_of(pair_end - 1, total, n_eff) == (int)blockIdx.x && cur == r0);
       if (lane == 0) {
-        // release: the warp's partial (ordered before this by __syncwarp) is visible to whoever
-        // reads the ticket after us; acquire: if we are last, the other owners' partials are
-        // visible to the loads below (passed on to the other lanes by the shuffle).
-        int ticket;
-        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.tickets + pair) : "memory");
-        last = ticket == c_last - c_first;
-      }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      __syncwarp();   // orders lane 0's acquire before the other lanes' loads
-      if (last) {
-        const int first_slot = (long long)c_first * total / n_eff < pair_start ? 1 : 0;
-        float M[kMaxGroup];
-#pragma unroll
-        for (int h = 0; h < kMaxGroup; ++h) M[h] = -INFINITY;
-#pragma unroll 4
-        for (int cc = c_first; cc <= c_last; ++cc) {
-          const float* cml = p.ws_ml + ((long long)cc * 2 + (cc == c_first ? first_slot : 0)) * 16;
-#pragma unroll
-          for (int h = 0; h < kMaxGroup; ++h)
-            if (h < G) M[h] = fmaxf(M[h], __ldcg(cml + h));
-        }
-        float ll[kMaxGroup], ax[kMaxGroup][UR], ay[kMaxGroup][UR];
-#pragma unroll
-        for (int h = 0; h < kMaxGroup; ++h) {
-          ll[h] = 0.f;
-#pragma unroll
-          for (int r = 0; r < UR; ++r) { ax[h][r] = 0.f; ay[h][r] = 0.f; }
-        }
-#pragma unroll 2
-        for (int cc = c_first; cc <= c_last; ++cc) {
-          const int sl = cc == c_first ? first_slot : 0;
-          const float* cml = p.ws_ml + ((long long)cc * 2 + sl) * 16;
-          const float* cacc = p.ws_acc + ((long long)cc * 2 + sl) * G * D;
-#pragma unroll
-          for (int h = 0; h < kMaxGroup; ++h) {
-            if (h < G) {
-              const float mc = __ldcg(cml + h);
-              const float f = mc == -INFINITY ? 0.f : ex2(mc - M[h]);
-              ll[h] += __ldcg(cml + 8 + h) * f;
-#pragma unroll
-              for (int r = 0; r < UR; ++r) {
-                const float2 v = __ldcg(reinterpret_cast<const float2*>(cacc + h * D + 2 * (lane + 32 * r)));
-                ax[h][r] += v.x * f;
-                ay[h][r] += v.y * f;
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < kMaxGroup; ++h) {
-          if (h < G) {
-            const float inv = ll[h] > 0.f ? vs / ll[h] : 0.f;
-#pragma unroll
-            for (int r = 0; r < UR; ++r) {
-              const long long idx = orow + h * D + 2 * (lane + 32 * r);
-              const uint32_t bits = out_bits(p, idx, ax[h][r] * inv, ay[h][r] * inv);
-              if (p.n_out == 0) *reinterpret_cast<uint32_t*>(p.out + idx) = bits;
-              else obuf[h * UR + r] = bits;
-            }
-          }
-        }
-        if (p.n_out) send_pair<D>(peer_tab, p.pkt, step, obuf, G, orow, prow, p.out, lane);
-        if (lane == 0) p.tickets[pair] = 0;   // ready for the next launch
+        deferred->orow = orow; deferred->prow = prow;
+        deferred->pair = (int)pair; deferred->c_first = c_first;
+        deferred->first_slot = (long long)c_first * total / n_eff < pair_start ? 1 : 0;
+        deferred->vs = vs;
+        deferred->valid = 1;
       }
     }
     ++seg;

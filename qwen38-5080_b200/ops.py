@@ -90,7 +90,7 @@ def workspace_bytes(shape: B200AttnShape, num_splits: int, variant: str = "auto"
 
 
 class Workspace:
-    """Split-K partials + combine tickets, allocated once (before any graph capture)."""
+    """Split-K partials (tagged words) + the step's CTA counter, allocated once (before any graph capture)."""
 
     def __init__(self, shape: B200AttnShape, device, variant: str = "auto", num_splits: int = 0,
                  max_seq_len: int | None = None):

@@ -107,7 +107,7 @@ def test_repeat_and_reset_are_bitwise_stable(pkg, oracle, cuda_device, variant):
     seq = torch.tensor(case["lens"], dtype=torch.int32, device=cuda_device)
     outs = []
     for i in range(4):
-        if i == 2:   # poison the partial area (not the tickets): stale partials must never be read
+        if i == 2:   # poison half of the partial area: what an earlier launch left there must never be taken for a partial
             ws.buf[: ws.nbytes // 2].fill_(0x7F)
         if i == 3:
             ws.init()
@@ -865,7 +865,7 @@ def test_reset_lifecycle_sequences(pkg, oracle, cuda_device):
 
 
 def test_canary_words_around_every_buffer_the_kernels_write(pkg, oracle, cuda_device):
-    """Every buffer a launch may write — output, workspace (partials, tickets, exit counter), status word, cache,
+    """Every buffer a launch may write — output, workspace (partials, CTA counter), status word, cache,
     positions — sits between guard regions filled with a pattern; lengths 1..160 (every position inside and across
     the 64- and 128-token tiles) x several CTA counts, attention alone and the fused step, both tensor-core kernels:
     the guards must come back untouched and the results must match the oracle.  (Stand-in for a memory checker.)"""
