@@ -41,12 +41,13 @@ int resolve(const B200AttnShape* s, Geometry* g) {
 // 128-token tiles, ~19 us of fixed cost per launch) takes long caches and both scale layouts (each
 // softmax thread owns one token and applies its two scales); the mma.sync kernel (three CTAs per SM,
 // 64-token tiles, finer split, per-head scales only) takes short caches, where it measured faster
-// (depth 512: 22 vs 25 us) — and small shards of long ones: below ~48 tiles per SM the fixed cost of the
-// all-tcgen05 kernel outweighs its faster streaming (one KV head of 64 layers at depth 8192, 28 tiles per
-// SM: 43.0 us against 39.0 us with the mma.sync kernel on two CTAs per SM; at 55 and 110 tiles per SM the two
-// are level, at 221 the all-tcgen05 kernel leads by 3 us).  The lengths live on the device, so the cache
-// capacity stands in for them: the all-tcgen05 kernel from 2048 token slots and 48 tiles per SM at capacity
-// (24 with per-token scales, which the mma.sync kernel does not take).  What is left (short caches with
+// (depth 512: 22 vs 25 us) — and small shards of long ones: below ~64 tiles per SM the fixed cost of the
+// all-tcgen05 kernel outweighs its faster streaming (64 layers at depth 8192 with one KV head, 28 tiles per
+// SM: 33.4 us against 32.3 us with the mma.sync kernel on two CTAs per SM; two KV heads, 57 tiles per SM:
+// 53.2 against 51.8 us; from 110 tiles per SM the two are level, at 221 the all-tcgen05 kernel leads by 6 us).
+// The lengths live on the device, so the cache capacity stands in for them: the all-tcgen05 kernel from 2048
+// token slots and 64 tiles per SM at capacity (24 with per-token scales, which the mma.sync kernel does not
+// take).  What is left (short caches with
 // per-token scales, batches beyond 2048) goes to the CUDA-core kernel.
 // An explicit request that cannot be met is an error.
 int resolve_variant(int variant, const Geometry& g) {
@@ -54,7 +55,7 @@ int resolve_variant(int variant, const Geometry& g) {
   const bool umma2_ok = g.batch <= 2048 && umma2_supported(g);
   if (variant == B200ATTN_VARIANT_AUTO && umma2_ok && g.capacity >= 2048) {
     const long long tiles = (long long)g.n_layers * g.batch * g.h_kv * ((g.capacity + 127) / 128);
-    if (tiles >= (mma_ok ? 48LL : 24LL) * device_sms()) return B200ATTN_VARIANT_UMMA2;
+    if (tiles >= (mma_ok ? 64LL : 24LL) * device_sms()) return B200ATTN_VARIANT_UMMA2;
   }
   if (variant == B200ATTN_VARIANT_AUTO) return mma_ok ? B200ATTN_VARIANT_MMA : B200ATTN_VARIANT_SIMT;
   if (variant == B200ATTN_VARIANT_SIMT) return variant;

@@ -505,7 +505,7 @@ int mma_pick_ctas(const Geometry& g, int max_seq_len, int num_sms) {
   }
   // long caches: three CTAs per SM keep HBM busiest; a small amount of work (a KV-head shard: fewer than 256 tiles
   // per SM) runs better on two per SM, which is also the instance without the register cap (64 layers x 1 KV head
-  // at depth 8192: 444 CTAs 51.0 us, 296 CTAs 39.0 us)
+  // at depth 8192: 444 CTAs 34.4 us, 296 CTAs 32.3 us; 2 KV heads: 53.5 / 51.8 us)
   if (per_sm > 2 && pairs * tiles < 256LL * num_sms) return 2 * num_sms;
   return full;
 }

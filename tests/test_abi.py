@@ -106,9 +106,11 @@ def test_kernel_choice_is_a_pure_host_function(pkg):
     assert r(_shape(pkg, scale_mode=1)) == L.VARIANT_UMMA2                      # per-token scales, long cache
     assert r(_shape(pkg, scale_mode=1, capacity=512)) == L.VARIANT_SIMT         # per-token scales, short cache
     assert r(_shape(pkg, h_q=8, h_kv=1, batch=16, capacity=16640)) == L.VARIANT_UMMA2   # group 8
-    # KV-head shards of the benchmark shape: a quarter keeps the all-tcgen05 kernel, an eighth (28 tiles per SM) does not,
-    # unless its scales are per token (the mma.sync kernel does not take those); an eighth at depth 32768 keeps it
-    assert r(_shape(pkg, h_q=10, h_kv=2)) == L.VARIANT_UMMA2
+    # KV-head shards of the benchmark shape: a half keeps the all-tcgen05 kernel, a quarter and an eighth (55 and 28 tiles
+    # per SM) do not, unless their scales are per token (the mma.sync kernel does not take those); an eighth at depth
+    # 32768 keeps it
+    assert r(_shape(pkg, h_q=20, h_kv=4)) == L.VARIANT_UMMA2
+    assert r(_shape(pkg, h_q=10, h_kv=2)) == L.VARIANT_MMA
     assert r(_shape(pkg, h_q=5, h_kv=1)) == L.VARIANT_MMA
     assert r(_shape(pkg, h_q=5, h_kv=1, scale_mode=1)) == L.VARIANT_UMMA2
     assert r(_shape(pkg, h_q=5, h_kv=1, capacity=32768 + 256)) == L.VARIANT_UMMA2
