@@ -127,8 +127,8 @@ def _random_bytes(shape, gen, dev):
 
 
 def _big_worker(rank, world, port, ret):
-    """64 layers x 2 sequences in capacity 4096: with one KV head per rank the default choice is still the
-    all-tcgen05 kernel, and its 148 CTAs split the (layer, sequence, head) pairs.  Graph-replayed steps;
+    """64 layers x 2 sequences in capacity 4096: the persistent grids of both stream-K kernels split the (layer,
+    sequence, head) pairs of a rank's shard, so the pieces go through the split-K hand-over.  Graph-replayed steps;
     the idle gathered buffer is poisoned before every step (a step must never read or leave stale data)."""
     dist, dev, pkg = _setup(rank, world, port)
     from oracle import ref_attention as oracle
@@ -150,43 +150,47 @@ def _big_worker(rank, world, port, ret):
     one.k_cache.copy_(kc); one.v_cache.copy_(vc); one.set_scales(ks, vs)
     one.seq_pos.copy_(torch.tensor(lens, dtype=torch.int32))
     want = [one.step(q, kn[i], vn[i]).clone() for i in range(steps)]
-    # this rank's heads, one graph-replayed launch per step with the gather and the barrier inside
-    mine = pkg.FP8StaticCache(n_layers, batch, h_q // world, h_kv // world, d, cap, device=dev)
-    ok = mine.workspace.resolved == "umma2" and one.workspace.resolved == "umma2"
-    mine.k_cache.copy_(kc[:, :, kv]); mine.v_cache.copy_(vc[:, :, kv]); mine.set_scales(ks[:, kv], vs[:, kv])
+    # this rank's heads, one graph-replayed launch per step with the gather inside; both stream-K kernels (the default
+    # choice depends on the shard's size: the all-tcgen05 kernel on two GPUs, the mma.sync kernel on small shards)
+    chk = _Checks()
+    chk("single GPU resolves to umma2", one.workspace.resolved == "umma2")
     start = torch.tensor(lens, dtype=torch.int32, device=dev)
     q_loc = q[:, :, qs].contiguous()
-    k_buf, v_buf = kn[0][:, :, kv].contiguous(), vn[0][:, :, kv].contiguous()
-    peer = pkg.dist.PeerOutput(q_loc, world, rank)
-
-    def launch():
-        pkg.append_decode(q_loc, k_buf, v_buf, mine.k_cache, mine.v_cache, mine.k_scale, mine.v_scale, mine.seq_pos,
-                          workspace=mine.workspace, peer_out=peer, barrier=True)
-    mine.seq_pos.copy_(start)
-    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        launch(); launch()                      # warm-up: an even number of steps keeps the buffer parity
-    torch.cuda.current_stream().wait_stream(side); torch.cuda.synchronize(); dist.barrier()
-    mine.k_cache.copy_(kc[:, :, kv]); mine.v_cache.copy_(vc[:, :, kv]); mine.seq_pos.copy_(start)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        launch()
-    torch.cuda.synchronize(); dist.barrier()
     worst = 0.0
-    for i in range(steps):
-        k_buf.copy_(kn[i][:, :, kv]); v_buf.copy_(vn[i][:, :, kv])
-        peer.poison_next()                      # the buffer this step writes holds NaN everywhere beforehand
+    for variant in ("umma2", "mma"):
+        mine = pkg.FP8StaticCache(n_layers, batch, h_q // world, h_kv // world, d, cap, device=dev, variant=variant)
+        chk(f"{variant}: resolved", mine.workspace.resolved == variant)
+        mine.k_cache.copy_(kc[:, :, kv]); mine.v_cache.copy_(vc[:, :, kv]); mine.set_scales(ks[:, kv], vs[:, kv])
+        k_buf, v_buf = kn[0][:, :, kv].contiguous(), vn[0][:, :, kv].contiguous()
+        peer = pkg.dist.PeerOutput(q_loc, world, rank)
+
+        def launch():
+            pkg.append_decode(q_loc, k_buf, v_buf, mine.k_cache, mine.v_cache, mine.k_scale, mine.v_scale, mine.seq_pos,
+                              workspace=mine.workspace, peer_out=peer, barrier=True)
+        mine.seq_pos.copy_(start)
+        side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            launch(); launch()                      # warm-up: an even number of steps keeps the buffer parity
+        torch.cuda.current_stream().wait_stream(side); torch.cuda.synchronize(); dist.barrier()
+        mine.k_cache.copy_(kc[:, :, kv]); mine.v_cache.copy_(vc[:, :, kv]); mine.seq_pos.copy_(start)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launch()
         torch.cuda.synchronize(); dist.barrier()
-        graph.replay()
-        torch.cuda.synchronize()
-        got = peer.current()
-        ok = ok and not bool(torch.isnan(got.float()).any())
-        m = oracle.error_metrics(got.cpu(), want[i].cpu())
-        worst = max(worst, m["max_abs"])
-        ok = ok and m["max_abs"] <= 2.0 ** -7 and m["cosine"] >= 0.99999
-        dist.barrier()
-    ok = ok and mine.workspace.read_status() == 0 and mine.seq_pos.cpu().tolist() == [x + steps for x in lens]
-    ok = ok and torch.equal(mine.k_cache, one.k_cache[:, :, kv]) and torch.equal(mine.v_cache, one.v_cache[:, :, kv])
+        for i in range(steps):
+            k_buf.copy_(kn[i][:, :, kv]); v_buf.copy_(vn[i][:, :, kv])
+            peer.poison_next()                      # the buffer this step writes holds NaN everywhere beforehand
+            torch.cuda.synchronize(); dist.barrier()
+            graph.replay()
+            torch.cuda.synchronize()
+            got = peer.current()
+            chk(f"{variant} step {i}: no NaN left", not bool(torch.isnan(got.float()).any()))
+            m = oracle.error_metrics(got.cpu(), want[i].cpu())
+            worst = max(worst, m["max_abs"])
+            chk(f"{variant} step {i}: {m}", m["max_abs"] <= 2.0 ** -7 and m["cosine"] >= 0.99999)
+            dist.barrier()
+        chk(f"{variant}: status and positions", mine.workspace.read_status() == 0 and mine.seq_pos.cpu().tolist() == [x + steps for x in lens])
+        chk(f"{variant}: cache bytes", torch.equal(mine.k_cache, one.k_cache[:, :, kv]) and torch.equal(mine.v_cache, one.v_cache[:, :, kv]))
     if rank == 0:      # the last step's gathered tensor against the CPU oracle, first and last layer
         got = peer.current().cpu()
         final = [x + steps for x in lens]
@@ -197,8 +201,8 @@ def _big_worker(rank, world, port, ret):
                 vb[:, b, :, L:] = 0
             ref = oracle.decode_step_reference(q[layer:layer + 1].cpu(), kb, vb, ks[layer:layer + 1].cpu(), vs[layer:layer + 1].cpu(), final, cap)
             m = oracle.error_metrics(got[layer:layer + 1], ref)
-            ok = ok and m["max_abs"] <= 2e-2 and m["cosine"] >= 0.9999
-    _finish(dist, ret, rank, bool(ok))
+            chk(f"oracle layer {layer}: {m}", m["max_abs"] <= 2e-2 and m["cosine"] >= 0.9999)
+    _finish(dist, ret, rank, chk)
 
 
 def _sequence_worker(rank, world, port, ret):
