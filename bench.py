@@ -715,7 +715,8 @@ def run_ours(args) -> int:
     traffic = load_traffic(key, h["resolved"])
     one_gpu_bytes = kv_bytes_per_step(WORKLOADS[key][0]) if key in WORKLOADS else None
     line = {
-        "metric": METRIC, "value": h["sec"] * 1e6, "unit": "us/step", "n_gpus": world, "steps": h["steps"],
+        "metric": METRIC if args.layers == 64 else METRIC.replace("64 layers", f"{args.layers} layers: profiling only"),
+        "value": h["sec"] * 1e6, "unit": "us/step", "n_gpus": world, "steps": h["steps"],
         "warmup": args.warmup, "ms_per_step": h["sec"] * 1e3, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": DTYPES[h["resolved"]], "data": "synthetic",
         "config": make_config(key, world),
