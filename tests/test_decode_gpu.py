@@ -136,6 +136,31 @@ def test_split_counts_agree(pkg, oracle, cuda_device):
         assert (o.float() - outs[0].float()).abs().max().item() <= 2.0 ** -7
 
 
+@pytest.mark.parametrize("variant", ["mma", "umma2"])
+@pytest.mark.parametrize("h_q,h_kv,d", [(5, 1, 128), (8, 1, 128), (6, 1, 256), (10, 2, 128)])
+def test_one_pair_spread_over_the_whole_grid(pkg, oracle, cuda_device, variant, h_q, h_kv, d):
+    """A single layer with one or two KV heads and a long cache: every CTA of the persistent grid owns a piece of the
+    same (layer, kv head) pair, so the owner of the last piece collects dozens of partials (several rounds of the
+    split-K hand-over), for every accumulator width the kernels have (groups of 5, 6 and 8 heads; head_dim 128 and
+    256); twice on one workspace, plus a forced grid larger than the device holds at once."""
+    L, cap = 8000, 8192
+    case = build_case(oracle, 1, 1, h_q, h_kv, d, [L], cap, seed=77)
+    ref = oracle.decode_step_reference(case["q"], case["k_cache"], case["v_cache"], case["k_scale"], case["v_scale"],
+                                       case["lens"], cap)
+    dev = {k: (v.to(cuda_device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    shape = pkg.make_shape(h_q, dev["k_cache"], dev["v_cache"], dev["k_scale"])
+    seq = torch.tensor([L], dtype=torch.int32, device=cuda_device)
+    for n in (0, 1000):
+        ws = pkg.Workspace(shape, cuda_device, variant=variant, num_splits=n)
+        outs = [pkg.decode_attention(dev["q"], dev["k_cache"], dev["v_cache"], dev["k_scale"], dev["v_scale"], seq,
+                                     workspace=ws).clone() for _ in range(2)]
+        torch.cuda.synchronize()
+        assert ws.read_status() == 0
+        assert_parity(oracle, outs[0].cpu(), ref, f"{variant} {h_q}/{h_kv}/{d} ctas {ws.num_splits}")
+        assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+        assert int(ws.buf.max()) == 0, "a launch leaves its workspace zeroed"
+
+
 @pytest.mark.parametrize("variant", VARIANTS)
 def test_reference_model_shape(pkg, oracle, cuda_device, variant):
     """The reference's own head shape: 24 q / 4 kv heads (group 6), head_dim 256."""
