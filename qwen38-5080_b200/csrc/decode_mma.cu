@@ -56,7 +56,7 @@ template <int D>
 __device__ __noinline__ void append_rows_by_warp(int batch, int h_kv, int capacity, long long k_layer_stride,
                                                  long long v_layer_stride, const uint16_t* k_new, const uint16_t* v_new,
                                                  uint8_t* k_cache, uint8_t* v_cache, const float* k_scale, const float* v_scale,
-                                                 const int* seq_pos, int lane, long long r0, long long r1,
+                                                 const int* sPos, int lane, long long r0, long long r1,
                                                  const int* sCum, const int* sLen, int* status) {
   (void)status;
   Cursor a = locate(r0, sCum, sLen, batch, h_kv);
@@ -64,7 +64,7 @@ __device__ __noinline__ void append_rows_by_warp(int batch, int h_kv, int capaci
   while (cur < r1) {
     const long long pair_end = cur - a.tile + a.tiles_b;
     if (pair_end <= r1) {
-      const int pos = seq_pos[a.b];
+      const int pos = sPos[a.b];   // as the prologue read it
       if (pos >= 0 && pos < capacity) {
         const long long rowi = ((long long)a.layer * batch + a.b) * h_kv + a.h;
         B200ATTN_CHECK(status, a.b >= 0 && a.b < batch && a.h >= 0 && a.h < h_kv && a.layer >= 0 && pos / kTileT == a.tiles_b - 1);
@@ -122,6 +122,8 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   int* sFlags = reinterpret_cast<int*>(sComb + 1);                                    // [0] timed_out [2] any_empty [3] copies
   int* sLen = sFlags + 4;                                                             // [batch]
   int* sCum = sLen + g.batch;                                                         // [batch+1]
+  int* sPos = sCum + g.batch + 1;                                                     // [batch] the positions as read
+  int* sStep = sPos + g.batch;                                                        // the step counter as read
   volatile int* timed_out = sFlags;
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * stages;
   const uint32_t qfull0 = empty0 + 8u * stages, qempty0 = qfull0 + 16u;
@@ -145,10 +147,12 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     sComb->valid = 0;
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
-      int len = p.seq_len[b] + p.seq_len_offset;
+      const int raw = p.seq_len[b];
+      int len = raw + p.seq_len_offset;
       if (p.k_new && (len < 1 || len > g.capacity)) st |= B200ATTN_STATUS_POS_AT_CAPACITY;   // the new token has no slot
       if (len < 0) { len = 0; st |= B200ATTN_STATUS_LEN_NEGATIVE; }
       if (len > g.capacity) { len = g.capacity; st |= B200ATTN_STATUS_LEN_OVER_CAP; }
+      sPos[b] = raw;
       sLen[b] = len;
       sCum[b] = acc;
       acc += (len + kTileT - 1) / kTileT;
@@ -156,6 +160,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       uniform &= b == 0 || acc - sCum[b] == sCum[1] - sCum[0];
     }
     sCum[g.batch] = acc;
+    *sStep = peer_step(p);
     sFlags[2] = any_empty | (uniform ? 2 : 0);
     if (st && blockIdx.x == 0) atomicOr(p.status, st);
   }
@@ -164,18 +169,19 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
   }
   __syncthreads();
+  const int step = *sStep;
 
   // sequences of length 0 have no tiles: their outputs are zero, written by whoever gets there
   if (sFlags[2] & 1) {
     if (p.n_out) {   // tensor parallel: the destinations are needed here already (the epilogue warp writes them again later)
-      if (tid < 8) fill_peer_table(p, sPeer, tid);
+      if (tid < 8) fill_peer_table(p, sPeer, tid, step);
       __syncthreads();
     }
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
         for (int i = 2 * tid; i < g.h_q * D; i += 2 * kThreads)
-          emit_bits(p, sPeer, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
+          emit_bits(p, sPeer, step, r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
     }
   }
 
@@ -235,11 +241,12 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       // fused step: this warp is idle until the first segment ends; it appends the new rows of the pairs
       // whose last tile this CTA loads while the producer is already streaming the tiles before them
       append_rows_by_warp<D>(g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new, p.k_cache_w,
-                             p.v_cache_w, p.k_scale, p.v_scale, p.seq_len, lane, r0, r1, sCum, sLen, p.status);
+                             p.v_cache_w, p.k_scale, p.v_scale, sPos, lane, r0, r1, sCum, sLen, p.status);
       if (lane == 0) mbar_arrive(appended0);
     }
+    if (arrives_early(p)) arrive_early(p.seq_pos, p.exit_count, p.pkt ? p.epoch : nullptr, step, g.batch, g.capacity, lane);
     if (has_work)
-      epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer, sComb);
+      epilogue_warp<D, kDumpBufs>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer, sComb, step);
   } else if (has_work) {
     // ================================ consumer warps ================================
     Cursor c = locate(r0, sCum, sLen, g.batch, g.h_kv);
@@ -456,9 +463,9 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     }
   }
   // the pair whose last piece this CTA holds: all warps collect the other pieces (they end when this CTA's range does)
-  if (sComb->valid && !sFlags[0]) combine_deferred<D>(combine_args_of(p, sPeer), *sComb, warp, kThreads / 32, lane);
+  if (sComb->valid && !sFlags[0]) combine_deferred<D>(combine_args_of(p, sPeer, step), *sComb, warp, kThreads / 32, lane);
   if (p.bar_world) __syncthreads();   // stores mode: every warp's peer stores are fenced before the CTA counts as finished
-  end_of_launch(p, tid, kThreads);
+  end_of_launch(p, tid, kThreads, step);
 }
 
 constexpr int kStages = 3;   // ring depth.  A deeper ring where a small grid leaves shared memory unused (short caches, up to
@@ -474,7 +481,7 @@ size_t smem_bytes_for(const Geometry& g, int stages) {
   b += 64;                                                    // destinations of the tensor-parallel output
   b += sizeof(DeferredCombine);                               // the pair finished at the CTA's end
   b += 16;                                                    // flags
-  b += (size_t)(2 * g.batch + 1) * 4;                         // sLen, sCum
+  b += (size_t)(3 * g.batch + 2) * 4;                         // sLen, sCum, sPos, the step counter
   return (b + 15) & ~(size_t)15;
 }
 

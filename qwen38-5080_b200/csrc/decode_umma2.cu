@@ -109,7 +109,7 @@ __host__ __device__ inline size_t umma2_fixed_bytes(int group, int head_dim, int
   b += 64;                                                           // destinations of the tensor-parallel output
   b += sizeof(DeferredCombine);                                      // the pair finished at the CTA's end
   b += 32;                                                           // flags
-  b += (size_t)(2 * batch + 1) * 4;
+  b += (size_t)(3 * batch + 2) * 4;                                  // sLen, sCum, sPos, the step counter
   return b;
 }
 
@@ -122,7 +122,7 @@ template <int D, bool PT>
 __device__ __noinline__ void append_new_rows(int batch, int h_kv, int capacity, long long k_layer_stride,
                                              long long v_layer_stride, const uint16_t* k_new, const uint16_t* v_new,
                                              uint8_t* k_cache, uint8_t* v_cache, float* k_scale, float* v_scale,
-                                             const int* seq_pos, int tid, long long r0, long long r1,
+                                             const int* sPos, int tid, long long r0, long long r1,
                                              const int* sCum, const int* sLen, int* status) {
   (void)status;
   constexpr int VPL = D / 32;   // values per lane: 4 or 8
@@ -133,7 +133,7 @@ __device__ __noinline__ void append_new_rows(int batch, int h_kv, int capacity, 
   while (cur < r1) {
     const long long pair_end = cur - a.tile + a.tiles_b;
     if (pair_end <= r1) {
-      const int pos = seq_pos[a.b];
+      const int pos = sPos[a.b];   // as the prologue read it
       if (pos >= 0 && pos < capacity) {
 #pragma unroll 1
         for (int which = 0; which < 2; ++which, ++n) {
@@ -229,6 +229,8 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   int* sFlags = reinterpret_cast<int*>(sComb + 1);   // [0] timed_out [1] tmem [2] flags [3..7] issued counts
   int* sLen = sFlags + 8;
   int* sCum = sLen + g.batch;
+  int* sPos = sCum + g.batch + 1;   // [batch] the positions as read
+  int* sStep = sPos + g.batch;      // the step counter as read
   volatile int* timed_out = sFlags;
 
   if (tid == 0) {
@@ -251,10 +253,12 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     sComb->valid = 0;
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
-      int len = p.seq_len[b] + p.seq_len_offset;
+      const int raw = p.seq_len[b];
+      int len = raw + p.seq_len_offset;
       if (p.k_new && (len < 1 || len > g.capacity)) st |= B200ATTN_STATUS_POS_AT_CAPACITY;   // the new token has no slot
       if (len < 0) { len = 0; st |= B200ATTN_STATUS_LEN_NEGATIVE; }
       if (len > g.capacity) { len = g.capacity; st |= B200ATTN_STATUS_LEN_OVER_CAP; }
+      sPos[b] = raw;
       sLen[b] = len;
       sCum[b] = acc;
       acc += (len + kTile2 - 1) / kTile2;
@@ -262,6 +266,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
       uniform &= b == 0 || acc - sCum[b] == sCum[1] - sCum[0];
     }
     sCum[g.batch] = acc;
+    *sStep = peer_step(p);
     sFlags[2] = any_empty | (uniform ? 2 : 0);
     if (st && blockIdx.x == 0) atomicOr(p.status, st);
   }
@@ -274,17 +279,18 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)sFlags[1];
+  const int step = *sStep;
 
   if (sFlags[2] & 1) {
     if (p.n_out) {   // tensor parallel: the destinations are needed here already (the epilogue warp writes them again later)
-      if (tid < 8) fill_peer_table(p, sPeer, tid);
+      if (tid < 8) fill_peer_table(p, sPeer, tid, step);
       __syncthreads();
     }
     const long long rows = (long long)g.n_layers * g.batch;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
       if (sLen[r % g.batch] == 0)
         for (int i = 2 * tid; i < g.h_q * D; i += 2 * kThreads2)
-          emit_bits(p, sPeer, peer_step(p), r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
+          emit_bits(p, sPeer, step, r * g.h_q * D + i, (r * p.out_hq_total + p.out_head_base) * D + i, 0u);
     }
   }
 
@@ -351,8 +357,9 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
      
     }
   } else if (warp == kEpilogue2) {
+    if (arrives_early(p)) arrive_early(p.seq_pos, p.exit_count, p.pkt ? p.epoch : nullptr, step, g.batch, g.capacity, lane);
     if (has_work)
-      epilogue_warp<D, 1, NG, true, PT>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer, sComb);
+      epilogue_warp<D, 1, NG, true, PT>(p, lane, r0, r1, total, n_eff, sCum, sLen, sDump, sML, dfull0, dempty0, timed_out, sPeer, sComb, step);
   } else if (warp == kIssuerS2) {
     // ===================== S issuer warp: query operand, S = K q^T =====================
     if (has_work) {
@@ -487,7 +494,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     // ===== softmax warps: groups of four; group = tile index mod NG; one thread = one token / one output dim =====
     if (p.k_new) {
       append_new_rows<D, PT>(g.batch, g.h_kv, g.capacity, g.k_layer_stride, g.v_layer_stride, p.k_new, p.v_new,
-                             p.k_cache_w, p.v_cache_w, const_cast<float*>(p.k_scale), const_cast<float*>(p.v_scale), p.seq_len, tid,
+                             p.k_cache_w, p.v_cache_w, const_cast<float*>(p.k_scale), const_cast<float*>(p.v_scale), sPos, tid,
                              r0, r1, sCum, sLen, p.status);
       asm volatile("fence.proxy.async.global;" ::: "memory");   // the rows -> visible to the TMA loads of this CTA
       __syncwarp();
@@ -725,9 +732,9 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
   // the pair whose last piece this CTA holds: all warps collect the other pieces (they end when this CTA's range does)
-  if (sComb->valid && !sFlags[0]) combine_deferred<D>(combine_args_of(p, sPeer), *sComb, warp, kThreads2 / 32, lane);
+  if (sComb->valid && !sFlags[0]) combine_deferred<D>(combine_args_of(p, sPeer, step), *sComb, warp, kThreads2 / 32, lane);
   if (p.bar_world) __syncthreads();   // stores mode: every warp's peer stores are fenced before the CTA counts as finished
-  end_of_launch(p, tid, kThreads2);
+  end_of_launch(p, tid, kThreads2, step);
 }
 
 // Ring depths: all of the shared memory that the fixed part leaves, at most 4 K and 8 V tiles.

@@ -294,8 +294,7 @@ __device__ __forceinline__ int peer_buffer_base(int step) { return (step & 1) ? 
 // and value costs ~150 cycles, and so does an out-of-line call per value (both ~2 us per pair).
 //   packet mode: entry r = this rank's slot in rank r's staging buffer for this step's parity (0 for the own rank)
 //   stores mode: entry r = rank r's gathered tensor of this step's parity (0 beyond n_out)
-__device__ __forceinline__ void fill_peer_table(const MmaParams& p, unsigned long long* tab, int r) {   // entry r < 8
-  const int step = peer_step(p);
+__device__ __forceinline__ void fill_peer_table(const MmaParams& p, unsigned long long* tab, int r, int step) {   // entry r < 8
   unsigned long long v = 0;
   if (p.pkt) {
     if (p.out_peer[r]) v = (unsigned long long)p.out_peer[r] + (unsigned long long)(step & 1) * p.n_out * p.pkt_slot_words * 8ull;
@@ -429,8 +428,8 @@ struct CombineArgs {
   int* status;
   int G, n_out, pkt, step;
 };
-__device__ __forceinline__ CombineArgs combine_args_of(const MmaParams& p, const unsigned long long* peer_tab) {
-  return CombineArgs{p.ws_pkt, p.out, p.gate, peer_tab, p.status, p.g.group, p.n_out, p.pkt, peer_step(p)};
+__device__ __forceinline__ CombineArgs combine_args_of(const MmaParams& p, const unsigned long long* peer_tab, int step) {
+  return CombineArgs{p.ws_pkt, p.out, p.gate, peer_tab, p.status, p.g.group, p.n_out, p.pkt, step};
 }
 
 // All warps of c_last, after the CTA's last barrier.  Warp w takes heads w, w + nwarps, ...; lane j polls owner j's
@@ -547,16 +546,15 @@ __device__ __forceinline__ void epilogue_warp(const MmaParams& p, int lane, long
                                               long long total, int n_eff, const int* sCum, const int* sLen,
                                               const float* sDump, const float* sML, uint32_t dfull0,
                                               uint32_t dempty0, volatile int* timed_out, const unsigned long long* peer_tab,
-                                              DeferredCombine* deferred) {
+                                              DeferredCombine* deferred, int step) {
   constexpr int DP = D + 4;                // padded head row of a dumped state, in floats
   constexpr int UR = D / 64;               // dim pairs per epilogue lane
   const Geometry& g = p.g;
   const int G = g.group;
   const int dump_warp_floats = G * DP;
-  const int step = peer_step(p);
   uint32_t obuf[kMaxGroup * UR];   // peer mode: the bf16 rows of the pair being finished, sent together (send_pair)
   if (p.n_out) {
-    if (lane < 8) fill_peer_table(p, const_cast<unsigned long long*>(peer_tab), lane);
+    if (lane < 8) fill_peer_table(p, const_cast<unsigned long long*>(peer_tab), lane, step);
     __syncwarp();
   }
 {
@@ -795,15 +793,44 @@ __device__ __noinline__ void finish_step(StepEnd s, Unpack u, int unpack_all, in
   if (s.bar_world) warp_peer_barrier(s.flags, s.bar_rank, s.bar_world, lane, s.status);
 }
 
+// A launch whose end needs no election among the CTAs — a whole step on one GPU, or with the packet exchange on a grid
+// that is resident at once — advances the positions and the step counter as soon as every CTA has READ them, which
+// each does once, in its prologue (later uses take them from shared memory): an idle warp takes the arrival counter
+// right after the prologue, and the counter's round trip and the last arrival's updates run under the tile loop
+// instead of after the unpacking.
+__device__ __forceinline__ bool arrives_early(const MmaParams& p) {
+  return (p.seq_pos || p.pkt) && !p.bar_world && !(p.pkt && p.n_out > 1 && !p.pkt_resident);
+}
+__device__ __noinline__ void arrive_early(int* seq_pos, int* exit_count, int* step_counter, int step, int batch, int capacity, int lane) {
+  int last = 0;
+  if (lane == 0) {
+    int arrived;   // after this CTA's reads of positions and step counter (ordered by its __syncthreads), before the last arrival's writes
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(exit_count) : "memory");
+    last = arrived == (int)gridDim.x - 1;
+  }
+  if (!__shfl_sync(0xffffffffu, last, 0)) return;
+  if (seq_pos)
+    for (int b = lane; b < batch; b += 32) {
+      const int pos = seq_pos[b];
+      if (pos >= 0 && pos + 1 <= capacity) seq_pos[b] = pos + 1;
+    }
+  if (lane == 0) {
+    *exit_count = 0;   // ready for the next launch
+    if (step_counter) *step_counter = step;
+  }
+}
+
 // What every CTA does after its final __syncthreads when the launch is a whole step and / or sends packets.
-__device__ __forceinline__ void end_of_launch(const MmaParams& p, int tid, int nthreads) {
+// `step`: the step counter as the CTA's prologue read it.
+__device__ __forceinline__ void end_of_launch(const MmaParams& p, int tid, int nthreads, int step) {
   if (!(p.seq_pos || p.bar_world || p.pkt)) return;
-  const int step = peer_step(p);   // read before this CTA arrives at the exit counter: the last arrival advances it
   const bool receive = p.pkt && p.n_out > 1;
+  const bool early = arrives_early(p);
   if (receive && p.pkt_resident) {
     unpack_packets(unpack_of(p, step), (int)blockIdx.x, (int)gridDim.x, tid, nthreads);
-    __syncthreads();   // this CTA's copies are done before it counts as finished
+    if (!early) __syncthreads();   // this CTA's copies are done before it counts as finished
   }
+  if (early) return;
   if (tid < 32) finish_step(step_end_of(p, step), unpack_of(p, step), receive && !p.pkt_resident, tid);
 }
 
