@@ -173,8 +173,8 @@ int b200attn_workspace_bytes(const B200AttnShape* shape, int num_splits, int var
 
 /*
  * Zero the workspace (the partial words and the counter must start at zero; a launch that ends without a
- * status error leaves them at zero again).  Call once after allocation and after any call that reported a
- * status error.
+ * status error leaves them at zero again).  Call once after allocation, after any call that reported a
+ * status error, and before a workspace that served one kernel variant is handed to another.
  */
 int b200attn_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
