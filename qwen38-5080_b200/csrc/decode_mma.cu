@@ -19,11 +19,11 @@
 //   * at the end of a pair (or of the CTA's range) the consumer warps dump their (m, l, acc)
 //     state into a double-buffered shared-memory area and go straight on to the next pair; an
 //     epilogue warp merges the four states off the critical path.  A pair owned by one CTA is
-//     normalised and written directly; otherwise each owner writes an (m, l, acc) partial and
-//     takes an arrival ticket; the last arriver merges the partials in CTA order (deterministic,
-//     so replays are bitwise identical) and resets the ticket.  Nothing ever spins on another CTA.
-//     The only waits are on the CTA's own copy barriers, and those are bounded: on expiry the CTA flags B200ATTN_STATUS_WAIT_TIMEOUT, stops waiting, drains
-//     its copies and returns.
+//     normalised and written directly; otherwise each owner leaves its (m, l, acc) piece in the workspace as
+//     tagged 8-byte words, and the owner of the pair's last piece collects them with all its warps when its own
+//     range is done, in CTA order (deterministic, so replays are bitwise identical).  It only waits for CTAs of
+//     lower index.  Every wait — for copies, for pieces — is bounded: on expiry the CTA flags
+//     B200ATTN_STATUS_WAIT_TIMEOUT, stops waiting, drains its copies and returns.
 //
 // It replaces repeat_kv + eager attention + the capacity mask of the reference
 // (bench/micro/attn_length_effect.py:41-66, runner/model/static_cache.py:79-82) and follows the

@@ -26,11 +26,12 @@
 //      length are zeroed in shared memory first (their bytes may be NaN patterns);
 //   6. at the end of a segment each group reads its O once (one thread per dim), adds the terms
 //      per head, and hands its state (m, l, acc) to the epilogue warp, which merges the four
-//      states, writes the output or a split-K partial, and as the last owner of a pair to arrive
-//      merges the pair's partials.
+//      states and writes the output or a split-K partial (tagged words); the CTA that holds a split pair's
+//      last piece collects the pair's partials with all its warps when its own range is done.
 // The same launch can be the whole decode step: the new token's K/V rows are quantised into the
-// cache by the CTA that is going to load the tile that holds them, and the last CTA to finish
-// advances the positions (and, tensor-parallel, does the cross-GPU arrive-and-wait).
+// cache by the CTA that is going to load the tile that holds them, and the last CTA to have read the
+// positions advances them (stores mode, tensor-parallel: the last CTA to finish, which also does the
+// cross-GPU arrive-and-wait).
 // Query groups of up to 5 heads use 16 probability-operand rows (3 G <= 16), groups of 6 to 8 an instance
 // with 32 rows.
 //
