@@ -257,9 +257,12 @@ class StepRunner:
             self.cache.prefill(k, v, calibrate=not scales_done and scale_mode == "per_head")
             scales_done = True
         self.start_pos = torch.tensor([d if advance else d - 1 for d in self.depths], dtype=torch.int32, device=device)
-        self.q = torch.randn(N_LAYERS, batch, h_q, D, generator=g, device=device, dtype=torch.bfloat16)
-        self.k_new = torch.randn(N_LAYERS, batch, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
-        self.v_new = torch.randn(N_LAYERS, batch, h_kv, D, generator=g, device=device, dtype=torch.bfloat16)
+        # the step's inputs share one device buffer, so that a host that owns them can send them with one copy
+        nq, nk = N_LAYERS * batch * h_q * D, N_LAYERS * batch * h_kv * D
+        self.inputs = torch.randn(nq + 2 * nk, generator=g, device=device, dtype=torch.bfloat16)
+        self.q = self.inputs[:nq].view(N_LAYERS, batch, h_q, D)
+        self.k_new = self.inputs[nq:nq + nk].view(N_LAYERS, batch, h_kv, D)
+        self.v_new = self.inputs[nq + nk:].view(N_LAYERS, batch, h_kv, D)
         self.out = torch.empty_like(self.q)
         distmod = importlib.import_module("qwen38-5080_b200.dist")
         self.peer = None
@@ -442,7 +445,7 @@ def timed_e2e(torch, dist, world, runner, steps, warmup) -> tuple[float, int, in
     stays on the device, where its consumer is).  The copies and the step are captured into one CUDA
     graph (memcpy nodes + the library's launch), as a host that replays its decode step would do; two
     steps per graph, because the stores mode of the tensor-parallel step alternates between two gathered buffers."""
-    hq, hk, hv = (t.cpu().pin_memory() for t in (runner.q, runner.k_new, runner.v_new))
+    hin = runner.inputs.cpu().pin_memory()   # q, k_new, v_new of the step: one pinned buffer, one copy
     if runner.peer is not None:
         rank, hq_loc, peer = runner.peer.rank, runner.h_q, runner.peer
         tensors = [peer.full, peer.full] if peer.mode == "packets" else [peer.buffers[(peer.steps_done() + 1 + i) & 1] for i in range(2)]
@@ -450,14 +453,12 @@ def timed_e2e(torch, dist, world, runner, steps, warmup) -> tuple[float, int, in
     else:
         sources = [runner.result()] * 2
     hout = torch.empty(sources[0].shape, dtype=sources[0].dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+    h2d = hin.numel() * hin.element_size()
     d2h = hout.numel() * hout.element_size()
 
     def sequence():
         for src in sources:
-            runner.q.copy_(hq, non_blocking=True)
-            runner.k_new.copy_(hk, non_blocking=True)
-            runner.v_new.copy_(hv, non_blocking=True)
+            runner.inputs.copy_(hin, non_blocking=True)
             runner.launch_step()
             if runner.gatherer is not None:
                 runner.gather()
