@@ -371,8 +371,8 @@ int b200attn_qk_norm_rope_append(const B200AttnShape* shape,
  * With the stream-K kernels (B200ATTN_VARIANT_UMMA2 for both scale layouts, B200ATTN_VARIANT_MMA
  * for per-head scales, i.e. whatever AUTO resolves to where a tensor-core kernel applies) the step
  * is ONE launch: the CTA that owns the tile holding a pair's new token quantises that row first
- * (per-token layout: after computing and storing its scale), and the last CTA to finish advances
- * the positions; the CUDA-core variant launches append, attention and the position kernel one
+ * (per-token layout: after computing and storing its scale), and the last CTA to have read the
+ * positions advances them; the CUDA-core variant launches append, attention and the position kernel one
  * after the other.  Cache bytes, scales, positions and status bits are the same either way.
  */
 int b200attn_append_decode(const B200AttnShape* shape,
