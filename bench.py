@@ -161,6 +161,9 @@ class ClockSampler:
         if self.handle is not None:
             self.thread = threading.Thread(target=self._loop, daemon=True)
             self.thread.start()
+            t0 = time.time()     # NVML's first queries are slow: they are over before anything is timed
+            while len(self.samples) < 2 and time.time() - t0 < 1.0:
+                time.sleep(0.005)
         return self
 
     def __exit__(self, *exc):
