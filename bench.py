@@ -13,7 +13,9 @@ heads of the single-sequence workloads are sharded (tensor parallel, strong scal
 step ends with the all-gather of the per-head outputs over NVLink, fused into the kernel.
 
 Protocol (the reference's: within-run step distribution apart from between-run spread,
-runner/report.py:228-258): W warm-up steps, then K steps between two CUDA events — that pass is
+runner/report.py:228-258): 30 ms of the workload's own steps so that the clocks are up (a pass of the
+short-cache workload lasts one millisecond), then W warm-up steps (the secondary workloads: at least
+20), then K steps between two CUDA events — that pass is
 `value` — then four more such passes (median / min / max over the five) and one pass with an event
 pair around every step (p50 / p95).  After the clock has stopped, two layers of the step's result
 are compared with the CPU oracle and reported as "parity".
@@ -390,8 +392,26 @@ def timed_pass(torch, dist, world, runner, steps, warmup, per_step=False):
     return max_over_ranks(torch, dist, world, runner.device, e0.elapsed_time(e1) / 1e3 / steps), None
 
 
+def prewarm(torch, dist, world, runner, steps, seconds=0.03) -> None:
+    """Keep the GPU busy with the workload's own steps for a few tens of milliseconds before anything is timed: a
+    workload whose timed pass lasts a millisecond would otherwise be measured while the clocks still come up from
+    the idle period of its set-up.  Positions are reset every `steps` steps so that the cache cannot overflow."""
+    t0 = time.time()
+    while True:
+        runner.reset_pos()
+        for _ in range(steps):
+            runner.step()
+        torch.cuda.synchronize()
+        done = torch.tensor([1.0 if time.time() - t0 >= seconds else 0.0], device=runner.device)
+        if world > 1:   # every rank leaves the loop in the same round (tensor-parallel steps wait for each other)
+            dist.all_reduce(done, op=dist.ReduceOp.MIN)
+        if done.item() > 0:
+            break
+
+
 def measure(torch, dist, world, runner, steps, warmup) -> dict:
     """The protocol of the module docstring for one workload; seconds."""
+    prewarm(torch, dist, world, runner, steps)
     passes = [timed_pass(torch, dist, world, runner, steps, warmup)[0] for _ in range(PASSES)]
     _, each = timed_pass(torch, dist, world, runner, steps, warmup, per_step=True)
     return {"first": passes[0], "passes": passes, "each": each}
