@@ -720,6 +720,7 @@ def run_ours(args) -> int:
                                     "copies": L2_FREE_COPIES, "note": "this rank's heads, no exchange; the step rotates through "
                                     f"{L2_FREE_COPIES} caches so that none of them stays in L2"}
         entry.update(stats_entry(m))
+        entry["clocks"] = sampler.summary()     # this workload's own timed passes
         if waits is not None:
             entry["exchange_wait_us"] = {"min": min(waits), "max": max(waits),
                                          "note": "last step: from a rank's arrival at the in-launch barrier to its release"}
