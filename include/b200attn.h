@@ -314,7 +314,7 @@ int b200attn_peer_barrier(void* const* flags, int rank, int world, int* status, 
  * takes its scratch from torch's allocator).  For hosts that may not allocate device memory where
  * they call the library — memory owned and budgeted by a framework pool, or a step that cannot
  * afford cudaMalloc's device synchronisation.  The split-K partials of the tensor-core
- * stream-K kernel (B200ATTN_VARIANT_MMA) live in a fixed 4 MiB array inside the library image
+ * stream-K kernel (B200ATTN_VARIANT_MMA) live in a fixed 8 MiB array inside the library image
  * (b200attn_static_scratch_bytes()), held by every GPU that loads the library until exit.
  *   - a request whose workspace would not fit returns B200ATTN_ERR_TOO_LARGE, nothing launched
  *     (fits: 64 layers x bs 1 with the default CTA count; check b200attn_workspace_bytes);

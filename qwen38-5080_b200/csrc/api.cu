@@ -148,7 +148,7 @@ const char* b200attn_error_string(int code) {
     case B200ATTN_ERR_CUDA: return "CUDA call failed";
     case B200ATTN_ERR_CAPACITY: return "length exceeds capacity";
     case B200ATTN_ERR_VARIANT: return "unknown kernel variant";
-    case B200ATTN_ERR_TOO_LARGE: return "request exceeds the fixed scratch of b200attn_decode_static (4 MiB)";
+    case B200ATTN_ERR_TOO_LARGE: return "request exceeds the fixed scratch of b200attn_decode_static (8 MiB)";
   }
   return "unknown error code";
 }

@@ -18,7 +18,7 @@
 
 namespace {
 
-constexpr size_t kStaticScratchBytes = 4u << 20;   // 4 MiB: 296 CTAs x 2 partials x (5 x 128 + 16) tagged 8-byte words = 3.0 MiB
+constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB: 444 CTAs x 2 partials x (5 x 128 + 16) tagged 8-byte words = 4.7 MB
 constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];

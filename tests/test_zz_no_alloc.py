@@ -25,7 +25,7 @@ def _call_static(lib, shape, dev, seq, scale, num_splits, out, status):
 
 def test_static_scratch_entry_point_matches_workspace_entry_point(pkg, oracle, cuda_device):
     lib = pkg._lib.lib()
-    assert lib.b200attn_static_scratch_bytes() == 4 << 20
+    assert lib.b200attn_static_scratch_bytes() == 8 << 20
     for lens, cap, n_layers in (([700, 333], 1024, 4), ([1000], 1024, 16)):
         case = build_case(oracle, n_layers, len(lens), 40, 8, 128, lens, cap, seed=7)
         dev = {k: (v.to(cuda_device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
@@ -52,6 +52,27 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(pkg, oracle, c
         assert m["max_abs"] <= TOL_MAX_ABS and m["cosine"] >= TOL_COSINE, m
 
 
+def test_static_scratch_holds_the_long_cache_grid(pkg, oracle, cuda_device):
+    """444 CTAs (three per SM: the grid of the mma.sync kernel on a long cache of the benchmark's head shape) fit the
+    fixed scratch; split pairs, so the partials go through it."""
+    lib = pkg._lib.lib()
+    lens, cap, n_layers = [8000], 8192, 8
+    case = build_case(oracle, n_layers, 1, 40, 8, 128, lens, cap, seed=11)
+    dev = {k: (v.to(cuda_device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    shape = pkg.make_shape(40, dev["k_cache"], dev["v_cache"], dev["k_scale"])
+    seq = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+    ref = oracle.decode_step_reference(case["q"], case["k_cache"], case["v_cache"], case["k_scale"], case["v_scale"], lens, cap)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    for call in range(2):
+        out = torch.full((n_layers, 1, 40, 128), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+        rc = _call_static(lib, shape, dev, seq, 128 ** -0.5, 444, out, status)
+        assert rc == 0, lib.b200attn_error_string(rc)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        m = oracle.error_metrics(out.cpu(), ref)
+        assert m["max_abs"] <= TOL_MAX_ABS and m["cosine"] >= TOL_COSINE, (call, m)
+
+
 def test_static_scratch_rejects_what_does_not_fit(pkg, cuda_device):
     """Refusals happen on the host, before the shared scratch is touched or anything is launched.  The
     pointers are real (small) tensors all the same: should the order of the checks ever change, the
@@ -62,7 +83,7 @@ def test_static_scratch_rejects_what_does_not_fit(pkg, cuda_device):
     a = buf.data_ptr()
     rc = lib.b200attn_decode_static(ctypes.byref(big), a, a, a, a, a, a, 0, 0.1, 4000, a, a, None)
     assert rc == pkg._lib.ERR_TOO_LARGE
-    assert b"4 MiB" in lib.b200attn_error_string(rc)
+    assert b"8 MiB" in lib.b200attn_error_string(rc)
     assert lib.b200attn_decode_static(None, a, a, a, a, a, a, 0, 0.1, 0, a, a, None) == pkg._lib.ERR_NULL
     small = pkg.B200AttnShape(1, 1, 40, 8, 128, 64, 0, 0, 0, 0)
     assert lib.b200attn_decode_static(ctypes.byref(small), a + 4, a, a, a, a, a, 0, 0.1, 0, a, a, None) == pkg._lib.ERR_ALIGN
