@@ -79,10 +79,12 @@ DTYPES = {"umma2": "fp8-e4m3 KV fed to tcgen05 as stored; query as two e4m3 term
           "simt": "fp8-e4m3 KV, fp32 CUDA-core products, fp32 accumulate/softmax, bf16 in/out"}
 
 
-def kernel_name(variant: str, per_token: bool = False) -> str:
-    """Name of the dominant kernel as a profiler lists it, for the head shape of this run."""
+def kernel_name(variant: str, per_token: bool = False, ctas: int = 0, sms: int = 148) -> str:
+    """Name of the dominant kernel as a profiler lists it, for the head shape of this run (the mma.sync kernel has an
+    instance for grids of up to two CTAs per SM and one for three)."""
     group = H_Q // H_KV
-    return {"simt": f"attn_splitk_simt_kernel<{D},{group}>", "mma": f"attn_streamk_mma_kernel<{D}, *>",
+    inst = "*" if D != 128 or ctas <= 0 else ("2" if ctas <= 2 * sms else "3")
+    return {"simt": f"attn_splitk_simt_kernel<{D},{group}>", "mma": f"attn_streamk_mma_kernel<{D}, {inst}>",
             "umma2": f"attn_streamk_umma2_kernel<{D}, {'true' if per_token else 'false'}, {5 if group <= 5 else 8}>"}[variant]
 
 
@@ -730,6 +732,7 @@ def run_ours(args) -> int:
         if is_headline:
             e2e_sec, h2d, d2h = timed_e2e(torch, dist, world, runner, steps, args.warmup)
             headline = {"key": key, "sec": sec, "ksec": ksec, "clocks": sampler.summary(), "steps": steps, "m": m,
+                        "ctas": runner.cache.workspace.num_splits, "sms": torch.cuda.get_device_properties(device).multi_processor_count,
                         "resolved": runner.cache.workspace.resolved, "per_token": runner.cache.per_token,
                         "launches": runner.kernels_per_step(), "bytes_per_launch": bytes_per_launch, "total_bytes": total_bytes,
                         "e2e": (e2e_sec, h2d, d2h), "parity": parity, "entry": entry}
@@ -753,7 +756,7 @@ def run_ours(args) -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None if traffic is None or not one_gpu_bytes else traffic * h["bytes_per_launch"] / one_gpu_bytes,
                      "traffic_note": "ncu DRAM bytes of a 16-layer launch on one GPU, scaled by the KV bytes this launch reads",
-                     "kernel": kernel_name(h["resolved"], h["per_token"]), "peak_kind": peak_kind,
+                     "kernel": kernel_name(h["resolved"], h["per_token"], h["ctas"], h["sms"]), "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": h["bytes_per_launch"], "launch_us": h["ksec"] * 1e6},
         "e2e": {"value": h["e2e"][0] * 1e6, "unit": "us/step", "h2d_bytes_per_step": h["e2e"][1], "d2h_bytes_per_step": h["e2e"][2]},
         "gpu_launches": h["launches"] * h["steps"],
