@@ -4,7 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
 
 A "step" is one decode step of the attention path for all 64 layers: quantize-and-append of the
-new token's K/V plus split-K GQA attention over the FP8 cache, replayed as one CUDA graph.
+new token's K/V plus split-K GQA attention over the FP8 cache: one kernel launch, replayed from CUDA
+graphs (five steps to a graph in the timed passes, so that the host's replay rate cannot be the limit
+of a 20 us step; single steps where every step is timed by itself).
 Headline workload (cfg2): depth 8192, capacity 8192, bs=1, H_q=40, H_kv=8, D=128; the cache is
 full, so every step re-quantises the newest token into the last slot and attends 8192 tokens.
 The other depths of the metric (512, 32768) are measured in the same run under "per_depth", the
@@ -13,7 +15,7 @@ heads of the single-sequence workloads are sharded (tensor parallel, strong scal
 step ends with the all-gather of the per-head outputs over NVLink, fused into the kernel.
 
 Protocol (the reference's: within-run step distribution apart from between-run spread,
-runner/report.py:228-258): 30 ms of the workload's own steps so that the clocks are up (a pass of the
+runner/report.py:228-258): 10 ms or more of the workload's own steps so that the clocks are up (a pass of the
 short-cache workload lasts one millisecond), then W warm-up steps (the secondary workloads: at least
 20), then K steps between two CUDA events — that pass is
 `value` — then four more such passes (median / min / max over the five) and one pass with an event
@@ -44,6 +46,7 @@ sys.path.insert(0, str(ROOT))
 
 N_LAYERS, H_Q, H_KV, D = 64, 40, 8, 128
 METRIC = "decode-attn us/step (64 layers)"
+STEPS_PER_GRAPH = 5
 WORKLOADS = {
     # name: (depth, capacity, advance)
     "cfg1": (512, 1024, True),
@@ -126,7 +129,7 @@ def make_config(key: str, world: int) -> dict:
           f"KV working set ({per_gpu / 1e6:.0f} MB per GPU) smaller than L2: L2-warm figure; an L2-free figure that rotates "
           f"{L2_FREE_COPIES} cache copies is reported beside it where measured")
     return {"workload": workload_name(key), "sharding": sharding, "l2": l2,
-            "execution": "one CUDA-graph replay per step: quantize-append + split-K attention + combine"
+            "execution": f"CUDA-graph replays of {STEPS_PER_GRAPH} steps, one launch per step: quantize-append + split-K attention + combine"
                          + (" + output all-gather over NVLink, in the same launch" if world > 1 and key != "cfg4" else "")}
 
 
@@ -279,6 +282,7 @@ class StepRunner:
         elif world > 1 and tensor_parallel:
             self.gatherer = distmod.HeadGather(self.out, world)
         self.graph = None
+        self.graph_multi = None
         self.gather_in_graph = False
 
     def launch_step(self):
@@ -333,6 +337,27 @@ class StepRunner:
                 self.launch_step()
         torch.cuda.synchronize()
         self.reset_pos()
+        # The same step STEPS_PER_GRAPH times in one graph, for the timed passes: a 20 us step replayed one by one
+        # from Python is at the edge of what the host can issue (the pass then times the host, 22.5 us a step on the
+        # slower hosts of the pool), and a caller with steps that short would not replay them one by one either.
+        if self.gatherer is None or self.gather_in_graph:
+            self.graph_multi = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph_multi):
+                for _ in range(STEPS_PER_GRAPH):
+                    self.launch_step()
+                    if self.gatherer is not None:
+                        self.gather()
+            torch.cuda.synchronize()
+            self.reset_pos()
+
+    def run(self, n: int):
+        """n steps: graphs of STEPS_PER_GRAPH steps, the remainder one by one."""
+        if self.graph_multi is not None:
+            while n >= STEPS_PER_GRAPH:
+                self.graph_multi.replay()
+                n -= STEPS_PER_GRAPH
+        for _ in range(n):
+            self.step()
 
     def reset_pos(self):
         self.cache.seq_pos.copy_(self.start_pos)
@@ -369,8 +394,7 @@ def timed_pass(torch, dist, world, runner, steps, warmup, per_step=False):
     Returns seconds per step (max over ranks); with per_step=True an event pair brackets every step
     instead and the list of this rank's step times (seconds) is returned too."""
     runner.reset_pos()
-    for _ in range(warmup):
-        runner.step()
+    runner.run(warmup)
     torch.cuda.synchronize()
     barrier(dist, world)
     torch.cuda.synchronize()
@@ -386,23 +410,21 @@ def timed_pass(torch, dist, world, runner, steps, warmup, per_step=False):
         return max_over_ranks(torch, dist, world, runner.device, sum(each) / steps), each
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        runner.step()
+    runner.run(steps)
     e1.record()
     torch.cuda.synchronize()
     barrier(dist, world)
     return max_over_ranks(torch, dist, world, runner.device, e0.elapsed_time(e1) / 1e3 / steps), None
 
 
-def prewarm(torch, dist, world, runner, steps, seconds=0.03) -> None:
-    """Keep the GPU busy with the workload's own steps for a few tens of milliseconds before anything is timed: a
+def prewarm(torch, dist, world, runner, steps, seconds=0.01) -> None:
+    """Keep the GPU busy with the workload's own steps for ten milliseconds or more before anything is timed: a
     workload whose timed pass lasts a millisecond would otherwise be measured while the clocks still come up from
     the idle period of its set-up.  Positions are reset every `steps` steps so that the cache cannot overflow."""
     t0 = time.time()
     while True:
         runner.reset_pos()
-        for _ in range(steps):
-            runner.step()
+        runner.run(steps)
         torch.cuda.synchronize()
         done = torch.tensor([1.0 if time.time() - t0 >= seconds else 0.0], device=runner.device)
         if world > 1:   # every rank leaves the loop in the same round (tensor-parallel steps wait for each other)
