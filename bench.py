@@ -16,8 +16,8 @@ step ends with the all-gather of the per-head outputs over NVLink, fused into th
 
 Protocol (the reference's: within-run step distribution apart from between-run spread,
 runner/report.py:228-258): 10 ms or more of the workload's own steps so that the clocks are up (a pass of the
-short-cache workload lasts one millisecond), then W warm-up steps (the secondary workloads: at least
-20), then K steps between two CUDA events — that pass is
+short-cache workload lasts one millisecond), then W warm-up steps, then K steps between two CUDA events —
+that pass is
 `value` — then four more such passes (median / min / max over the five) and one pass with an event
 pair around every step (p50 / p95).  After the clock has stopped, two layers of the step's result
 are compared with the CPU oracle and reported as "parity".
@@ -420,11 +420,13 @@ def timed_pass(torch, dist, world, runner, steps, warmup, per_step=False):
 def prewarm(torch, dist, world, runner, steps, seconds=0.01) -> None:
     """Keep the GPU busy with the workload's own steps for ten milliseconds or more before anything is timed: a
     workload whose timed pass lasts a millisecond would otherwise be measured while the clocks still come up from
-    the idle period of its set-up.  Positions are reset every `steps` steps so that the cache cannot overflow."""
+    the idle period of its set-up.  A few steps at a time (positions reset each time), so that a workload whose step
+    takes milliseconds is not run hot before its first pass either."""
     t0 = time.time()
+    chunk = min(steps, STEPS_PER_GRAPH)
     while True:
         runner.reset_pos()
-        runner.run(steps)
+        runner.run(chunk)
         torch.cuda.synchronize()
         done = torch.tensor([1.0 if time.time() - t0 >= seconds else 0.0], device=runner.device)
         if world > 1:   # every rank leaves the loop in the same round (tensor-parallel steps wait for each other)
@@ -655,13 +657,13 @@ def build_runner(pkg, torch, device, dist, world, rank, key, args):
         depths_all = cfg4_depths(torch)
         plan = pkg.dist.assign_sequences(depths_all, world)
         depths = [depths_all[i] for i in plan[rank]]
-        steps = max(1, min(args.steps, 256 - max(args.warmup, 20) - 8))
+        steps = max(1, min(args.steps, 256 - args.warmup - 8))
         runner = StepRunner(pkg, torch, device, depths, CFG4_CAP, True, H_Q, H_KV, seed=rank, dist=dist, world=world,
                             variant=args.variant, num_splits=args.ctas, tensor_parallel=False)
         loads = [sum(depths_all[i] for i in p) for p in plan]
         return runner, steps, {"plan": plan, "depths": depths_all, "loads": loads}
     depth, cap, advance = WORKLOADS[key]
-    room = cap - depth - max(args.warmup, 20) - 8 if advance else 1 << 30   # the cache must not overflow
+    room = cap - depth - args.warmup - 8 if advance else 1 << 30   # the cache must not overflow
     steps = max(1, min(args.steps, room))
     runner = StepRunner(pkg, torch, device, [depth], cap, advance, H_Q // world, H_KV // world, seed=rank, dist=dist, world=world,
                         variant=args.variant, num_splits=args.ctas, gather=args.gather, scale_mode=args.scales)
@@ -701,9 +703,7 @@ def run_ours(args) -> int:
             torch.cuda.synchronize()
             dist.barrier()
         is_headline = key == args.workload
-        # the headline workload gets exactly W warm-up steps; the others at least 20 (a 20 us step needs more than a
-        # handful before the first timed pass is representative)
-        warm = args.warmup if is_headline else max(args.warmup, 20)
+        warm = args.warmup
         with ClockSampler(torch, local) as sampler:
             m = measure(torch, dist, world, runner, steps, warm)
             ksec = timed_kernel(torch, runner, steps, warm)
