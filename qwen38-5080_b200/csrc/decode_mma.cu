@@ -145,6 +145,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     sFlags[0] = 0; sFlags[1] = 0; sFlags[3] = 0;
     sComb->valid = 0;
+    pdl_wait();   // the kernel before this one has completed: positions, cache rows and workspace are as it left them
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
       const int raw = p.seq_len[b];
@@ -169,6 +170,7 @@ attn_streamk_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
     asm volatile("prefetch.tensormap [%0];" ::"l"(&vmap) : "memory");
   }
   __syncthreads();
+  if (tid == 0) pdl_launch_dependents();
   const int step = *sStep;
 
   // sequences of length 0 have no tiles: their outputs are zero, written by whoever gets there
@@ -564,8 +566,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const DecodeArgs& a, cudaStream
       if (e != cudaSuccess) return e;
       p.pkt_resident = (long long)per_sm * device_sms() >= n ? 1 : 0;
     }
-    kernel<<<n, kThreads, smem, stream>>>(kmap, vmap, p);
-    return cudaGetLastError();
+    return launch_pdl(kernel, n, kThreads, smem, stream, kmap, vmap, p);
   };
   if (g.head_dim != 128) return launch(attn_streamk_mma_kernel<256, 1>);
   return n <= 2 * device_sms() ? launch(attn_streamk_mma_kernel<128, 2>) : launch(attn_streamk_mma_kernel<128, kCtasPerSm>);

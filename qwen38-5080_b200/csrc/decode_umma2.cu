@@ -252,6 +252,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     sFlags[0] = 0; sFlags[3] = 0; sFlags[4] = 0; sFlags[5] = 0; sFlags[6] = 0; sFlags[7] = 0;
     sComb->valid = 0;
+    pdl_wait();   // the kernel before this one has completed: positions, cache rows and workspace are as it left them
     int acc = 0, any_empty = 0, st = 0, uniform = 1;
     for (int b = 0; b < g.batch; ++b) {
       const int raw = p.seq_len[b];
@@ -280,6 +281,7 @@ attn_streamk_umma2_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)sFlags[1];
+  if (tid == 0) pdl_launch_dependents();
   const int step = *sStep;
 
   if (sFlags[2] & 1) {
@@ -818,8 +820,7 @@ cudaError_t launch_decode_umma2(const Geometry& g, const DecodeArgs& a, cudaStre
       if (e != cudaSuccess) return e;
       p.pkt_resident = (long long)per_sm * device_sms() >= n ? 1 : 0;
     }
-    kernel<<<n, kThreads2, pl.bytes, stream>>>(kmap, vmap, p);
-    return cudaGetLastError();
+    return launch_pdl(kernel, n, kThreads2, pl.bytes, stream, kmap, vmap, p);
   };
   const bool pt = g.scale_mode == B200ATTN_SCALE_PER_TOKEN, wide = g.group > 5;
   if (g.head_dim == 128) {

@@ -133,6 +133,14 @@ __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy) : "memory");
 }
+// Programmatic dependent launch: the stream-K kernels are launched with programmatic stream serialization, so their
+// CTAs may become resident while the kernel before them in the stream is still finishing (the set-up of the CTA's
+// barriers and tensor memory runs meanwhile); pdl_wait() returns once that kernel has completed and its memory is
+// visible — it stands before the CTA's first read of global memory — and pdl_launch_dependents() lets the next
+// kernel's CTAs in as soon as SMs have room.  A kernel launched without the attribute sees both as no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
@@ -840,6 +848,22 @@ __device__ __forceinline__ void end_of_launch(const MmaParams& p, int tid, int n
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// <<<grid, threads, smem, stream>>> with programmatic stream serialization (see pdl_wait).
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_pdl(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 inline EncodeTiledFn get_encode_fn() {
   static EncodeTiledFn fn = nullptr;
