@@ -228,6 +228,10 @@ int b200attn_kv_quant_append_bulk(const B200AttnShape* shape, int n_tokens,
  *   num_splits   : from b200attn_pick_splits (0 = pick for capacity and 148 SMs)
  *   out          : bf16 [n_layers][batch][h_q][head_dim]  (the reference's
  *                  out.transpose(1,2).contiguous() layout, attn_length_effect.py:66)
+ * The tensor-core kernels are launched with programmatic stream serialization: their thread blocks
+ * may become resident while the previous kernel of the stream is finishing and wait for its
+ * completion on the device before they read anything.  Nothing changes for the caller: stream order
+ * holds, and the launch is captured into CUDA graphs like any other.
  */
 int b200attn_decode(const B200AttnShape* shape,
                     const void* q_bf16,
