@@ -684,9 +684,10 @@ __device__ __forceinline__ void warp_peer_barrier(int* const* flags, int rank, i
   }
 }
 
-// Last act of a launch that is a whole decode step, called by warp 0 of every CTA after the CTA's final
-// __syncthreads (all of the CTA's reads of the positions and all its output stores are done): the warp of the
-// last CTA to arrive advances the positions and, tensor-parallel, does the cross-GPU arrive-and-wait.
+// Last act of a launch whose end does need an election among the CTAs (stores mode: someone has to run the cross-GPU
+// barrier after everybody's peer stores; packets on a grid that is not resident at once: someone has to unpack after
+// everything is sent; see arrives_early for all other launches), called by warp 0 of every CTA after the CTA's final
+// __syncthreads: the warp of the last CTA to arrive advances the positions and does the barrier or the unpacking.
 // Out of line: it runs once per CTA and must not cost the tile loops registers.  Its arguments travel by value:
 // handing the kernel's parameter block to an out-of-line function by reference takes that block's address, and
 // the tile loops then read their parameters through memory instead of as constant operands (measured: +6 % on
