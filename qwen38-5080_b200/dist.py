@@ -24,14 +24,42 @@ def head_shard(h_q: int, h_kv: int, world: int, rank: int) -> tuple[slice, slice
 
 
 def assign_sequences(depths: list[int], world: int) -> list[list[int]]:
-    """Greedy longest-first assignment of sequence indices to ranks, balancing total depth
-    (ties broken by rank index, so every rank computes the same plan)."""
+    """Assignment of sequence indices to ranks that balances total depth: greedy longest-first, then moves and swaps
+    between pairs of ranks for as long as one lowers the larger load of its pair (with two sequences per rank the
+    greedy plan alone leaves the busiest rank 18 % above the mean on the benchmark's ragged batch).  Deterministic
+    (ties broken by index), so every rank computes the same plan.  A rank may end up with no sequence only when
+    there are fewer sequences than ranks."""
     load = [0] * world
     plan: list[list[int]] = [[] for _ in range(world)]
     for idx in sorted(range(len(depths)), key=lambda i: (-depths[i], i)):
         r = min(range(world), key=lambda j: (load[j], len(plan[j]), j))
         plan[r].append(idx)
         load[r] += depths[idx]
+    # pairwise balancing: the move or swap between any two ranks that lowers the larger of their two loads the most;
+    # every accepted step lowers the sum of squared loads, so this ends by itself (the bound is a safety belt)
+    for _ in range(64 * max(1, len(depths)) * world):
+        best = None                                     # (gain, kind, a, b, i, j)
+        for a in range(world):
+            for b in range(world):
+                if b == a or load[a] <= load[b]:
+                    continue
+                for i in plan[a]:
+                    if len(plan[a]) > 1:                # move i from a to b
+                        gain = load[a] - max(load[a] - depths[i], load[b] + depths[i])
+                        if gain > 0 and (best is None or (-gain, 0, a, b, i, -1) < best):
+                            best = (-gain, 0, a, b, i, -1)
+                    for j in plan[b]:                   # swap i and j
+                        gain = load[a] - max(load[a] - depths[i] + depths[j], load[b] - depths[j] + depths[i])
+                        if gain > 0 and (best is None or (-gain, 1, a, b, i, j) < best):
+                            best = (-gain, 1, a, b, i, j)
+        if best is None:
+            break
+        _, kind, a, b, i, j = best
+        plan[a].remove(i); plan[b].append(i)
+        load[a] -= depths[i]; load[b] += depths[i]
+        if kind == 1:
+            plan[b].remove(j); plan[a].append(j)
+            load[b] -= depths[j]; load[a] += depths[j]
     for p in plan:
         p.sort()
     return plan

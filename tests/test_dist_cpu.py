@@ -31,7 +31,7 @@ def test_head_shard_and_sequence_plan():
         assert sorted(i for p in plan for i in p) == list(range(16))
         loads = [sum(depths[i] for i in p) for p in plan]
         assert max(loads) - min(loads) <= max(depths)          # greedy bound
-        assert max(loads) <= 1.25 * sum(depths) / world
+        assert max(loads) <= 1.08 * sum(depths) / world          # greedy alone: 1.18 on 8 ranks (two sequences per rank)
 
 
 def _worker(rank, world, port, ret):
